@@ -1,0 +1,184 @@
+/*
+ * moddit.h — C ABI of the B200 (sm_100a) implementation of the MOD-DiT sparse-attention hot path.
+ *
+ * Conventions for every entry point
+ *   - plain pointers and sizes only; all tensor pointers are DEVICE pointers owned by the caller;
+ *   - nothing is allocated or freed, and the host is never synchronised with the device: all work
+ *     is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream);
+ *   - the return value is 0 on success or a negative MODDIT_E_* code; a message for the last
+ *     failure on the calling thread is available from moddit_last_error_string();
+ *   - q/k/v/out tensors are contiguous (BH, N, D) — "HND" with batch folded into heads — of
+ *     `dtype` MODDIT_BF16 or MODDIT_FP16, 16-byte aligned;
+ *   - "map" tensors are the reference's block sparsity maps: (H, n, n) float16, 1 = nothing there.
+ *
+ * Each declaration cites the reference interface it replaces (paths inside the MOD-DiT project).
+ */
+#ifndef MODDIT_H_
+#define MODDIT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MODDIT_BF16 0
+#define MODDIT_FP16 1
+
+#define MODDIT_OK 0
+#define MODDIT_E_ARG (-1)         /* null pointer, negative size, inconsistent arguments */
+#define MODDIT_E_UNSUPPORTED (-2) /* head_dim / block_size / size outside what the kernels cover */
+#define MODDIT_E_ALIGN (-3)       /* pointer not 16-byte aligned */
+#define MODDIT_E_WORKSPACE (-4)   /* workspace pointer null or too small */
+#define MODDIT_E_CUDA (-5)        /* a CUDA runtime/driver call failed (message has the detail) */
+#define MODDIT_E_DEVICE (-6)      /* device is not compute capability 10.x */
+
+/* layout codes for masks (token order of the sequence) — MoD/mod/triton_flash_sparsity.py:101-120 */
+#define MODDIT_LAYOUT_WAN 0       /* video only */
+#define MODDIT_LAYOUT_HUNYUAN 1   /* video first, then text */
+#define MODDIT_LAYOUT_COGVIDEOX 2 /* text first, then video */
+
+/* per-head mode codes — MoD/mod/attn_mask.py:408-410,484-486 */
+#define MODDIT_MODE_SPARSE 0
+#define MODDIT_MODE_BLOCK_DIAGONAL 1
+#define MODDIT_MODE_FULL 2
+
+/* Version of this ABI (bumped on any signature change). */
+int moddit_abi_version(void);
+/* Message describing the last failure on the calling thread ("" if none). */
+const char* moddit_last_error_string(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Block mean-pooling of Q and K (no reference function; the specification's first stage.  Nearest
+ * reference call site: MoD/mod/attn_mask.py:611-614).
+ *   x    : (BH, N, D) bf16/fp16            out : (BH, ceil(N/block_size), D) float32
+ * The last block may be short; its mean is over the tokens present.
+ */
+int moddit_pool_blocks(const void* x, int dtype, int BH, int N, int D, int block_size,
+                       float* out, void* stream);
+
+/* Pooled stand-in for the sparsity map: map[h,i,j] = 1 - softmax_j(qbar[h,qo+i,:].kbar[h,ko+j,:]*scale)
+ * over the n video blocks, written as float16 (no reference function; consumed exactly like the
+ * reference map of MoD/mod/triton_flash_sparsity.py:275-341).
+ *   qbar,kbar : (BH, nb, D) float32      map : (BH, n, n) float16
+ */
+int moddit_pooled_map(const float* qbar, const float* kbar, int BH, int nb, int D,
+                      int q_block_offset, int k_block_offset, int n, float scale,
+                      void* map_f16, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Exact sparsity-map replay.  Replaces the pybind function `sparsity_map(q,k,lse,scale,log_thr,
+ * q_off,k_off,video_blocks,block_size)` of MoD/mod/cuda_flash_sparsity_kernel.cu:289-334 (kernel
+ * :41-169) and the Triton twin MoD/mod/triton_flash_sparsity.py:28-98,181-225.
+ *   q,k : (BH, N, D); lse : (BH, N) float32 natural log; map : (BH, n, n) float16
+ *   map = count(S[r,c] < lse[r] + log_threshold) / block_size^2 with S = round_dtype(q*scale) k^T.
+ */
+int moddit_replay_map(const void* q, const void* k, const float* lse, int dtype, int BH, int N, int D,
+                      int block_size, float softmax_scale, float log_threshold, int q_video_offset,
+                      int k_video_offset, int video_blocks, void* map_f16, void* stream);
+
+/* Reads and clears the status words of the replay kernel on the current device (code, block, role,
+ * position; all zero unless a bounded wait inside the kernel expired, in which case the maps written
+ * since the last call are invalid).  Synchronises `stream`.  No reference counterpart: the reference
+ * kernel has no waits. */
+int moddit_replay_status(int32_t* host_status4, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * M^T S: diagonal sums (offsets -(n-1)..n-1), column sums and the per-frame block-diagonal sum of
+ * every head's map, in one pass.  Replaces `compute_mts(S_T, blocks_per_frame)` of
+ * MoD/mod/cuda_lstsq_kernel.cu:421-482 (kernels :17-162) and `compute_mts_pytorch`
+ * (MoD/mod/cuda_lstsq.py:91-139).  Optionally first merges history as MoD/mod/attn_mask.py:671-675
+ * does: merged = keep_mask ? cur : prev, written to `merged_out` (may alias `prev`).
+ *   map        : (H, n, n) float16 (current map)
+ *   prev       : NULL or (H, n, n) float16       keep_mask : NULL or bool bytes; element (h,i,j) at
+ *                keep_mask[h*mask_head_stride + (i+mask_off)*mask_row_stride + (j+mask_off)]
+ *   mts        : (H, 3n) float32 = [2n-1 diagonals | n columns | 1 block]
+ *   workspace  : moddit_mts_workspace_bytes(H, n) bytes of scratch (contents irrelevant on entry)
+ */
+size_t moddit_mts_workspace_bytes(int H, int n);
+int moddit_mts(const void* map_f16, const void* prev_f16, const uint8_t* keep_mask,
+               int64_t mask_head_stride, int64_t mask_row_stride, int mask_off, void* merged_out_f16,
+               int H, int n, int blocks_per_frame, float* mts, void* workspace, size_t workspace_bytes,
+               void* stream);
+
+/* Structural Gram matrix M^T M + reg*I, (3n x 3n) float32.  Replaces `compute_mtm(S_T, bpf, reg)` of
+ * MoD/mod/cuda_lstsq_kernel.cu:319-418 and `compute_mtm_pytorch` (MoD/mod/cuda_lstsq.py:42-89). */
+int moddit_mtm(int n, int blocks_per_frame, float regularization, float* mtm, void* stream);
+
+/* One-time set-up of the solve for a geometry (n, blocks_per_frame, regularization): eliminates the
+ * 2n-1 diagonal unknowns analytically and inverts the remaining (n+1)x(n+1) system in float64.
+ * Replaces the cached `torch.linalg.cholesky(MTM)` of MoD/mod/cuda_lstsq.py:153-186.
+ *   factor    : moddit_solve_factor_bytes(n) bytes, filled here, read by moddit_solve
+ *   workspace : moddit_solve_prepare_workspace_bytes(n) bytes of scratch
+ */
+size_t moddit_solve_factor_bytes(int n);
+size_t moddit_solve_prepare_workspace_bytes(int n);
+int moddit_solve_prepare(int n, int blocks_per_frame, double regularization, void* factor,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* X = (M^T M + reg I)^-1 M^T S for all heads.  Replaces `_solve_all_heads` /
+ * `torch.cholesky_solve` of MoD/mod/cuda_lstsq.py:189-208,245-261.
+ *   mts : (H, 3n) float32        X : (H, 3n) float32, same unknown order
+ *   workspace : moddit_solve_workspace_bytes(H, n) bytes of scratch
+ */
+size_t moddit_solve_workspace_bytes(int H, int n);
+int moddit_solve(const float* mts, const void* factor, int H, int n, int blocks_per_frame,
+                 double regularization, float* X, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Line selection.  Replaces `choose_topk_lines` (MoD/mod/attn_mask.py:351-370): extrapolate
+ * cur + (cur-last)/predict_T for verticals c (H,n) and diagonals d (H,2n-1), concatenate [c | d],
+ * pick the k = min(top_k, 3n-1) smallest per head.  Output (H,k) int64 indices in ascending
+ * (value, index) order; equal values are taken lowest index first, NaN sorts last.
+ */
+int moddit_select_lines(const float* cur_c, const float* cur_d, const float* last_c, const float* last_d,
+                        int H, int n, int top_k, float predict_T, int64_t* selected, void* stream);
+
+/* Per-head mode from the last block-diagonal coefficient: b_d <= threshold -> BLOCK_DIAGONAL else
+ * SPARSE.  Replaces `check_bd_values` (MoD/mod/attn_mask.py:336-349) as called at :408-410. */
+int moddit_head_modes(const float* b_d, int H, float threshold, int32_t* modes, void* stream);
+
+/* Bool block mask from selected lines.  Replaces `generate_mask_from_lines`
+ * (MoD/mod/attn_mask.py:440-559).  mask: (H, nbt, nbt) bool bytes where nbt = n for WAN and the total
+ * number of blocks otherwise; text rows/columns are all true; the video region is the union of the
+ * selected columns/diagonals, plus row/bpf == col/bpf for BLOCK_DIAGONAL heads; FULL heads are all true.
+ */
+int moddit_mask_from_lines(const int64_t* selected, int k, const int32_t* modes, int H, int n,
+                           int blocks_per_frame, int layout, int text_blocks, int nbt, uint8_t* mask,
+                           void* stream);
+
+/* Cumulative-mass selection on a darkness map (no reference function).  keep: (H,n,n) bool bytes. */
+int moddit_select_mass(const void* map_f16, int H, int n, float tau, uint8_t* keep, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Work lists for the sparse forward: for each (mask head, pair of 128-row query tiles) the key tiles
+ * that either tile needs, ascending, each as (key_tile << 8) | (flagsB << 4) | flagsA where flag bit
+ * (2*row_half + col_half) marks a kept 64x64 quarter (block_size 128: 0 or 0xF).
+ *   mask    : (Hm, nbq, nbk) bool bytes, blocks of `block_size` tokens on the grid that starts at token 0
+ *   counts  : (Hm, npairs) int32      entries : (Hm, npairs, ntiles) int32,
+ *   npairs = ceil(ceil(N/128)/2), ntiles = ceil(N/128); key blocks >= kv_block_limit are dropped.
+ * Re-encodes the mask that MoD/mod/attn_mask.py:297-317 hands to the third-party sparse kernel.
+ */
+int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, int block_size, int N,
+                      int kv_block_limit, int32_t* counts, int32_t* entries, void* stream);
+
+/* Block-sparse flash-attention forward.  Replaces `AttentionSparseEngine` (MoD/mod/attn_mask.py:266-331:
+ * block_sparse_sage2_attn_cuda for video rows, flashinfer prefill for text rows, sageattn for all-true
+ * masks) and, with all-true lists and `lse` non-null, the dense pass of
+ * MoD/mod/triton_flash_sparsity.py:314-324.
+ *   q,k,v,out : (BH, N, D); head bh uses lists of mask head bh % Hm
+ *   rows < q_split attend keys < kv_len_lo, other rows keys < kv_len_hi
+ *   lse       : NULL or (BH, N) float32 natural-log row log-sum-exp
+ *   status    : device int32[4], zeroed by the caller; non-zero afterwards means a bounded wait
+ *               expired inside the kernel (status[0]=code, [1]=block, [2]=role) and `out` is invalid
+ */
+int moddit_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
+                           const int32_t* counts, const int32_t* entries, int Hm, float softmax_scale,
+                           int q_split, int kv_len_lo, int kv_len_hi, void* out, float* lse,
+                           int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MODDIT_H_ */

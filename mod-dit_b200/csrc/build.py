@@ -1,0 +1,82 @@
+"""Builds libmoddit.so (all CUDA kernels + the C ABI) for sm_100a with nvcc, in-tree.
+
+    python mod-dit_b200/csrc/build.py [--verbose] [--force]
+
+Object files go to mod-dit_b200/csrc/build/, the library to mod-dit_b200/moddit_b200/libmoddit.so.
+Only sources newer than their objects are recompiled.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+OUT_DIR = os.path.join(os.path.dirname(HERE), "moddit_b200")
+LIB = os.path.join(OUT_DIR, "libmoddit.so")
+SOURCES = ["api.cu", "tmap.cu", "pool.cu", "lstsq.cu", "select.cu", "replay.cu", "sparse_attn.cu"]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", HERE,
+]
+
+
+def find_nvcc() -> str:
+    cand = shutil.which("nvcc") or os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found (set CUDA_HOME)")
+    return cand
+
+
+def newer(a: str, b: str) -> bool:
+    return not os.path.exists(b) or os.path.getmtime(a) > os.path.getmtime(b)
+
+
+def build(verbose: bool = False, force: bool = False) -> str:
+    nvcc = find_nvcc()
+    obj_dir = os.path.join(HERE, "build")
+    os.makedirs(obj_dir, exist_ok=True)
+    headers = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith((".cuh", ".h"))]
+    headers.append(os.path.join(ROOT, "include", "moddit.h"))
+    hdr_time = max(os.path.getmtime(h) for h in headers)
+    jobs = []
+    objs = []
+    for src in SOURCES:
+        s = os.path.join(HERE, src)
+        o = os.path.join(obj_dir, src[:-3] + ".o")
+        objs.append(o)
+        if force or newer(s, o) or hdr_time > os.path.getmtime(o):
+            cmd = [nvcc, *NVCC_FLAGS, "-c", s, "-o", o]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            jobs.append(cmd)
+
+    def run(cmd):
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        return cmd, res
+
+    with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
+        for cmd, res in pool.map(run, jobs):
+            if verbose or res.returncode != 0:
+                sys.stderr.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
+            if res.returncode != 0:
+                raise RuntimeError(f"nvcc failed on {cmd[-3]}")
+    if jobs or not os.path.exists(LIB):
+        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError("link of libmoddit.so failed")
+    return LIB
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--force", action="store_true")
+    a = ap.parse_args()
+    print(build(a.verbose, a.force))

@@ -1,0 +1,535 @@
+// Least-squares fit of a block map onto the (diagonals | verticals | per-frame block diagonal) basis.
+//
+// Unknown order everywhere: [2n-1 diagonals, offset -(n-1)..n-1 | n verticals | 1 block], F = 3n.
+//
+// mts      : one pass over the map.  A CTA stages 32 map rows in shared memory (optionally merging
+//            history on the way in), then threads own a column / a diagonal and walk down the rows,
+//            so no atomics are needed; per-tile partial sums go to scratch and a second small
+//            kernel adds them in a fixed order (deterministic).  Algorithmic traffic: H*n*n*2 bytes.
+// mtm      : closed-form Gram matrix (kept for API parity; the solve below never forms it).
+// solve    : the Gram matrix is  [[Dd+lI, A, b], [A^T, (n+l)I, c], [b^T, c^T, e+l]]  with Dd diagonal,
+//            so the 2n-1 diagonal unknowns are eliminated analytically; products with A and A^T are
+//            prefix/suffix/window sums.  What remains is a data-independent (n+1)x(n+1) SPD system
+//            whose inverse is computed once per geometry in float64 (solve_prepare); a solve is then
+//            two scans, one (n+1)^2 matrix-vector product per head and an elementwise back-substitution.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace moddit {
+namespace {
+
+constexpr int kTileRows = 32;
+constexpr int kMtsThreads = 256;
+
+__device__ __forceinline__ double block_sum_double(double v, double* scratch) {
+  // scratch: at least 32 doubles of shared memory
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  double t = 0.0;
+  if (warp == 0) {
+    t = (lane < (blockDim.x + 31) / 32) ? scratch[lane] : 0.0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) scratch[0] = t;
+  }
+  __syncthreads();
+  t = scratch[0];
+  __syncthreads();
+  return t;
+}
+
+// Partial layout per (head, tile): [n + kTileRows - 1 diagonal partials | n column partials], then one double.
+__global__ void __launch_bounds__(kMtsThreads) mts_partial_kernel(
+    const __half* __restrict__ map, const __half* __restrict__ prev, const uint8_t* __restrict__ keep,
+    int64_t mask_head_stride, int64_t mask_row_stride, int mask_off, __half* __restrict__ merged, int n, int bpf,
+    float* __restrict__ part_f, double* __restrict__ part_blk) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __half* tile = reinterpret_cast<__half*>(smem_raw);            // [kTileRows][n]
+  __shared__ double red[32];
+
+  const int h = blockIdx.y;
+  const int tiles = gridDim.x;
+  const int i0 = blockIdx.x * kTileRows;
+  const int rows = min(kTileRows, n - i0);
+  const int tid = threadIdx.x;
+  const int64_t span0 = (static_cast<int64_t>(h) * n + i0) * n;  // first element of the tile
+  const int len = rows * n;
+
+  if (prev == nullptr) {
+    // contiguous span of rows*n halves: scalar head until 16-byte aligned, 128-bit body, scalar tail
+    const __half* src = map + span0;
+    const int mis = static_cast<int>((reinterpret_cast<uintptr_t>(src) >> 1) & 7);
+    const int head = min(len, (8 - mis) & 7);
+    for (int e = tid; e < head; e += kMtsThreads) tile[e] = src[e];
+    const int body = (len - head) / 8;
+    const uint4* vsrc = reinterpret_cast<const uint4*>(src + head);
+    for (int e = tid; e < body; e += kMtsThreads) {
+      const uint4 v = __ldg(vsrc + e);
+      // shared destination is only 2-byte aligned in general: store as halves
+      const __half* hv = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) tile[head + e * 8 + u] = hv[u];
+    }
+    for (int e = head + body * 8 + tid; e < len; e += kMtsThreads) tile[e] = src[e];
+  } else {
+    const uint8_t* kh = keep + static_cast<int64_t>(h) * mask_head_stride;
+    for (int e = tid; e < len; e += kMtsThreads) {
+      const int r = e / n, j = e - r * n;
+      const bool kp = kh[static_cast<int64_t>(i0 + r + mask_off) * mask_row_stride + (j + mask_off)] != 0;
+      const __half v = kp ? map[span0 + e] : prev[span0 + e];
+      tile[e] = v;
+      merged[span0 + e] = v;
+    }
+  }
+  __syncthreads();
+
+  float* pf = part_f + (static_cast<int64_t>(h) * tiles + blockIdx.x) * (2 * n + kTileRows - 1);
+  // diagonals of the tile: index dd = (j - r) + kTileRows - 1 in [0, n + kTileRows - 1)
+  for (int dd = tid; dd < n + kTileRows - 1; dd += kMtsThreads) {
+    const int d = dd - (kTileRows - 1);
+    float s = 0.f;
+    for (int r = 0; r < rows; ++r) {
+      const int j = d + r;
+      if (j >= 0 && j < n) s += __half2float(tile[r * n + j]);
+    }
+    pf[dd] = s;
+  }
+  for (int j = tid; j < n; j += kMtsThreads) {
+    float s = 0.f;
+    for (int r = 0; r < rows; ++r) s += __half2float(tile[r * n + j]);
+    pf[n + kTileRows - 1 + j] = s;
+  }
+  // per-frame block-diagonal: rows/cols below cov = (n / bpf) * bpf with row/bpf == col/bpf
+  const int cov = (n / bpf) * bpf;
+  double bsum = 0.0;
+  for (int e = tid; e < rows * bpf; e += kMtsThreads) {
+    const int r = e / bpf, c = e - r * bpf;
+    const int i = i0 + r;
+    if (i < cov) bsum += static_cast<double>(__half2float(tile[r * n + (i / bpf) * bpf + c]));
+  }
+  bsum = block_sum_double(bsum, red);
+  if (tid == 0) part_blk[static_cast<int64_t>(h) * tiles + blockIdx.x] = bsum;
+}
+
+__global__ void __launch_bounds__(256) mts_finish_kernel(const float* __restrict__ part_f,
+                                                         const double* __restrict__ part_blk, int n, int tiles,
+                                                         float* __restrict__ mts) {
+  const int h = blockIdx.y;
+  const int x = blockIdx.x * blockDim.x + threadIdx.x;
+  const int F = 3 * n;
+  if (x >= F) return;
+  const int stride = 2 * n + kTileRows - 1;
+  const float* pf = part_f + static_cast<int64_t>(h) * tiles * stride;
+  float out;
+  if (x < 2 * n - 1) {
+    const int o = x - (n - 1);
+    float s = 0.f;
+    for (int t = 0; t < tiles; ++t) {
+      // tile-local diagonal d = j - r = o + i0
+      const int dd = o + t * kTileRows + (kTileRows - 1);
+      if (dd >= 0 && dd < n + kTileRows - 1) s += pf[static_cast<int64_t>(t) * stride + dd];
+    }
+    out = s;
+  } else if (x < 3 * n - 1) {
+    const int j = x - (2 * n - 1);
+    float s = 0.f;
+    for (int t = 0; t < tiles; ++t) s += pf[static_cast<int64_t>(t) * stride + n + kTileRows - 1 + j];
+    out = s;
+  } else {
+    double s = 0.0;
+    for (int t = 0; t < tiles; ++t) s += part_blk[static_cast<int64_t>(h) * tiles + t];
+    out = static_cast<float>(s);
+  }
+  mts[static_cast<int64_t>(h) * F + x] = out;
+}
+
+__global__ void mtm_kernel(int n, int bpf, float reg, float* __restrict__ mtm) {
+  const int F = 3 * n;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(F) * F) return;
+  int a = static_cast<int>(idx / F), b = static_cast<int>(idx % F);
+  const bool diag = (a == b);
+  if (a > b) {  // symmetric: evaluate the upper triangle
+    const int t = a;
+    a = b;
+    b = t;
+  }
+  const int nd = 2 * n - 1;
+  const int nb = n / bpf, cov = nb * bpf;
+  float v = 0.f;
+  if (a < nd) {
+    const int o = a - (n - 1);
+    const int ao = o < 0 ? -o : o;
+    if (b < nd) {
+      v = diag ? static_cast<float>(n - ao) : 0.f;
+    } else if (b < nd + n) {
+      const int j = b - nd;
+      v = (o >= 0 ? (j >= o) : (j < n + o)) ? 1.f : 0.f;
+    } else {
+      v = (ao < bpf) ? static_cast<float>(nb * (bpf - ao)) : 0.f;
+    }
+  } else if (a < nd + n) {
+    const int j = a - nd;
+    if (b < nd + n) {
+      v = diag ? static_cast<float>(n) : 0.f;
+    } else {
+      v = (j < cov) ? static_cast<float>(bpf) : 0.f;
+    }
+  } else {
+    v = static_cast<float>(nb * bpf * bpf);
+  }
+  if (diag) v = __fadd_rn(v, reg);
+  mtm[idx] = v;
+}
+
+// ---- solve set-up -------------------------------------------------------------------------------
+// factor layout (doubles): Sinv[(n+1)^2] | w[2n-1] | wb[2n-1]      (w = 1/(n-|o|+l), wb = w*b)
+// workspace (doubles)    : pw[2n] | pwb[2n] | row[n+1] | col[n+1] | scalars[2]
+
+__global__ void solve_vectors_kernel(int n, int bpf, double lam, double* __restrict__ w, double* __restrict__ wb,
+                                     double* __restrict__ pw, double* __restrict__ pwb,
+                                     double* __restrict__ scalars) {
+  // single thread: 2n-1 terms, runs once per geometry
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  const int nd = 2 * n - 1;
+  const int nb = n / bpf;
+  double accw = 0.0, accwb = 0.0, bwb = 0.0;
+  pw[0] = 0.0;
+  pwb[0] = 0.0;
+  for (int oi = 0; oi < nd; ++oi) {
+    const int o = oi - (n - 1);
+    const int ao = o < 0 ? -o : o;
+    const double wi = 1.0 / (static_cast<double>(n - ao) + lam);
+    const double bi = (ao < bpf) ? static_cast<double>(nb) * (bpf - ao) : 0.0;
+    w[oi] = wi;
+    wb[oi] = wi * bi;
+    accw += wi;
+    accwb += wi * bi;
+    bwb += wi * bi * bi;
+    pw[oi + 1] = accw;      // exclusive prefix at index oi+1
+    pwb[oi + 1] = accwb;
+  }
+  scalars[0] = bwb;
+}
+
+__global__ void schur_build_kernel(int n, int bpf, double lam, const double* __restrict__ pw,
+                                   const double* __restrict__ pwb, const double* __restrict__ scalars,
+                                   double* __restrict__ S) {
+  const int m = n + 1;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(m) * m) return;
+  const int a = static_cast<int>(idx / m), b = static_cast<int>(idx % m);
+  const int nb = n / bpf, cov = nb * bpf;
+  double v;
+  if (a < n && b < n) {
+    const int lo = a < b ? a : b, hi = a < b ? b : a;
+    // sum of w over offsets o in [hi-n+1, lo]  ->  prefix indices [hi, lo+n)
+    v = -(pw[lo + n] - pw[hi]);
+    if (a == b) v += static_cast<double>(n) + lam;
+  } else if (a == n && b == n) {
+    v = static_cast<double>(nb) * bpf * bpf + lam - scalars[0];
+  } else {
+    const int j = a < n ? a : b;
+    v = ((j < cov) ? static_cast<double>(bpf) : 0.0) - (pwb[j + n] - pwb[j]);
+  }
+  S[idx] = v;
+}
+
+// In-place Gauss-Jordan inversion of an SPD matrix, one pivot per pair of launches.
+__global__ void gj_save_kernel(const double* __restrict__ A, int m, int k, double* __restrict__ row,
+                               double* __restrict__ col) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= m) return;
+  row[i] = A[static_cast<int64_t>(k) * m + i];
+  col[i] = A[static_cast<int64_t>(i) * m + k];
+}
+
+__global__ void gj_update_kernel(double* __restrict__ A, int m, int k, const double* __restrict__ row,
+                                 const double* __restrict__ col) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int i = blockIdx.y;
+  if (j >= m) return;
+  const double p = 1.0 / row[k];
+  double v;
+  if (i == k) {
+    v = (j == k) ? p : row[j] * p;
+  } else if (j == k) {
+    v = -col[i] * p;
+  } else {
+    v = A[static_cast<int64_t>(i) * m + j] - col[i] * row[j] * p;
+  }
+  A[static_cast<int64_t>(i) * m + j] = v;
+}
+
+// ---- per-call solve -----------------------------------------------------------------------------
+// workspace (doubles): g[H][n+1] | y[H][n+1]
+
+constexpr int kSolveThreads = 512;
+
+// Inclusive block scan of `vals` (length len) in shared memory, in place; every thread takes part.
+__device__ void block_scan_inclusive(double* vals, int len, double* carry_smem) {
+  // chunked: each thread scans a contiguous chunk, then chunk totals are scanned by thread 0
+  const int per = (len + blockDim.x - 1) / blockDim.x;
+  const int beg = min(len, static_cast<int>(threadIdx.x) * per);
+  const int end = min(len, beg + per);
+  double run = 0.0;
+  for (int e = beg; e < end; ++e) {
+    run += vals[e];
+    vals[e] = run;
+  }
+  carry_smem[threadIdx.x] = run;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double acc = 0.0;
+    for (int t = 0; t < static_cast<int>(blockDim.x); ++t) {
+      const double v = carry_smem[t];
+      carry_smem[t] = acc;
+      acc += v;
+    }
+  }
+  __syncthreads();
+  const double off = carry_smem[threadIdx.x];
+  for (int e = beg; e < end; ++e) vals[e] += off;
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kSolveThreads) solve_rhs_kernel(const float* __restrict__ mts,
+                                                                  const double* __restrict__ w,
+                                                                  const double* __restrict__ wb, int n,
+                                                                  double* __restrict__ g) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  double* t = reinterpret_cast<double*>(smem_raw);   // [2n-1] -> inclusive prefix of w*rd
+  double* carry = t + (2 * n - 1);                   // [kSolveThreads]
+  __shared__ double red[32];
+  const int h = blockIdx.x;
+  const int nd = 2 * n - 1;
+  const float* r = mts + static_cast<int64_t>(h) * 3 * n;
+  double dot = 0.0;
+  for (int oi = threadIdx.x; oi < nd; oi += kSolveThreads) {
+    const double rd = static_cast<double>(r[oi]);
+    t[oi] = w[oi] * rd;
+    dot += wb[oi] * rd;
+  }
+  __syncthreads();
+  block_scan_inclusive(t, nd, carry);
+  dot = block_sum_double(dot, red);
+  double* gh = g + static_cast<int64_t>(h) * (n + 1);
+  for (int j = threadIdx.x; j < n; j += kSolveThreads) {
+    // sum_{o=j-n+1..j} t[o] -> indices oi in [j, j+n-1]
+    const double win = t[j + n - 1] - (j > 0 ? t[j - 1] : 0.0);
+    gh[j] = static_cast<double>(r[nd + j]) - win;
+  }
+  if (threadIdx.x == 0) gh[n] = static_cast<double>(r[nd + n]) - dot;
+}
+
+// y = Sinv * g for one head; Sinv is symmetric, so thread i walks column i (coalesced across threads).
+__global__ void __launch_bounds__(128) solve_gemv_kernel(const double* __restrict__ Sinv,
+                                                         const double* __restrict__ g, int m,
+                                                         double* __restrict__ y) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  double* gs = reinterpret_cast<double*>(smem_raw);
+  const int h = blockIdx.y;
+  for (int j = threadIdx.x; j < m; j += blockDim.x) gs[j] = g[static_cast<int64_t>(h) * m + j];
+  __syncthreads();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= m) return;
+  double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+  int j = 0;
+  for (; j + 3 < m; j += 4) {
+    a0 = fma(Sinv[static_cast<int64_t>(j) * m + i], gs[j], a0);
+    a1 = fma(Sinv[static_cast<int64_t>(j + 1) * m + i], gs[j + 1], a1);
+    a2 = fma(Sinv[static_cast<int64_t>(j + 2) * m + i], gs[j + 2], a2);
+    a3 = fma(Sinv[static_cast<int64_t>(j + 3) * m + i], gs[j + 3], a3);
+  }
+  for (; j < m; ++j) a0 = fma(Sinv[static_cast<int64_t>(j) * m + i], gs[j], a0);
+  y[static_cast<int64_t>(h) * m + i] = (a0 + a1) + (a2 + a3);
+}
+
+__global__ void __launch_bounds__(kSolveThreads) solve_back_kernel(const float* __restrict__ mts,
+                                                                   const double* __restrict__ w,
+                                                                   const double* __restrict__ wb,
+                                                                   const double* __restrict__ y, int n,
+                                                                   float* __restrict__ X) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  double* pc = reinterpret_cast<double*>(smem_raw);  // [n] inclusive prefix of c
+  double* carry = pc + n;                            // [kSolveThreads]
+  const int h = blockIdx.x;
+  const int nd = 2 * n - 1;
+  const double* yh = y + static_cast<int64_t>(h) * (n + 1);
+  const float* r = mts + static_cast<int64_t>(h) * 3 * n;
+  float* xh = X + static_cast<int64_t>(h) * 3 * n;
+  for (int j = threadIdx.x; j < n; j += kSolveThreads) {
+    pc[j] = yh[j];
+    xh[nd + j] = static_cast<float>(yh[j]);
+  }
+  const double e = yh[n];
+  if (threadIdx.x == 0) xh[nd + n] = static_cast<float>(e);
+  __syncthreads();
+  block_scan_inclusive(pc, n, carry);
+  const double total = pc[n - 1];
+  for (int oi = threadIdx.x; oi < nd; oi += kSolveThreads) {
+    const int o = oi - (n - 1);
+    // (A c)[o] = sum_{j>=o} c_j for o >= 0 ; sum_{j<n+o} c_j for o < 0
+    const double ac = (o >= 0) ? (total - (o > 0 ? pc[o - 1] : 0.0)) : pc[n + o - 1];
+    xh[oi] = static_cast<float>(w[oi] * (static_cast<double>(r[oi]) - ac) - wb[oi] * e);
+  }
+}
+
+}  // namespace
+}  // namespace moddit
+
+using namespace moddit;
+
+static int check_n(const char* who, int n) {
+  if (n < 1 || n > 4096) return fail(MODDIT_E_UNSUPPORTED, "%s: n=%d video blocks outside [1, 4096]", who, n);
+  return MODDIT_OK;
+}
+
+extern "C" size_t moddit_mts_workspace_bytes(int H, int n) {
+  if (H <= 0 || n <= 0) return 0;
+  const size_t tiles = static_cast<size_t>(ceil_div(n, kTileRows));
+  const size_t f = static_cast<size_t>(H) * tiles * (2 * static_cast<size_t>(n) + kTileRows - 1) * sizeof(float);
+  const size_t fpad = (f + 15) / 16 * 16;
+  return fpad + static_cast<size_t>(H) * tiles * sizeof(double);
+}
+
+extern "C" int moddit_mts(const void* map_f16, const void* prev_f16, const uint8_t* keep_mask,
+                          int64_t mask_head_stride, int64_t mask_row_stride, int mask_off, void* merged_out_f16,
+                          int H, int n, int blocks_per_frame, float* mts, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(map_f16 && mts, "mts: null pointer");
+  MODDIT_CHECK_ARG(H > 0 && H <= 65535, "mts: H=%d outside [1, 65535]", H);
+  if (int rc = check_n("mts", n)) return rc;
+  MODDIT_CHECK_ARG(blocks_per_frame > 0, "mts: blocks_per_frame=%d must be positive", blocks_per_frame);
+  MODDIT_CHECK_ARG((prev_f16 == nullptr) == (keep_mask == nullptr) && (prev_f16 == nullptr) == (merged_out_f16 == nullptr),
+                   "mts: prev, keep_mask and merged_out must be given together");
+  if (!workspace || workspace_bytes < moddit_mts_workspace_bytes(H, n))
+    return fail(MODDIT_E_WORKSPACE, "mts: workspace of %zu bytes needed, got %zu", moddit_mts_workspace_bytes(H, n),
+                workspace_bytes);
+  if (!aligned16(workspace)) return fail(MODDIT_E_ALIGN, "mts: workspace must be 16-byte aligned");
+  const size_t smem = static_cast<size_t>(kTileRows) * n * sizeof(__half);
+  if (smem > 200 * 1024) return fail(MODDIT_E_UNSUPPORTED, "mts: n=%d rows do not fit shared memory", n);
+  if (int rc = require_sm100()) return rc;
+  const int tiles = ceil_div(n, kTileRows);
+  const size_t f = static_cast<size_t>(H) * tiles * (2 * static_cast<size_t>(n) + kTileRows - 1) * sizeof(float);
+  float* part_f = static_cast<float*>(workspace);
+  double* part_blk = reinterpret_cast<double*>(static_cast<unsigned char*>(workspace) + (f + 15) / 16 * 16);
+  cudaStream_t st = as_stream(stream);
+  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(mts_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)));
+  mts_partial_kernel<<<dim3(tiles, H), kMtsThreads, smem, st>>>(
+      static_cast<const __half*>(map_f16), static_cast<const __half*>(prev_f16), keep_mask, mask_head_stride,
+      mask_row_stride, mask_off, static_cast<__half*>(merged_out_f16), n, blocks_per_frame, part_f, part_blk);
+  MODDIT_CHECK_LAUNCH("mts_partial_kernel");
+  mts_finish_kernel<<<dim3(ceil_div(3 * n, 256), H), 256, 0, st>>>(part_f, part_blk, n, tiles, mts);
+  MODDIT_CHECK_LAUNCH("mts_finish_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_mtm(int n, int blocks_per_frame, float regularization, float* mtm, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(mtm, "mtm: null pointer");
+  if (int rc = check_n("mtm", n)) return rc;
+  MODDIT_CHECK_ARG(blocks_per_frame > 0, "mtm: blocks_per_frame=%d must be positive", blocks_per_frame);
+  if (int rc = require_sm100()) return rc;
+  const int64_t total = static_cast<int64_t>(3 * n) * (3 * n);
+  mtm_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(n, blocks_per_frame,
+                                                                                         regularization, mtm);
+  MODDIT_CHECK_LAUNCH("mtm_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" size_t moddit_solve_factor_bytes(int n) {
+  if (n <= 0) return 0;
+  const size_t m = static_cast<size_t>(n) + 1;
+  return sizeof(double) * (m * m + 2 * (2 * static_cast<size_t>(n) - 1));
+}
+
+extern "C" size_t moddit_solve_prepare_workspace_bytes(int n) {
+  if (n <= 0) return 0;
+  return sizeof(double) * (2 * 2 * static_cast<size_t>(n) + 2 * (static_cast<size_t>(n) + 1) + 2);
+}
+
+extern "C" int moddit_solve_prepare(int n, int blocks_per_frame, double regularization, void* factor,
+                                    void* workspace, size_t workspace_bytes, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(factor, "solve_prepare: null factor pointer");
+  if (int rc = check_n("solve_prepare", n)) return rc;
+  MODDIT_CHECK_ARG(blocks_per_frame > 0, "solve_prepare: blocks_per_frame=%d must be positive", blocks_per_frame);
+  MODDIT_CHECK_ARG(regularization > 0.0,
+                   "solve_prepare: regularization=%g must be positive (the basis is rank deficient without it)",
+                   regularization);
+  if (!workspace || workspace_bytes < moddit_solve_prepare_workspace_bytes(n))
+    return fail(MODDIT_E_WORKSPACE, "solve_prepare: workspace of %zu bytes needed, got %zu",
+                moddit_solve_prepare_workspace_bytes(n), workspace_bytes);
+  if (!aligned16(factor) || !aligned16(workspace))
+    return fail(MODDIT_E_ALIGN, "solve_prepare: factor and workspace must be 16-byte aligned");
+  if (int rc = require_sm100()) return rc;
+  const int m = n + 1;
+  double* Sinv = static_cast<double*>(factor);
+  double* w = Sinv + static_cast<size_t>(m) * m;
+  double* wb = w + (2 * n - 1);
+  double* pw = static_cast<double*>(workspace);
+  double* pwb = pw + 2 * n;
+  double* row = pwb + 2 * n;
+  double* col = row + m;
+  double* scalars = col + m;
+  cudaStream_t st = as_stream(stream);
+  solve_vectors_kernel<<<1, 1, 0, st>>>(n, blocks_per_frame, regularization, w, wb, pw, pwb, scalars);
+  MODDIT_CHECK_LAUNCH("solve_vectors_kernel");
+  const int64_t total = static_cast<int64_t>(m) * m;
+  schur_build_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(n, blocks_per_frame, regularization,
+                                                                                 pw, pwb, scalars, Sinv);
+  MODDIT_CHECK_LAUNCH("schur_build_kernel");
+  for (int k = 0; k < m; ++k) {
+    gj_save_kernel<<<ceil_div(m, 256), 256, 0, st>>>(Sinv, m, k, row, col);
+    gj_update_kernel<<<dim3(ceil_div(m, 256), m), 256, 0, st>>>(Sinv, m, k, row, col);
+  }
+  MODDIT_CHECK_LAUNCH("gauss-jordan kernels");
+  return MODDIT_OK;
+}
+
+extern "C" size_t moddit_solve_workspace_bytes(int H, int n) {
+  if (H <= 0 || n <= 0) return 0;
+  return sizeof(double) * 2 * static_cast<size_t>(H) * (static_cast<size_t>(n) + 1);
+}
+
+extern "C" int moddit_solve(const float* mts, const void* factor, int H, int n, int blocks_per_frame,
+                            double regularization, float* X, void* workspace, size_t workspace_bytes, void* stream) {
+  clear_error();
+  (void)blocks_per_frame;
+  (void)regularization;
+  MODDIT_CHECK_ARG(mts && factor && X, "solve: null pointer");
+  MODDIT_CHECK_ARG(H > 0 && H <= 65535, "solve: H=%d outside [1, 65535]", H);
+  if (int rc = check_n("solve", n)) return rc;
+  if (!workspace || workspace_bytes < moddit_solve_workspace_bytes(H, n))
+    return fail(MODDIT_E_WORKSPACE, "solve: workspace of %zu bytes needed, got %zu", moddit_solve_workspace_bytes(H, n),
+                workspace_bytes);
+  if (!aligned16(factor) || !aligned16(workspace))
+    return fail(MODDIT_E_ALIGN, "solve: factor and workspace must be 16-byte aligned");
+  if (int rc = require_sm100()) return rc;
+  const int m = n + 1;
+  const double* Sinv = static_cast<const double*>(factor);
+  const double* w = Sinv + static_cast<size_t>(m) * m;
+  const double* wb = w + (2 * n - 1);
+  double* g = static_cast<double*>(workspace);
+  double* y = g + static_cast<size_t>(H) * m;
+  cudaStream_t st = as_stream(stream);
+  const size_t sm_rhs = sizeof(double) * ((2 * n - 1) + kSolveThreads);
+  const size_t sm_back = sizeof(double) * (n + kSolveThreads);
+  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(solve_rhs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(sm_rhs)));
+  solve_rhs_kernel<<<H, kSolveThreads, sm_rhs, st>>>(mts, w, wb, n, g);
+  MODDIT_CHECK_LAUNCH("solve_rhs_kernel");
+  solve_gemv_kernel<<<dim3(ceil_div(m, 128), H), 128, sizeof(double) * m, st>>>(Sinv, g, m, y);
+  MODDIT_CHECK_LAUNCH("solve_gemv_kernel");
+  solve_back_kernel<<<H, kSolveThreads, sm_back, st>>>(mts, w, wb, y, n, X);
+  MODDIT_CHECK_LAUNCH("solve_back_kernel");
+  return MODDIT_OK;
+}

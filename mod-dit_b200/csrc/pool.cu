@@ -1,0 +1,240 @@
+// Block mean-pooling of Q/K and the pooled darkness map (HBM-bound and latency-bound stages).
+//
+// pool_blocks: one CTA per (block, head) streams the block's rows with 128-bit loads; every thread
+// keeps eight fp32 column sums, row groups are combined through shared memory in a fixed order.
+// Algorithmic traffic: N*D*2 bytes read + ceil(N/bs)*D*4 bytes written per head.
+//
+// pooled_map: one CTA per (32 query blocks, head): fp32 logits against all key blocks are kept in
+// shared memory, then each warp normalises its rows and writes 1 - softmax as float16.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace moddit {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]);
+
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+    const float2 p = __half22float2(h);
+    f[2 * i] = p.x;
+    f[2 * i + 1] = p.y;
+  }
+}
+
+constexpr int kPoolThreads = 256;
+
+// D is 64 or 128: D/8 threads cover one row with one 16-byte load each.
+template <typename T, int D>
+__global__ void __launch_bounds__(kPoolThreads) pool_blocks_kernel(const T* __restrict__ x, int N, int bs,
+                                                                   float* __restrict__ out) {
+  constexpr int kTpr = D / 8;                   // threads per row
+  constexpr int kRpp = kPoolThreads / kTpr;     // rows per pass
+  __shared__ float red[kRpp][D];
+
+  const int blk = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int nb = gridDim.x;
+  const int row0 = blk * bs;
+  const int rows = min(bs, N - row0);
+  const int cg = threadIdx.x % kTpr;
+  const int rg = threadIdx.x / kTpr;
+  const uint4* base = reinterpret_cast<const uint4*>(x + (static_cast<int64_t>(bh) * N + row0) * D) + cg;
+
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  // rows/kRpp is at most 8 (bs=128, D=128): issue the loads of up to eight rows before using any.
+  for (int r0 = rg; r0 < rows; r0 += 8 * kRpp) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int r = r0 + u * kRpp;
+      v[u] = (r < rows) ? __ldg(base + static_cast<int64_t>(r) * kTpr) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      float f[8];
+      unpack8<T>(v[u], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[rg][cg * 8 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int g = 0; g < kRpp; ++g) s += red[g][threadIdx.x];
+    out[(static_cast<int64_t>(bh) * nb + blk) * D + threadIdx.x] = s / static_cast<float>(rows);
+  }
+}
+
+constexpr int kMapThreads = 256;
+constexpr int kMapCols = 64;   // key blocks per staged tile
+
+// ROWS query blocks per CTA; every thread owns (ROWS/16) rows x 4 columns of the staged 64-column tile.
+template <int ROWS>
+__global__ void __launch_bounds__(kMapThreads) pooled_map_kernel(const float* __restrict__ qbar,
+                                                                 const float* __restrict__ kbar, int nb, int D,
+                                                                 int q_off, int k_off, int n, float scale,
+                                                                 __half* __restrict__ map) {
+  constexpr int kRpt = ROWS / 16;               // rows per thread
+  extern __shared__ float smem[];
+  float* qs = smem;                             // [ROWS][D+1]
+  float* ks = qs + ROWS * (D + 1);              // [kMapCols][D+1]
+  float* lg = ks + kMapCols * (D + 1);          // [ROWS][n]
+
+  const int bh = blockIdx.y;
+  const int i0 = blockIdx.x * ROWS;
+  const int tid = threadIdx.x;
+  const float* qh = qbar + (static_cast<int64_t>(bh) * nb + q_off) * D;
+  const float* kh = kbar + (static_cast<int64_t>(bh) * nb + k_off) * D;
+
+  for (int e = tid; e < ROWS * D; e += kMapThreads) {
+    const int r = e / D, d = e - r * D;
+    qs[r * (D + 1) + d] = (i0 + r < n) ? qh[static_cast<int64_t>(i0 + r) * D + d] * scale : 0.f;
+  }
+  const int tc = tid % 16;                      // column lane: columns tc, tc+16, tc+32, tc+48
+  const int tr = tid / 16;                      // row lane: rows tr, tr+16, ...
+  for (int j0 = 0; j0 < n; j0 += kMapCols) {
+    __syncthreads();
+    for (int e = tid; e < kMapCols * D; e += kMapThreads) {
+      const int c = e / D, d = e - c * D;
+      ks[c * (D + 1) + d] = (j0 + c < n) ? kh[static_cast<int64_t>(j0 + c) * D + d] : 0.f;
+    }
+    __syncthreads();
+    float acc[kRpt][4];
+#pragma unroll
+    for (int a = 0; a < kRpt; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+    for (int d = 0; d < D; ++d) {
+      float qv[kRpt], kv[4];
+#pragma unroll
+      for (int a = 0; a < kRpt; ++a) qv[a] = qs[(tr + 16 * a) * (D + 1) + d];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) kv[b] = ks[(tc + 16 * b) * (D + 1) + d];
+#pragma unroll
+      for (int a = 0; a < kRpt; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(qv[a], kv[b], acc[a][b]);
+    }
+#pragma unroll
+    for (int a = 0; a < kRpt; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int j = j0 + tc + 16 * b;
+        if (j < n) lg[(tr + 16 * a) * n + j] = acc[a][b];
+      }
+  }
+  __syncthreads();
+  // row softmax: warp w handles rows w, w+8, ...
+  const int warp = tid / 32, lane = tid % 32;
+  for (int r = warp; r < ROWS; r += kMapThreads / 32) {
+    const int i = i0 + r;
+    if (i >= n) break;
+    const float* row = lg + r * n;
+    float m = -INFINITY;
+    for (int j = lane; j < n; j += 32) m = fmaxf(m, row[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.f;
+    for (int j = lane; j < n; j += 32) s += expf(row[j] - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float inv = 1.f / s;
+    __half* dst = map + (static_cast<int64_t>(bh) * n + i) * n;
+    for (int j = lane; j < n; j += 32) dst[j] = __float2half_rn(1.f - expf(row[j] - m) * inv);
+  }
+}
+
+template <int ROWS>
+size_t pooled_map_smem(int D, int n) {
+  return sizeof(float) * (static_cast<size_t>(ROWS) * (D + 1) + kMapCols * (D + 1) + static_cast<size_t>(ROWS) * n);
+}
+
+}  // namespace
+}  // namespace moddit
+
+using namespace moddit;
+
+extern "C" int moddit_pool_blocks(const void* x, int dtype, int BH, int N, int D, int block_size, float* out,
+                                  void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(x && out, "pool_blocks: null pointer");
+  MODDIT_CHECK_ARG(BH > 0 && N > 0, "pool_blocks: BH=%d N=%d must be positive", BH, N);
+  if (D != 64 && D != 128) return fail(MODDIT_E_UNSUPPORTED, "pool_blocks: head_dim must be 64 or 128, got %d", D);
+  if (block_size != 64 && block_size != 128)
+    return fail(MODDIT_E_UNSUPPORTED, "pool_blocks: block_size must be 64 or 128, got %d", block_size);
+  if (dtype != MODDIT_BF16 && dtype != MODDIT_FP16) return fail(MODDIT_E_ARG, "pool_blocks: unknown dtype %d", dtype);
+  if (!aligned16(x)) return fail(MODDIT_E_ALIGN, "pool_blocks: input must be 16-byte aligned");
+  if (BH > 65535) return fail(MODDIT_E_UNSUPPORTED, "pool_blocks: BH=%d exceeds 65535", BH);
+  if (int rc = require_sm100()) return rc;
+  const dim3 grid(ceil_div(N, block_size), BH);
+  cudaStream_t st = as_stream(stream);
+  if (dtype == MODDIT_BF16) {
+    if (D == 64)
+      pool_blocks_kernel<__nv_bfloat16, 64><<<grid, kPoolThreads, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(x), N, block_size, out);
+    else
+      pool_blocks_kernel<__nv_bfloat16, 128><<<grid, kPoolThreads, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(x), N, block_size, out);
+  } else {
+    if (D == 64)
+      pool_blocks_kernel<__half, 64><<<grid, kPoolThreads, 0, st>>>(static_cast<const __half*>(x), N, block_size, out);
+    else
+      pool_blocks_kernel<__half, 128><<<grid, kPoolThreads, 0, st>>>(static_cast<const __half*>(x), N, block_size,
+                                                                       out);
+  }
+  MODDIT_CHECK_LAUNCH("pool_blocks_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_pooled_map(const float* qbar, const float* kbar, int BH, int nb, int D, int q_block_offset,
+                                 int k_block_offset, int n, float scale, void* map_f16, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(qbar && kbar && map_f16, "pooled_map: null pointer");
+  MODDIT_CHECK_ARG(BH > 0 && nb > 0 && n > 0 && D > 0, "pooled_map: sizes must be positive");
+  MODDIT_CHECK_ARG(q_block_offset >= 0 && k_block_offset >= 0 && q_block_offset + n <= nb && k_block_offset + n <= nb,
+                   "pooled_map: video region [%d+%d) / [%d+%d) exceeds %d blocks", q_block_offset, n, k_block_offset,
+                   n, nb);
+  if (BH > 65535) return fail(MODDIT_E_UNSUPPORTED, "pooled_map: BH=%d exceeds 65535", BH);
+  if (int rc = require_sm100()) return rc;
+  cudaStream_t st = as_stream(stream);
+  __half* map = static_cast<__half*>(map_f16);
+  const size_t limit = 227 * 1024;
+  if (pooled_map_smem<32>(D, n) <= limit) {
+    const size_t sm = pooled_map_smem<32>(D, n);
+    MODDIT_CHECK_CUDA(cudaFuncSetAttribute(pooled_map_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(sm)));
+    pooled_map_kernel<32><<<dim3(ceil_div(n, 32), BH), kMapThreads, sm, st>>>(qbar, kbar, nb, D, q_block_offset,
+                                                                               k_block_offset, n, scale, map);
+  } else if (pooled_map_smem<16>(D, n) <= limit) {
+    const size_t sm = pooled_map_smem<16>(D, n);
+    MODDIT_CHECK_CUDA(cudaFuncSetAttribute(pooled_map_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(sm)));
+    pooled_map_kernel<16><<<dim3(ceil_div(n, 16), BH), kMapThreads, sm, st>>>(qbar, kbar, nb, D, q_block_offset,
+                                                                               k_block_offset, n, scale, map);
+  } else {
+    return fail(MODDIT_E_UNSUPPORTED, "pooled_map: n=%d video blocks do not fit the shared-memory row buffer", n);
+  }
+  MODDIT_CHECK_LAUNCH("pooled_map_kernel");
+  return MODDIT_OK;
+}

@@ -1,0 +1,311 @@
+// Line selection, mask generation, cumulative-mass selection and the work lists of the sparse forward.
+// All integer / byte work on small arrays: each kernel is one pass with coalesced reads and writes.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace moddit {
+namespace {
+
+// Monotone map float -> uint32 (ascending); -0 and +0 coincide, NaN sorts last.
+__device__ __forceinline__ uint32_t order_key(float f) {
+  if (f != f) return 0xffffffffu;
+  if (f == 0.f) f = 0.f;
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+constexpr int kSelectThreads = 1024;
+
+// One CTA per head.  keys[] in shared memory; the rank of element i is the number of elements that
+// sort before it under (key, index); ranks < k are written to selected[h][rank].
+__global__ void __launch_bounds__(kSelectThreads) select_lines_kernel(
+    const float* __restrict__ cur_c, const float* __restrict__ cur_d, const float* __restrict__ last_c,
+    const float* __restrict__ last_d, int n, int k, float predict_T, int64_t* __restrict__ selected) {
+  extern __shared__ uint32_t keys[];
+  const int h = blockIdx.x;
+  const int nd = 2 * n - 1;
+  const int L = n + nd;
+  for (int i = threadIdx.x; i < L; i += kSelectThreads) {
+    float cur, last;
+    if (i < n) {
+      cur = cur_c[static_cast<int64_t>(h) * n + i];
+      last = last_c[static_cast<int64_t>(h) * n + i];
+    } else {
+      cur = cur_d[static_cast<int64_t>(h) * nd + (i - n)];
+      last = last_d[static_cast<int64_t>(h) * nd + (i - n)];
+    }
+    // cur + (cur - last) / predict_T with IEEE operations in this order (no contraction)
+    const float pred = __fadd_rn(cur, __fdiv_rn(__fsub_rn(cur, last), predict_T));
+    keys[i] = order_key(pred);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < L; i += kSelectThreads) {
+    const uint32_t ki = keys[i];
+    int rank = 0;
+    for (int j = 0; j < L; ++j) {
+      const uint32_t kj = keys[j];
+      rank += (kj < ki) || (kj == ki && j < i);
+    }
+    if (rank < k) selected[static_cast<int64_t>(h) * k + rank] = i;
+  }
+}
+
+__global__ void head_modes_kernel(const float* __restrict__ b_d, int H, float threshold, int32_t* __restrict__ modes) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h < H) modes[h] = (b_d[h] <= threshold) ? MODDIT_MODE_BLOCK_DIAGONAL : MODDIT_MODE_SPARSE;
+}
+
+constexpr int kMaskRows = 8;
+constexpr int kMaskThreads = 256;
+
+// One CTA per (8 mask rows, head): flags of selected columns / diagonals are rebuilt in shared memory.
+__global__ void __launch_bounds__(kMaskThreads) mask_from_lines_kernel(
+    const int64_t* __restrict__ selected, int k, const int32_t* __restrict__ modes, int n, int bpf, int voff, int nbt,
+    uint8_t* __restrict__ mask) {
+  extern __shared__ uint8_t flags[];   // [n] columns | [2n-1] diagonals
+  uint8_t* col_sel = flags;
+  uint8_t* off_sel = flags + n;
+  const int h = blockIdx.y;
+  const int mode = modes[h];
+  for (int i = threadIdx.x; i < 3 * n - 1; i += kMaskThreads) flags[i] = 0;
+  __syncthreads();
+  for (int t = threadIdx.x; t < k; t += kMaskThreads) {
+    const int64_t idx = selected[static_cast<int64_t>(h) * k + t];
+    if (idx >= 0 && idx < 3 * n - 1) flags[idx] = 1;   // [0,n): column; n + (offset + n - 1): diagonal
+  }
+  __syncthreads();
+  for (int rr = 0; rr < kMaskRows; ++rr) {
+    const int R = blockIdx.x * kMaskRows + rr;
+    if (R >= nbt) break;
+    const int i = R - voff;
+    uint8_t* dst = mask + (static_cast<int64_t>(h) * nbt + R) * nbt;
+    const bool text_row = (i < 0 || i >= n);
+    for (int C = threadIdx.x; C < nbt; C += kMaskThreads) {
+      const int j = C - voff;
+      bool keep = text_row || j < 0 || j >= n || mode == MODDIT_MODE_FULL;
+      if (!keep) {
+        keep = col_sel[j] || off_sel[j - i + n - 1] ||
+               (mode == MODDIT_MODE_BLOCK_DIAGONAL && (i / bpf) == (j / bpf));
+      }
+      dst[C] = keep ? 1 : 0;
+    }
+  }
+}
+
+// ---- cumulative-mass selection ------------------------------------------------------------------
+constexpr int kMassBits = 24;
+constexpr int kMassThreads = 512;
+
+// One CTA per (query block, head).  Keys ((2^24 - w) << 32 | j) are bitonic-sorted ascending, i.e.
+// by brightness descending then index ascending; integer prefix sums decide the kept prefix.
+__global__ void __launch_bounds__(kMassThreads) select_mass_kernel(const __half* __restrict__ map, int n, int P,
+                                                                   uint32_t tau_fixed, uint8_t* __restrict__ keep) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned long long* key = reinterpret_cast<unsigned long long*>(smem_raw);   // [P]
+  unsigned long long* pre = key + P;                                           // [P] inclusive prefix of w
+  __shared__ unsigned long long carry[kMassThreads];
+  const int i = blockIdx.x, h = blockIdx.y;
+  const __half* row = map + (static_cast<int64_t>(h) * n + i) * n;
+  for (int j = threadIdx.x; j < P; j += kMassThreads) {
+    if (j < n) {
+      float b = 1.0f - __half2float(row[j]);
+      b = fminf(fmaxf(b, 0.f), 1.f);
+      const uint32_t w = static_cast<uint32_t>(floorf(b * 16777216.0f));       // exact: b is a multiple of 2^-24
+      key[j] = (static_cast<unsigned long long>((1u << kMassBits) - w) << 32) | static_cast<uint32_t>(j);
+    } else {
+      key[j] = ~0ull;
+    }
+  }
+  __syncthreads();
+  for (int size = 2; size <= P; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < P / 2; t += kMassThreads) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi = lo + stride;
+        const bool up = ((lo & size) == 0);
+        const unsigned long long a = key[lo], b = key[hi];
+        if ((a > b) == up) {
+          key[lo] = b;
+          key[hi] = a;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  // inclusive prefix of w over the sorted order (padding has w = 2^24 - 0xffffffff wraps; mask it out)
+  const int per = (P + kMassThreads - 1) / kMassThreads;
+  const int beg = min(P, static_cast<int>(threadIdx.x) * per), end = min(P, beg + per);
+  unsigned long long run = 0;
+  for (int e = beg; e < end; ++e) {
+    const unsigned long long kk = key[e];
+    const unsigned long long w = (static_cast<uint32_t>(kk) < static_cast<uint32_t>(n) && kk != ~0ull)
+                                     ? (1ull << kMassBits) - (kk >> 32)
+                                     : 0ull;
+    run += w;
+    pre[e] = run;
+  }
+  carry[threadIdx.x] = run;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long acc = 0;
+    for (int t = 0; t < kMassThreads; ++t) {
+      const unsigned long long v = carry[t];
+      carry[t] = acc;
+      acc += v;
+    }
+  }
+  __syncthreads();
+  for (int e = beg; e < end; ++e) pre[e] += carry[threadIdx.x];
+  __syncthreads();
+  const unsigned long long total = pre[P - 1];
+  const unsigned long long target = (static_cast<unsigned long long>(tau_fixed) * total + ((1ull << kMassBits) - 1)) >>
+                                    kMassBits;
+  uint8_t* dst = keep + (static_cast<int64_t>(h) * n + i) * n;
+  for (int e = threadIdx.x; e < P; e += kMassThreads) {
+    const unsigned long long kk = key[e];
+    if (kk == ~0ull) continue;
+    const int j = static_cast<int>(static_cast<uint32_t>(kk));
+    const unsigned long long excl = (e == 0) ? 0ull : pre[e - 1];
+    dst[j] = (excl < target || j == i) ? 1 : 0;
+  }
+}
+
+// ---- work lists ---------------------------------------------------------------------------------
+constexpr int kListThreads = 256;
+
+// One CTA per (pair of 128-row query tiles, mask head); ordered compaction with ballots.
+__global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t* __restrict__ mask, int nbq, int nbk,
+                                                                  int sub, int ntq, int ntk, int kv_block_limit,
+                                                                  int32_t* __restrict__ counts,
+                                                                  int32_t* __restrict__ entries) {
+  __shared__ int warp_tot[kListThreads / 32];
+  __shared__ int base_s;
+  const int p = blockIdx.x, h = blockIdx.y;
+  const int npairs = gridDim.x;
+  const uint8_t* mh = mask + static_cast<int64_t>(h) * nbq * nbk;
+  int32_t* out = entries + (static_cast<int64_t>(h) * npairs + p) * ntk;
+  const int lim = min(nbk, kv_block_limit);
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  if (threadIdx.x == 0) base_s = 0;
+  __syncthreads();
+  for (int t0 = 0; t0 < ntk; t0 += kListThreads) {
+    const int t = t0 + threadIdx.x;
+    int fl = 0;
+    if (t < ntk) {
+      for (int x = 0; x < 2; ++x) {
+        const int qt = 2 * p + x;
+        if (qt >= ntq) continue;
+        for (int rh = 0; rh < 2; ++rh)
+          for (int ch = 0; ch < 2; ++ch) {
+            const int bi = (sub == 1) ? qt : qt * 2 + rh;
+            const int bj = (sub == 1) ? t : t * 2 + ch;
+            if (bi < nbq && bj < lim && mh[static_cast<int64_t>(bi) * nbk + bj]) fl |= 1 << (4 * x + 2 * rh + ch);
+          }
+      }
+    }
+    const unsigned bal = __ballot_sync(0xffffffffu, fl != 0);
+    if (lane == 0) warp_tot[warp] = __popc(bal);
+    __syncthreads();
+    int off = base_s;
+    for (int wv = 0; wv < warp; ++wv) off += warp_tot[wv];
+    if (fl) out[off + __popc(bal & ((1u << lane) - 1))] = (t << 8) | fl;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int s = 0;
+      for (int wv = 0; wv < kListThreads / 32; ++wv) s += warp_tot[wv];
+      base_s += s;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) counts[static_cast<int64_t>(h) * npairs + p] = base_s;
+}
+
+}  // namespace
+}  // namespace moddit
+
+using namespace moddit;
+
+extern "C" int moddit_select_lines(const float* cur_c, const float* cur_d, const float* last_c, const float* last_d,
+                                   int H, int n, int top_k, float predict_T, int64_t* selected, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(cur_c && cur_d && last_c && last_d && selected, "select_lines: null pointer");
+  MODDIT_CHECK_ARG(H > 0 && n > 0 && top_k > 0, "select_lines: H=%d n=%d top_k=%d must be positive", H, n, top_k);
+  MODDIT_CHECK_ARG(predict_T != 0.f, "select_lines: predict_T must be non-zero");
+  if (n > 4096) return fail(MODDIT_E_UNSUPPORTED, "select_lines: n=%d exceeds 4096", n);
+  if (int rc = require_sm100()) return rc;
+  const int L = 3 * n - 1;
+  const int k = top_k < L ? top_k : L;
+  select_lines_kernel<<<H, kSelectThreads, sizeof(uint32_t) * L, as_stream(stream)>>>(cur_c, cur_d, last_c, last_d, n,
+                                                                                      k, predict_T, selected);
+  MODDIT_CHECK_LAUNCH("select_lines_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_head_modes(const float* b_d, int H, float threshold, int32_t* modes, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(b_d && modes && H > 0, "head_modes: bad arguments");
+  if (int rc = require_sm100()) return rc;
+  head_modes_kernel<<<ceil_div(H, 128), 128, 0, as_stream(stream)>>>(b_d, H, threshold, modes);
+  MODDIT_CHECK_LAUNCH("head_modes_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_mask_from_lines(const int64_t* selected, int k, const int32_t* modes, int H, int n,
+                                      int blocks_per_frame, int layout, int text_blocks, int nbt, uint8_t* mask,
+                                      void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(selected && modes && mask, "mask_from_lines: null pointer");
+  MODDIT_CHECK_ARG(H > 0 && H <= 65535 && n > 0 && k >= 0 && blocks_per_frame > 0 && text_blocks >= 0,
+                   "mask_from_lines: bad sizes");
+  if (n > 4096) return fail(MODDIT_E_UNSUPPORTED, "mask_from_lines: n=%d exceeds 4096", n);
+  int voff = 0;
+  if (layout == MODDIT_LAYOUT_WAN) {
+    MODDIT_CHECK_ARG(nbt == n, "mask_from_lines: wan layout needs nbt == n (got %d, %d)", nbt, n);
+  } else if (layout == MODDIT_LAYOUT_HUNYUAN) {
+    MODDIT_CHECK_ARG(nbt >= n, "mask_from_lines: nbt=%d smaller than n=%d", nbt, n);
+  } else if (layout == MODDIT_LAYOUT_COGVIDEOX) {
+    MODDIT_CHECK_ARG(nbt == n + text_blocks, "mask_from_lines: cogvideox layout needs nbt == text_blocks + n");
+    voff = text_blocks;
+  } else {
+    return fail(MODDIT_E_ARG, "mask_from_lines: unknown layout %d", layout);
+  }
+  if (int rc = require_sm100()) return rc;
+  mask_from_lines_kernel<<<dim3(ceil_div(nbt, kMaskRows), H), kMaskThreads, 3 * n, as_stream(stream)>>>(
+      selected, k, modes, n, blocks_per_frame, voff, nbt, mask);
+  MODDIT_CHECK_LAUNCH("mask_from_lines_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_select_mass(const void* map_f16, int H, int n, float tau, uint8_t* keep, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(map_f16 && keep, "select_mass: null pointer");
+  MODDIT_CHECK_ARG(H > 0 && H <= 65535 && n > 0, "select_mass: bad sizes");
+  MODDIT_CHECK_ARG(tau >= 0.f && tau <= 1.f, "select_mass: tau=%g outside [0, 1]", tau);
+  if (n > 2048) return fail(MODDIT_E_UNSUPPORTED, "select_mass: n=%d exceeds 2048", n);
+  if (int rc = require_sm100()) return rc;
+  int P = 2;
+  while (P < n) P <<= 1;
+  const uint32_t tau_fixed = static_cast<uint32_t>(floorf(tau * 16777216.0f));
+  select_mass_kernel<<<dim3(n, H), kMassThreads, 2 * sizeof(unsigned long long) * P, as_stream(stream)>>>(
+      static_cast<const __half*>(map_f16), n, P, tau_fixed, keep);
+  MODDIT_CHECK_LAUNCH("select_mass_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, int block_size, int N,
+                                 int kv_block_limit, int32_t* counts, int32_t* entries, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(mask && counts && entries, "tile_lists: null pointer");
+  MODDIT_CHECK_ARG(Hm > 0 && Hm <= 65535 && nbq > 0 && nbk > 0 && N > 0 && kv_block_limit >= 0, "tile_lists: bad sizes");
+  if (block_size != 64 && block_size != 128)
+    return fail(MODDIT_E_UNSUPPORTED, "tile_lists: block_size must be 64 or 128, got %d", block_size);
+  const int ntq = ceil_div(N, 128);
+  if (ntq >= (1 << 23)) return fail(MODDIT_E_UNSUPPORTED, "tile_lists: N=%d too large", N);
+  if (int rc = require_sm100()) return rc;
+  const int npairs = (ntq + 1) / 2;
+  tile_lists_kernel<<<dim3(npairs, Hm), kListThreads, 0, as_stream(stream)>>>(mask, nbq, nbk, 128 / block_size, ntq,
+                                                                              ntq, kv_block_limit, counts, entries);
+  MODDIT_CHECK_LAUNCH("tile_lists_kernel");
+  return MODDIT_OK;
+}

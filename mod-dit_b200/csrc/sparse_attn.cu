@@ -1,0 +1,418 @@
+// Block-sparse flash-attention forward for sm_100a: tcgen05 MMAs with accumulators in tensor memory,
+// K/V tiles fetched by TMA from a compacted work list (a skipped block costs no memory traffic),
+// warp-specialised online softmax.
+//
+// One CTA owns a PAIR of adjacent 128-row query tiles (A, B) of one head and walks the union of
+// their key-tile lists, so a K/V tile needed by both is fetched once.  Roles (12 warps):
+//   warp 0      TMA producer: Q tiles once, then K and V tiles through two 2-stage rings
+//   warp 1      MMA issuer: S_X = Q_X K^T (SS form), O_X += P_X V (P read from tensor memory)
+//   warp 2      tensor-memory allocation / release
+//   warps 4-7   softmax of tile A: thread r owns row r (tensor-memory lane r)
+//   warps 8-11  softmax of tile B
+// Tensor memory (512 columns): S_A [0,128) S_B [128,256) O_A [256,256+D) O_B [256+D,256+2D); P_X
+// (16-bit) overwrites the first 64 columns of S_X.  MMAs issued by one thread execute in order, which
+// is what makes the aliasing and the "S ready implies the previous P V finished" reasoning valid.
+// The issue order  PV(A,e) QK(A,e+1) PV(B,e) QK(B,e+1)  lets the softmax of one tile overlap the MMAs
+// of the other.
+//
+// Every wait is bounded (ptx::mbar_wait); on expiry the CTA records a status word, lets its copies
+// land, releases tensor memory and returns.
+//
+// Tensor-pipe work per kept 128x128 tile: 4*128*128*D flop (QK^T and PV); memory traffic per fetched
+// key tile: 2*128*D*2 bytes (K and V), shared by both query tiles.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace moddit {
+namespace {
+
+constexpr int kThreads = 384;
+constexpr int kTile = 128;
+constexpr float kRescaleThreshold = 8.0f;   // log2 domain: rescale O only when the row max grew by more than this
+
+enum BarrierIndex {
+  kQFull = 0,
+  kKFull0, kKFull1, kKEmpty0, kKEmpty1,
+  kVFull0, kVFull1, kVEmpty0, kVEmpty1,
+  kSFullA, kSFullB, kPFullA, kPFullB,
+  kOFinal,
+  kNumBarriers
+};
+
+struct __align__(8) Control {
+  unsigned long long bars[kNumBarriers];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int D>
+constexpr size_t smem_bytes() {
+  // 2 Q tiles + 2 K stages + 2 V stages, 1024-byte alignment slack, control block
+  return static_cast<size_t>(6) * kTile * D * 2 + 1024 + sizeof(Control);
+}
+
+__device__ __forceinline__ void report(int32_t* status, int code, int role, int where) {
+  if (atomicCAS(status, 0, code) == 0) {
+    status[1] = static_cast<int32_t>(blockIdx.y * gridDim.x + blockIdx.x);
+    status[2] = role;
+    status[3] = where;
+  }
+}
+
+template <bool kBF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kBF16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  } else {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+
+template <int D, bool kBF16>
+__global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
+    const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+    const __grid_constant__ CUtensorMap tm_v, const int32_t* __restrict__ counts,
+    const int32_t* __restrict__ entries, int Hm, int ntk, int N, float scale_log2, int q_split, int kvl_lo,
+    int kvl_hi, void* __restrict__ out_raw, float* __restrict__ lse, int32_t* __restrict__ status) {
+  constexpr int kTileBytes = kTile * D * 2;       // one Q, K or V tile
+  constexpr int kChunks = D / 64;                 // 64-element (128-byte) column chunks per tile
+  constexpr int kChunkBytes = kTile * 128;
+  constexpr uint32_t kIdescQK = ptx::idesc_f16(128, 128, kBF16, false);
+  constexpr uint32_t kIdescPV = ptx::idesc_f16(128, D, kBF16, true);
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Control* ctl = reinterpret_cast<Control*>(smem + 6 * kTileBytes);
+  const uint32_t sQ = ptx::smem_u32(smem);
+  const uint32_t sK = sQ + 2 * kTileBytes;
+  const uint32_t sV = sQ + 4 * kTileBytes;
+  const uint32_t bar0 = ptx::smem_u32(&ctl->bars[0]);
+  auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int pair = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int npairs = gridDim.x;
+  const int ntq = (N + kTile - 1) / kTile;
+  const bool has_b = (2 * pair + 1) < ntq;
+  const int mh = bh % Hm;
+  const int cnt = counts[static_cast<int64_t>(mh) * npairs + pair];
+  const int32_t* ent = entries + (static_cast<int64_t>(mh) * npairs + pair) * ntk;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kNumBarriers; ++i) ptx::mbar_init(bar(i), (i == kPFullA || i == kPFullB) ? 128u : 1u);
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&tm_q);
+    ptx::prefetch_tensormap(&tm_k);
+    ptx::prefetch_tensormap(&tm_v);
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_base), 512);
+    ptx::tmem_relinquish();
+    ptx::tc_fence_before();
+  }
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      ptx::mbar_expect_tx(bar(kQFull), (has_b ? 2u : 1u) * kTileBytes);
+      for (int x = 0; x < (has_b ? 2 : 1); ++x)
+        for (int c = 0; c < kChunks; ++c)
+          ptx::tma_load_3d(sQ + x * kTileBytes + c * kChunkBytes, &tm_q, bar(kQFull), c * 64, (2 * pair + x) * kTile,
+                           bh);
+      bool ok = true;
+      int issued = 0;
+      for (int e = 0; e < cnt && ok; ++e) {
+        const int s = e & 1;
+        const uint32_t par = ((e >> 1) & 1) ^ 1;
+        const int row0 = (ent[e] >> 8) * kTile;
+        ok = ptx::mbar_wait(bar(kKEmpty0 + s), par, abort_flag);
+        if (!ok) { report(status, 1, 0, e); break; }
+        ptx::mbar_expect_tx(bar(kKFull0 + s), kTileBytes);
+        for (int c = 0; c < kChunks; ++c)
+          ptx::tma_load_3d(sK + s * kTileBytes + c * kChunkBytes, &tm_k, bar(kKFull0 + s), c * 64, row0, bh);
+        ok = ptx::mbar_wait(bar(kVEmpty0 + s), par, abort_flag);
+        if (!ok) {
+          // the K copy just issued must land before the CTA may exit
+          report(status, 1, 0, e);
+          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(kKFull0 + s), (e >> 1) & 1); ++i) {}
+          break;
+        }
+        ptx::mbar_expect_tx(bar(kVFull0 + s), kTileBytes);
+        for (int c = 0; c < kChunks; ++c)
+          ptx::tma_load_3d(sV + s * kTileBytes + c * kChunkBytes, &tm_v, bar(kVFull0 + s), c * 64, row0, bh);
+        issued = e + 1;
+      }
+      if (!ok) {
+        // give copies in flight a bounded time to land (their barriers may never be consumed)
+        for (int e = max(0, issued - 2); e < issued; ++e) {
+          const int s = e & 1;
+          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(kKFull0 + s), (e >> 1) & 1); ++i) {}
+          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(kVFull0 + s), (e >> 1) & 1); ++i) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      auto issue_qk = [&](int x, int s) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
+          const uint64_t a = ptx::smem_desc_sw128(sQ + x * kTileBytes + off, 16, 1024);
+          const uint64_t b = ptx::smem_desc_sw128(sK + s * kTileBytes + off, 16, 1024);
+          ptx::mma_ss(tmem + x * 128, a, b, kIdescQK, kk > 0 ? 1u : 0u);
+        }
+        ptx::tc_commit(bar(kSFullA + x));
+      };
+      auto issue_pv = [&](int x, int s, uint32_t acc) {
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          const uint64_t b = ptx::smem_desc_sw128(sV + s * kTileBytes + kk * 2048, kChunkBytes, 1024);
+          ptx::mma_ts(tmem + 256 + x * D, tmem + x * 128 + kk * 8, b, kIdescPV, (acc || kk > 0) ? 1u : 0u);
+        }
+      };
+      bool ok = ptx::mbar_wait(bar(kQFull), 0, abort_flag);
+      if (!ok) report(status, 2, 1, -1);
+      uint32_t par_p[2] = {0, 0};
+      uint32_t acc[2] = {0, 0};
+      if (ok && cnt > 0) {
+        ok = ptx::mbar_wait(bar(kKFull0), 0, abort_flag);
+        if (!ok) report(status, 2, 1, 0);
+        if (ok) {
+          ptx::tc_fence_after();
+          const int fl = ent[0] & 0xff;
+          if (fl & 0x0f) issue_qk(0, 0);
+          if (fl & 0xf0) issue_qk(1, 0);
+          ptx::tc_commit(bar(kKEmpty0));
+        }
+      }
+      for (int e = 0; e < cnt && ok; ++e) {
+        const int s = e & 1;
+        const int fl = ent[e] & 0xff;
+        const bool next = (e + 1) < cnt;
+        const int fln = next ? (ent[e + 1] & 0xff) : 0;
+        if (next) ok = ptx::mbar_wait(bar(kKFull0 + (s ^ 1)), ((e + 1) >> 1) & 1, abort_flag);
+        if (ok) ok = ptx::mbar_wait(bar(kVFull0 + s), (e >> 1) & 1, abort_flag);
+        if (!ok) { report(status, 2, 1, e); break; }
+        if (fl & 0x0f) {
+          ok = ptx::mbar_wait(bar(kPFullA), par_p[0], abort_flag);
+          if (!ok) { report(status, 3, 1, e); break; }
+          par_p[0] ^= 1;
+          ptx::tc_fence_after();
+          issue_pv(0, s, acc[0]);
+          acc[0] = 1;
+        }
+        if (fln & 0x0f) issue_qk(0, s ^ 1);
+        if (fl & 0xf0) {
+          ok = ptx::mbar_wait(bar(kPFullB), par_p[1], abort_flag);
+          if (!ok) { report(status, 3, 1, e); break; }
+          par_p[1] ^= 1;
+          ptx::tc_fence_after();
+          issue_pv(1, s, acc[1]);
+          acc[1] = 1;
+        }
+        ptx::tc_commit(bar(kVEmpty0 + s));
+        if (fln & 0xf0) issue_qk(1, s ^ 1);
+        if (next) ptx::tc_commit(bar(kKEmpty0 + (s ^ 1)));
+      }
+      ptx::tc_commit(bar(kOFinal));
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int x = (warp - 4) / 4;                 // 0: tile A, 1: tile B
+    const int wq = warp % 4;                      // tensor-memory lane quarter of this warp
+    const int r = wq * 32 + lane;                 // row inside the tile
+    const int tile = 2 * pair + x;
+    const int grow = tile * kTile + r;            // global query row
+    const int kvl = (grow < q_split) ? kvl_lo : kvl_hi;
+    const int kvl_min = min(kvl_lo, kvl_hi);
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t tS = tmem + lane_base + x * 128;
+    const uint32_t tO = tmem + lane_base + 256 + x * D;
+    const int rh = r >> 6;
+
+    float m = -INFINITY, l = 0.f;
+    uint32_t par_s = 0;
+    int done = 0;
+    bool ok = true;
+    for (int e = 0; e < cnt; ++e) {
+      const int en = ent[e];
+      const int sub = (en >> (4 * x)) & 0xf;
+      if (!sub) continue;
+      const int col0 = (en >> 8) * kTile;
+      ok = ptx::mbar_wait(bar(kSFullA + x), par_s, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { if (lane == 0) report(status, 4, 2 + x, e); break; }
+      par_s ^= 1;
+      ptx::tc_fence_after();
+
+      float v[kTile];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) ptx::tmem_ld32(tS + c * 32, reinterpret_cast<uint32_t*>(v) + c * 32);
+      ptx::tmem_ld_wait();
+
+      if (sub != 0xf || col0 + kTile > kvl_min) {
+        const int lim = kvl - col0;               // columns >= lim are beyond the valid keys
+        const bool keep_lo = (sub >> (2 * rh)) & 1;
+        const bool keep_hi = (sub >> (2 * rh + 1)) & 1;
+#pragma unroll
+        for (int c = 0; c < kTile; ++c) {
+          const bool valid = (c < 64 ? keep_lo : keep_hi) && (c < lim);
+          v[c] = valid ? v[c] : -INFINITY;
+        }
+      }
+      float mx = v[0];
+#pragma unroll
+      for (int c = 1; c < kTile; ++c) mx = fmaxf(mx, v[c]);
+      const float m_new = fmaxf(m, mx * scale_log2);
+      if (done == 0) {
+        m = m_new;
+      } else if (__any_sync(0xffffffffu, m_new > m + kRescaleThreshold)) {
+        const float alpha = (m == -INFINITY) ? 0.f : ptx::ex2(m - m_new);
+        l *= alpha;
+        m = m_new;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          float o[32];
+          ptx::tmem_ld32(tO + c * 32, reinterpret_cast<uint32_t*>(o));
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= alpha;
+          ptx::tmem_st32(tO + c * 32, reinterpret_cast<const uint32_t*>(o));
+        }
+      }
+      const float mm = (m == -INFINITY) ? 0.f : m;
+      float sum = 0.f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = ptx::ex2(fmaf(v[half * 64 + 2 * i], scale_log2, -mm));
+          const float p1 = ptx::ex2(fmaf(v[half * 64 + 2 * i + 1], scale_log2, -mm));
+          sum += p0 + p1;
+          pk[i] = pack2<kBF16>(p0, p1);
+        }
+        ptx::tmem_st32(tS + half * 32, pk);
+      }
+      l += sum;
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar(kPFullA + x));
+      ++done;
+    }
+
+    if (ok) {
+      ok = ptx::mbar_wait(bar(kOFinal), 0, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok && lane == 0) report(status, 5, 2 + x, -1);
+    }
+    if (ok && tile < ntq) {
+      ptx::tc_fence_after();
+      const float inv = (done > 0 && l > 0.f) ? 1.f / l : 0.f;
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(out_raw) +
+                                            (static_cast<int64_t>(bh) * N + grow) * D * 2);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        if (done > 0) {
+          ptx::tmem_ld32(tO + c * 32, reinterpret_cast<uint32_t*>(o));
+          ptx::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+        }
+        if (grow < N) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 w;
+            w.x = pack2<kBF16>(o[q4 * 8 + 0] * inv, o[q4 * 8 + 1] * inv);
+            w.y = pack2<kBF16>(o[q4 * 8 + 2] * inv, o[q4 * 8 + 3] * inv);
+            w.z = pack2<kBF16>(o[q4 * 8 + 4] * inv, o[q4 * 8 + 5] * inv);
+            w.w = pack2<kBF16>(o[q4 * 8 + 6] * inv, o[q4 * 8 + 7] * inv);
+            dst[c * 4 + q4] = w;
+          }
+        }
+      }
+      if (lse != nullptr && grow < N) {
+        lse[static_cast<int64_t>(bh) * N + grow] =
+            (done > 0 && l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int D, bool kBF16>
+int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N, const int32_t* counts,
+           const int32_t* entries, int Hm, float softmax_scale, int q_split, int kvl_lo, int kvl_hi, void* out,
+           float* lse, int32_t* status, cudaStream_t st) {
+  CUtensorMap tq, tk, tv;
+  if (int rc = make_tmap_rows(&tq, q, dtype, BH, N, D, kTile)) return rc;
+  if (int rc = make_tmap_rows(&tk, k, dtype, BH, N, D, kTile)) return rc;
+  if (int rc = make_tmap_rows(&tv, v, dtype, BH, N, D, kTile)) return rc;
+  const int ntq = ceil_div(N, kTile);
+  const int npairs = (ntq + 1) / 2;
+  auto kernel = sparse_attn_fwd_kernel<D, kBF16>;
+  const size_t smem = smem_bytes<D>();
+  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  const float scale_log2 = softmax_scale * 1.4426950408889634f;
+  kernel<<<dim3(npairs, BH), kThreads, smem, st>>>(tq, tk, tv, counts, entries, Hm, ntq, N, scale_log2, q_split,
+                                                   kvl_lo, kvl_hi, out, lse, status);
+  MODDIT_CHECK_LAUNCH("sparse_attn_fwd_kernel");
+  return MODDIT_OK;
+}
+
+}  // namespace
+}  // namespace moddit
+
+using namespace moddit;
+
+extern "C" int moddit_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
+                                      const int32_t* counts, const int32_t* entries, int Hm, float softmax_scale,
+                                      int q_split, int kv_len_lo, int kv_len_hi, void* out, float* lse,
+                                      int32_t* status, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(q && k && v && out && counts && entries && status, "sparse_attn_fwd: null pointer");
+  MODDIT_CHECK_ARG(BH > 0 && BH <= 65535 && N > 0 && Hm > 0, "sparse_attn_fwd: BH=%d N=%d Hm=%d out of range", BH, N, Hm);
+  MODDIT_CHECK_ARG(BH % Hm == 0, "sparse_attn_fwd: BH=%d is not a multiple of the mask heads Hm=%d", BH, Hm);
+  MODDIT_CHECK_ARG(softmax_scale > 0.f, "sparse_attn_fwd: softmax_scale must be positive");
+  MODDIT_CHECK_ARG(kv_len_lo >= 0 && kv_len_lo <= N && kv_len_hi >= 0 && kv_len_hi <= N,
+                   "sparse_attn_fwd: kv_len (%d, %d) outside [0, N=%d]", kv_len_lo, kv_len_hi, N);
+  if (D != 64 && D != 128) return fail(MODDIT_E_UNSUPPORTED, "sparse_attn_fwd: head_dim must be 64 or 128, got %d", D);
+  if (dtype != MODDIT_BF16 && dtype != MODDIT_FP16) return fail(MODDIT_E_ARG, "sparse_attn_fwd: unknown dtype %d", dtype);
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out))
+    return fail(MODDIT_E_ALIGN, "sparse_attn_fwd: q, k, v and out must be 16-byte aligned");
+  if (int rc = require_sm100()) return rc;
+  cudaStream_t st = as_stream(stream);
+  if (D == 128) {
+    return dtype == MODDIT_BF16
+               ? launch<128, true>(q, k, v, dtype, BH, N, counts, entries, Hm, softmax_scale, q_split, kv_len_lo,
+                                   kv_len_hi, out, lse, status, st)
+               : launch<128, false>(q, k, v, dtype, BH, N, counts, entries, Hm, softmax_scale, q_split, kv_len_lo,
+                                    kv_len_hi, out, lse, status, st);
+  }
+  return dtype == MODDIT_BF16 ? launch<64, true>(q, k, v, dtype, BH, N, counts, entries, Hm, softmax_scale, q_split,
+                                                 kv_len_lo, kv_len_hi, out, lse, status, st)
+                              : launch<64, false>(q, k, v, dtype, BH, N, counts, entries, Hm, softmax_scale, q_split,
+                                                  kv_len_lo, kv_len_hi, out, lse, status, st);
+}

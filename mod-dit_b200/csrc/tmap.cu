@@ -1,0 +1,38 @@
+#include "tmap.cuh"
+
+#include <mutex>
+
+namespace moddit {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn g_encode = nullptr;
+static std::once_flag g_once;
+static cudaError_t g_lookup_error = cudaSuccess;
+
+static void lookup_encode() {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  g_lookup_error = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (g_lookup_error == cudaSuccess && qres == cudaDriverEntryPointSuccess) g_encode = reinterpret_cast<EncodeFn>(fn);
+}
+
+int make_tmap_rows(CUtensorMap* map, const void* base, int dtype, int BH, int N, int D, int box_rows) {
+  std::call_once(g_once, lookup_encode);
+  if (!g_encode) return fail(MODDIT_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver (%s)",
+                             cudaGetErrorString(g_lookup_error));
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(BH)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(N) * D * 2};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = (dtype == MODDIT_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult res = g_encode(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) return fail(MODDIT_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(res));
+  return MODDIT_OK;
+}
+
+}  // namespace moddit

@@ -1,0 +1,341 @@
+"""Tensor-level wrappers over the C ABI: pointer extraction, output allocation, current stream.
+
+Every function here only allocates outputs/workspaces with torch, takes raw device pointers and
+calls one `moddit_*` entry point on torch's current stream.  No arithmetic happens in Python and
+there is no alternative implementation: CPU tensors are rejected.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+_DTYPE = {torch.bfloat16: _lib.MODDIT_BF16, torch.float16: _lib.MODDIT_FP16}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(device: torch.device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _need_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError("moddit_b200 ops need CUDA tensors (there is no CPU implementation)")
+        if t.device != dev:
+            raise ValueError("all tensors must be on the same CUDA device")
+    return dev
+
+
+def _need_contig(**named: torch.Tensor) -> None:
+    for name, t in named.items():
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+
+
+def _qkv_dtype(t: torch.Tensor) -> int:
+    if t.dtype not in _DTYPE:
+        raise TypeError(f"expected float16 or bfloat16 inputs, got {t.dtype}")
+    return _DTYPE[t.dtype]
+
+
+# ---------------------------------------------------------------------------------------------
+# pooled map producer
+# ---------------------------------------------------------------------------------------------
+
+def pool_blocks(x: torch.Tensor, block_size: int) -> torch.Tensor:
+    """(B,H,N,D) bf16/fp16 -> (B,H,ceil(N/bs),D) float32 block means."""
+    dev = _need_cuda(x)
+    _need_contig(x=x)
+    B, H, N, D = x.shape
+    nb = (N + block_size - 1) // block_size
+    out = torch.empty(B, H, nb, D, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        check(lib.moddit_pool_blocks(_ptr(x), _qkv_dtype(x), B * H, N, D, block_size, _ptr(out), _stream(dev)),
+              "moddit_pool_blocks")
+    return out
+
+
+def pooled_map(qbar: torch.Tensor, kbar: torch.Tensor, *, q_block_offset: int, k_block_offset: int,
+               video_blocks: int, scale: float) -> torch.Tensor:
+    """(B,H,nb,D) float32 block means -> (B,H,n,n) float16 darkness map (1 - row softmax)."""
+    dev = _need_cuda(qbar, kbar)
+    _need_contig(qbar=qbar, kbar=kbar)
+    if qbar.dtype != torch.float32 or kbar.dtype != torch.float32 or qbar.shape != kbar.shape:
+        raise ValueError("qbar and kbar must be float32 tensors of the same shape")
+    B, H, nb, D = qbar.shape
+    out = torch.empty(B, H, video_blocks, video_blocks, device=dev, dtype=torch.float16)
+    with torch.cuda.device(dev):
+        check(lib.moddit_pooled_map(_ptr(qbar), _ptr(kbar), B * H, nb, D, q_block_offset, k_block_offset,
+                                    video_blocks, float(scale), _ptr(out), _stream(dev)), "moddit_pooled_map")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# exact replay map
+# ---------------------------------------------------------------------------------------------
+
+def replay_map(q: torch.Tensor, k: torch.Tensor, lse: torch.Tensor, *, softmax_scale: float,
+               log_threshold: float, q_video_offset: int, k_video_offset: int, video_blocks: int,
+               block_size: int) -> torch.Tensor:
+    dev = _need_cuda(q, k, lse)
+    if q.dim() != 4 or k.dim() != 4:
+        raise RuntimeError("Q and K must have shape [B, H, S, D]")
+    if q.shape != k.shape:
+        raise RuntimeError("Q and K shapes must match")
+    if lse.dim() != 3 or tuple(lse.shape) != tuple(q.shape[:3]):
+        raise RuntimeError("LSE shape must match Q except for head_dim")
+    if not (q.is_contiguous() and k.is_contiguous() and lse.is_contiguous()):
+        raise RuntimeError("Q, K, and LSE must be contiguous")
+    if q.dtype != k.dtype:
+        raise RuntimeError("Q and K dtypes must match")
+    if q.dtype not in _DTYPE:
+        raise RuntimeError("Q and K must be float16 or bfloat16")
+    if lse.dtype != torch.float32:
+        raise RuntimeError("LSE must be float32")
+    B, H, N, D = q.shape
+    out = torch.empty(B, H, video_blocks, video_blocks, device=dev, dtype=torch.float16)
+    with torch.cuda.device(dev):
+        rc = lib.moddit_replay_map(_ptr(q), _ptr(k), _ptr(lse), _DTYPE[q.dtype], B * H, N, D, block_size,
+                                   float(softmax_scale), float(log_threshold), int(q_video_offset),
+                                   int(k_video_offset), int(video_blocks), _ptr(out), _stream(dev))
+    if rc != 0:
+        raise RuntimeError("moddit_replay_map: " + lib.moddit_last_error_string().decode())
+    return out
+
+
+def replay_status(device: torch.device) -> Tuple[int, int, int, int]:
+    host = (ctypes.c_int32 * 4)()
+    with torch.cuda.device(device):
+        check(lib.moddit_replay_status(host, _stream(device)), "moddit_replay_status")
+    return tuple(int(x) for x in host)
+
+
+# ---------------------------------------------------------------------------------------------
+# least squares
+# ---------------------------------------------------------------------------------------------
+
+def mts(S_T: torch.Tensor, blocks_per_frame: int, *, prev: Optional[torch.Tensor] = None,
+        keep_mask: Optional[torch.Tensor] = None, mask_off: int = 0
+        ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """M^T S of a (H,n,n) float16 map.  With `prev` and `keep_mask` (bool (H,R,R), video region starting at
+    block `mask_off`) the history merge `where(keep, S_T, prev)` happens first and is returned too."""
+    dev = _need_cuda(S_T)
+    if S_T.dtype != torch.float16:
+        S_T = S_T.to(torch.float16)
+    S_T = S_T.contiguous()
+    H, n, _ = S_T.shape
+    merged = None
+    hs = rs = 0
+    if prev is not None:
+        if keep_mask is None:
+            raise ValueError("prev needs keep_mask")
+        prev = prev.to(torch.float16).contiguous()
+        keep_mask = keep_mask.contiguous()
+        if keep_mask.dtype != torch.bool:
+            raise ValueError("keep_mask must be bool")
+        hs, rs = keep_mask.stride(0), keep_mask.stride(1)
+        merged = torch.empty_like(S_T)
+    wsb = lib.moddit_mts_workspace_bytes(H, n)
+    ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
+    out = torch.empty(H, 3 * n, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        check(lib.moddit_mts(_ptr(S_T), _ptr(prev), _ptr(keep_mask), hs, rs, mask_off, _ptr(merged), H, n,
+                             blocks_per_frame, _ptr(out), _ptr(ws), wsb, _stream(dev)), "moddit_mts")
+    return out, merged
+
+
+def mtm(n: int, blocks_per_frame: int, regularization: float, device) -> torch.Tensor:
+    device = torch.device(device)
+    out = torch.empty(3 * n, 3 * n, device=device, dtype=torch.float32)
+    with torch.cuda.device(device):
+        check(lib.moddit_mtm(n, blocks_per_frame, float(regularization), _ptr(out), _stream(device)), "moddit_mtm")
+    return out
+
+
+_FACTOR_CACHE: Dict[tuple, torch.Tensor] = {}
+_FACTOR_LOCK = threading.Lock()
+
+
+def solve_factor(n: int, blocks_per_frame: int, regularization: float, device) -> torch.Tensor:
+    """Inverse of the reduced system for this geometry, computed once per (device, n, bpf, lambda)."""
+    device = torch.device(device)
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device(), n,
+           int(blocks_per_frame), float(regularization))
+    fac = _FACTOR_CACHE.get(key)
+    if fac is not None:
+        return fac
+    with _FACTOR_LOCK:
+        fac = _FACTOR_CACHE.get(key)
+        if fac is not None:
+            return fac
+        fb = lib.moddit_solve_factor_bytes(n)
+        wb = lib.moddit_solve_prepare_workspace_bytes(n)
+        fac = torch.empty(fb, device=device, dtype=torch.uint8)
+        ws = torch.empty(wb, device=device, dtype=torch.uint8)
+        with torch.cuda.device(device):
+            check(lib.moddit_solve_prepare(n, blocks_per_frame, float(regularization), _ptr(fac), _ptr(ws), wb,
+                                           _stream(device)), "moddit_solve_prepare")
+        # other streams may use the factor later: make it globally visible once
+        torch.cuda.current_stream(device).synchronize()
+        _FACTOR_CACHE[key] = fac
+        return fac
+
+
+def solve(mts_: torch.Tensor, n: int, blocks_per_frame: int, regularization: float) -> torch.Tensor:
+    dev = _need_cuda(mts_)
+    mts_ = mts_.contiguous()
+    if mts_.dtype != torch.float32 or mts_.shape[1] != 3 * n:
+        raise ValueError("mts must be float32 (H, 3n)")
+    H = mts_.shape[0]
+    fac = solve_factor(n, blocks_per_frame, regularization, dev)
+    wb = lib.moddit_solve_workspace_bytes(H, n)
+    ws = torch.empty(wb, device=dev, dtype=torch.uint8)
+    X = torch.empty(H, 3 * n, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        check(lib.moddit_solve(_ptr(mts_), _ptr(fac), H, n, blocks_per_frame, float(regularization), _ptr(X),
+                               _ptr(ws), wb, _stream(dev)), "moddit_solve")
+    return X
+
+
+# ---------------------------------------------------------------------------------------------
+# selection, masks, work lists
+# ---------------------------------------------------------------------------------------------
+
+def select_lines(cur_c, cur_d, last_c, last_d, top_k: int, predict_T: float) -> torch.Tensor:
+    dev = _need_cuda(cur_c, cur_d, last_c, last_d)
+    ts = [t.to(torch.float32).contiguous() for t in (cur_c, cur_d, last_c, last_d)]
+    H, n = ts[0].shape
+    if ts[1].shape != (H, 2 * n - 1) or ts[2].shape != (H, n) or ts[3].shape != (H, 2 * n - 1):
+        raise ValueError("feature shapes must be c:(H,n) d:(H,2n-1)")
+    k = min(int(top_k), 3 * n - 1)
+    out = torch.empty(H, k, device=dev, dtype=torch.int64)
+    with torch.cuda.device(dev):
+        check(lib.moddit_select_lines(_ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]), _ptr(ts[3]), H, n, int(top_k),
+                                      float(predict_T), _ptr(out), _stream(dev)), "moddit_select_lines")
+    return out
+
+
+def head_modes(b_d: torch.Tensor, threshold: float = 1.0) -> torch.Tensor:
+    dev = _need_cuda(b_d)
+    b_d = b_d.to(torch.float32).contiguous()
+    out = torch.empty(b_d.shape[0], device=dev, dtype=torch.int32)
+    with torch.cuda.device(dev):
+        check(lib.moddit_head_modes(_ptr(b_d), b_d.shape[0], float(threshold), _ptr(out), _stream(dev)),
+              "moddit_head_modes")
+    return out
+
+
+def mask_from_lines(selected: torch.Tensor, modes: torch.Tensor, *, n: int, blocks_per_frame: int,
+                    model_type: str, text_blocks: int, total_blocks: int) -> torch.Tensor:
+    dev = _need_cuda(selected, modes)
+    if model_type not in _lib.LAYOUT:
+        raise ValueError(f"Unknown model_type: {model_type}, expected 'wan', 'hunyuan', or 'cogvideox'")
+    selected = selected.to(torch.int64).contiguous()
+    modes = modes.to(torch.int32).contiguous()
+    H, k = selected.shape
+    nbt = n if model_type == "wan" else total_blocks
+    mask = torch.empty(H, nbt, nbt, device=dev, dtype=torch.bool)
+    with torch.cuda.device(dev):
+        check(lib.moddit_mask_from_lines(_ptr(selected), k, _ptr(modes), H, n, blocks_per_frame,
+                                         _lib.LAYOUT[model_type], text_blocks, nbt, _ptr(mask), _stream(dev)),
+              "moddit_mask_from_lines")
+    return mask
+
+
+def select_mass(dark_map: torch.Tensor, tau: float) -> torch.Tensor:
+    dev = _need_cuda(dark_map)
+    dark_map = dark_map.to(torch.float16).contiguous()
+    H, n, _ = dark_map.shape
+    keep = torch.empty(H, n, n, device=dev, dtype=torch.bool)
+    with torch.cuda.device(dev):
+        check(lib.moddit_select_mass(_ptr(dark_map), H, n, float(tau), _ptr(keep), _stream(dev)),
+              "moddit_select_mass")
+    return keep
+
+
+def tile_lists(mask: torch.Tensor, block_size: int, n_tokens: int, kv_block_limit: Optional[int] = None
+               ) -> Tuple[torch.Tensor, torch.Tensor]:
+    dev = _need_cuda(mask)
+    if mask.dtype != torch.bool or mask.dim() != 3:
+        raise ValueError("mask must be a bool (H, nbq, nbk) tensor")
+    mask = mask.contiguous()
+    Hm, nbq, nbk = mask.shape
+    ntq = (n_tokens + 127) // 128
+    npairs = (ntq + 1) // 2
+    counts = torch.empty(Hm, npairs, device=dev, dtype=torch.int32)
+    entries = torch.empty(Hm, npairs, ntq, device=dev, dtype=torch.int32)
+    lim = nbk if kv_block_limit is None else int(kv_block_limit)
+    with torch.cuda.device(dev):
+        check(lib.moddit_tile_lists(_ptr(mask), Hm, nbq, nbk, block_size, n_tokens, lim, _ptr(counts),
+                                    _ptr(entries), _stream(dev)), "moddit_tile_lists")
+    return counts, entries
+
+
+# ---------------------------------------------------------------------------------------------
+# sparse forward
+# ---------------------------------------------------------------------------------------------
+
+_STATUS: Dict[int, torch.Tensor] = {}
+
+
+def _status_words(dev: torch.device) -> torch.Tensor:
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = _STATUS.get(idx)
+    if st is None:
+        st = torch.zeros(4, device=dev, dtype=torch.int32)
+        _STATUS[idx] = st
+    return st
+
+
+def raise_on_status(device) -> None:
+    """Synchronising check of the sparse forward's status words on `device`."""
+    device = torch.device(device)
+    st = _status_words(device)
+    vals = st.tolist()
+    if vals[0] != 0:
+        st.zero_()
+        raise _lib.ModditError(
+            f"sparse_attn_fwd: a bounded wait expired inside the kernel (code={vals[0]} block={vals[1]} "
+            f"role={vals[2]} position={vals[3]}); the output is invalid")
+
+
+def sparse_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, counts: torch.Tensor,
+                    entries: torch.Tensor, *, softmax_scale: Optional[float] = None,
+                    q_split: Optional[int] = None, kv_len_lo: Optional[int] = None,
+                    kv_len_hi: Optional[int] = None, return_lse: bool = False, check_status: bool = True,
+                    out: Optional[torch.Tensor] = None):
+    """Block-sparse attention forward of (B,H,N,D) tensors over the work lists from `tile_lists`."""
+    dev = _need_cuda(q, k, v, counts, entries)
+    _need_contig(q=q, k=k, v=v, counts=counts, entries=entries)
+    if q.shape != k.shape or q.shape != v.shape or q.dtype != k.dtype or q.dtype != v.dtype:
+        raise ValueError("query, key, and value must have identical shapes and dtypes")
+    B, H, N, D = q.shape
+    Hm = counts.shape[0]
+    ntq = (N + 127) // 128
+    if counts.dtype != torch.int32 or entries.dtype != torch.int32 or \
+            tuple(counts.shape) != (Hm, (ntq + 1) // 2) or tuple(entries.shape) != (Hm, (ntq + 1) // 2, ntq):
+        raise ValueError("counts/entries do not match the sequence length (see tile_lists)")
+    scale = float(D ** -0.5 if softmax_scale is None else softmax_scale)
+    if out is None:
+        out = torch.empty_like(q)
+    lse = torch.empty(B, H, N, device=dev, dtype=torch.float32) if return_lse else None
+    st = _status_words(dev)
+    with torch.cuda.device(dev):
+        check(lib.moddit_sparse_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _qkv_dtype(q), B * H, N, D, _ptr(counts),
+                                         _ptr(entries), Hm, scale, N if q_split is None else int(q_split),
+                                         N if kv_len_lo is None else int(kv_len_lo),
+                                         N if kv_len_hi is None else int(kv_len_hi), _ptr(out), _ptr(lse),
+                                         _ptr(st), _stream(dev)), "moddit_sparse_attn_fwd")
+    if check_status:
+        raise_on_status(dev)
+    return (out, lse) if return_lse else out

@@ -1,0 +1,189 @@
+"""GPU parity of the pooling / least-squares / selection / mask / work-list kernels against the oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moddit_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from moddit_b200 import ops as _ops
+    return _ops
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D,bs,N", [(128, 128, 640), (64, 64, 448), (128, 64, 200), (64, 128, 385)])
+def test_pool_blocks(ops, dtype, D, bs, N):
+    torch.manual_seed(0)
+    x = torch.randn(1, 3, N, D).to(dtype)
+    ref = orc.pool_blocks(x, bs)
+    got = ops.pool_blocks(x.cuda(), bs).cpu()
+    assert got.shape == ref.shape
+    # fp32 accumulation of exactly representable inputs: differences are summation order only
+    assert torch.allclose(got, ref, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("n,nb,qo,D", [(20, 22, 0, 128), (37, 40, 3, 64), (70, 70, 0, 128)])
+def test_pooled_map(ops, n, nb, qo, D):
+    torch.manual_seed(1)
+    qbar = torch.randn(1, 2, nb, D)
+    kbar = torch.randn(1, 2, nb, D)
+    scale = D ** -0.5
+    ref = orc.pooled_darkness_map(qbar, kbar, q_block_offset=qo, k_block_offset=qo, video_blocks=n, scale=scale)
+    got = ops.pooled_map(qbar.cuda(), kbar.cuda(), q_block_offset=qo, k_block_offset=qo, video_blocks=n,
+                         scale=scale).cpu()
+    assert got.dtype == torch.float16 and got.shape == ref.shape
+    assert (got.float() - ref.float()).abs().max().item() <= 2e-3       # one fp16 ulp near 1.0 is 4.9e-4
+
+
+def _grid_map(H, n, bs, seed):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randint(0, bs * bs + 1, (H, n, n), generator=g).float() / float(bs * bs)).to(torch.float16)
+
+
+@pytest.mark.parametrize("n,bpf,H", [(12, 4, 3), (13, 4, 2), (64, 16, 2), (100, 30, 3), (33, 40, 1)])
+def test_mts_exact_on_count_grid(ops, n, bpf, H):
+    S = _grid_map(H, n, 128, 10 + n)
+    ref = orc.compute_mts(S, bpf)
+    got, merged = ops.mts(S.cuda(), bpf)
+    assert merged is None
+    got = got.cpu()
+    # line sums of count/bs^2 values are exact in fp32 for n <= 1024: bit-exact whatever the order
+    assert torch.equal(got[:, :-1], ref[:, :-1])
+    assert torch.allclose(got[:, -1], ref[:, -1], rtol=1e-6)
+
+
+def test_mts_matches_reference_golden(ops, golden_dir):
+    g = np.load(os.path.join(golden_dir, "lstsq.npz"))
+    for ci in range(4):
+        n, bpf, H = (int(x) for x in g[f"ls{ci}_meta"])
+        S = torch.from_numpy(g[f"ls{ci}_S"]).to(torch.float16)
+        got, _ = ops.mts(S.cuda(), bpf)
+        ref = torch.from_numpy(g[f"ls{ci}_mts"])
+        assert torch.equal(got.cpu()[:, :-1], ref[:, :-1])
+        assert torch.allclose(got.cpu()[:, -1], ref[:, -1], rtol=1e-6)
+
+
+@pytest.mark.parametrize("layout,off", [("wan", 0), ("hunyuan", 0), ("cogvideox", 2)])
+def test_mts_history_merge(ops, layout, off):
+    H, n, bpf = 2, 21, 5
+    cur = _grid_map(H, n, 64, 1)
+    prev = _grid_map(H, n, 64, 2)
+    nbt = n if layout == "wan" else n + 2
+    g = torch.Generator().manual_seed(3)
+    full_mask = torch.rand(H, nbt, nbt, generator=g) < 0.5
+    video_mask = full_mask[:, off:off + n, off:off + n]
+    ref_merged = torch.where(video_mask == False, prev, cur)      # noqa: E712  (as MoD/mod/attn_mask.py:671-675)
+    got, merged = ops.mts(cur.cuda(), bpf, prev=prev.cuda(), keep_mask=full_mask.cuda(), mask_off=off)
+    assert torch.equal(merged.cpu(), ref_merged)
+    assert torch.equal(got.cpu()[:, :-1], orc.compute_mts(ref_merged, bpf)[:, :-1])
+
+
+@pytest.mark.parametrize("n,bpf,lam", [(12, 4, 1.0), (13, 4, 1.0), (64, 16, 1.0), (30, 7, 1e-3), (200, 30, 1.0)])
+def test_mtm_and_solve(ops, n, bpf, lam):
+    H = 3
+    S = _grid_map(H, n, 128, 20 + n)
+    mtm = ops.mtm(n, bpf, lam, "cuda").cpu()
+    assert torch.equal(mtm, orc.compute_mtm(n, bpf, lam))
+    mts = orc.compute_mts(S, bpf)
+    ref = orc.solve_features(mts, n, bpf, lam, precise=True)["X"]
+    X = ops.solve(mts.cuda(), n, bpf, lam).cpu()
+    # float64 structured solve rounded to float32 against a float64 dense solve
+    assert torch.allclose(X.double(), ref, rtol=2e-5, atol=2e-6 / min(1.0, lam))
+    # and against the reference's own fp32 path within that path's rounding error
+    ref32 = orc.solve_features(mts, n, bpf, lam)["X"]
+    tol = 5e-4 if lam >= 0.5 else 5e-2
+    assert (X - ref32).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+
+
+def test_solve_matches_reference_golden(ops, golden_dir):
+    g = np.load(os.path.join(golden_dir, "lstsq.npz"))
+    for ci in range(4):
+        n, bpf, H = (int(x) for x in g[f"ls{ci}_meta"])
+        lam = float(g[f"ls{ci}_lam"])
+        mts = torch.from_numpy(g[f"ls{ci}_mts"])
+        X = ops.solve(mts.cuda(), n, bpf, lam).cpu()
+        tol = dict(atol=2e-5, rtol=1e-4) if lam >= 0.5 else dict(atol=2e-3, rtol=1e-2)
+        nd = 2 * n - 1
+        assert torch.allclose(X[:, :nd], torch.from_numpy(g[f"ls{ci}_d"]), **tol)
+        assert torch.allclose(X[:, nd:nd + n] / 2, torch.from_numpy(g[f"ls{ci}_c"]), **tol)
+        assert torch.allclose(X[:, -1], torch.from_numpy(g[f"ls{ci}_bd"]), **tol)
+
+
+def test_selection_and_mask_bit_exact_vs_golden(ops, golden_dir):
+    g = np.load(os.path.join(golden_dir, "selection.npz"))
+    for ci in range(4):
+        bs, video, text, bpf, H, top_k, pT = (int(x) for x in g[f"sel{ci}_meta"])
+        model = str(g[f"sel{ci}_model"])
+        n = video // bs
+        hist = [{k_: torch.from_numpy(g[f"sel{ci}_h{t}_{k_}"]).cuda() for k_ in ("c", "d", "b_d")} for t in range(2)]
+        lines = ops.select_lines(hist[1]["c"], hist[1]["d"], hist[0]["c"], hist[0]["d"], top_k, pT)
+        ref_lines = torch.from_numpy(g[f"sel{ci}_lines"])
+        assert lines.shape == ref_lines.shape
+        # identical to the oracle including order; identical to the reference as a set
+        hist_cpu = [{k_: v.cpu() for k_, v in h.items()} for h in hist]
+        assert torch.equal(lines.cpu(), orc.choose_topk_lines(hist_cpu[0], hist_cpu[1], top_k, pT))
+        for h in range(H):
+            assert set(lines[h].tolist()) == set(ref_lines[h].tolist())
+        modes = ops.head_modes(hist[1]["b_d"], 1.0)
+        ref_modes = [str(x) for x in g[f"sel{ci}_mode"]]
+        from moddit_b200 import _lib
+        assert [_lib.MODE_NAME[int(m)] for m in modes.tolist()] == ref_modes
+        kw = dict(n=n, blocks_per_frame=bpf, model_type=model, text_blocks=text // bs,
+                  total_blocks=(video + text) // bs)
+        mask = ops.mask_from_lines(lines, modes, **kw).cpu()
+        assert torch.equal(mask, torch.from_numpy(g[f"sel{ci}_mask"]))
+        modes2 = torch.tensor([_lib.MODE_CODE[str(x)] for x in g[f"sel{ci}_modes2"]], dtype=torch.int32).cuda()
+        mask2 = ops.mask_from_lines(ref_lines.cuda(), modes2, **kw).cpu()
+        assert torch.equal(mask2, torch.from_numpy(g[f"sel{ci}_mask2"]))
+
+
+def test_select_lines_ties_and_full_size(ops):
+    H, n = 24, 900
+    g = torch.Generator().manual_seed(5)
+    c0, c1 = torch.randn(H, n, generator=g), torch.randn(H, n, generator=g)
+    d0, d1 = torch.randn(H, 2 * n - 1, generator=g), torch.randn(H, 2 * n - 1, generator=g)
+    c1[:, 10:40] = 0.25
+    c0[:, 10:40] = 0.25                       # thirty exactly equal predictions
+    d1[0, 5] = float("nan")
+    last, cur = {"c": c0, "d": d0}, {"c": c1, "d": d1}
+    got = ops.select_lines(c1.cuda(), d1.cuda(), c0.cuda(), d0.cuda(), 300, 5).cpu()
+    pred = orc.predict_lines(last, cur, 5)
+    pred = torch.where(torch.isnan(pred), torch.full_like(pred, float("inf")), pred)
+    ref = torch.sort(pred, dim=1, stable=True).indices[:, :300]
+    assert torch.equal(got, ref)
+
+
+@pytest.mark.parametrize("n,tau", [(16, 0.9), (100, 0.5), (900, 0.9), (33, 1.0), (7, 0.0)])
+def test_select_mass_bit_exact(ops, n, tau):
+    torch.manual_seed(n)
+    H = 2
+    dark = (1 - torch.softmax(torch.randn(H, n, n) * 3, -1)).to(torch.float16)
+    dark[0, 0, : min(n, 5)] = dark[0, 0, 0]        # ties
+    got = ops.select_mass(dark.cuda(), tau).cpu()
+    rows = range(n) if n <= 100 else [0, 1, n // 2, n - 1]       # the oracle's loops are slow at full size
+    for h in range(H):
+        for i in rows:
+            assert np.array_equal(got[h, i].numpy(), orc.select_mass_row(dark[h, i], i, tau)), (h, i)
+
+
+@pytest.mark.parametrize("bs,N,H", [(128, 640, 2), (64, 448, 3), (64, 458, 1), (128, 1000, 1), (128, 128 * 300, 1)])
+def test_tile_lists_bit_exact(ops, bs, N, H):
+    torch.manual_seed(N)
+    nb = (N + bs - 1) // bs
+    mask = torch.rand(H, nb, nb) < 0.35
+    lim = nb - 1 if N % 7 == 0 else None
+    if N > 20000:
+        mask = torch.rand(H, nb, nb) < 0.05
+    counts, entries = ops.tile_lists(mask.cuda(), bs, N, lim)
+    rc, re = orc.build_tile_lists(mask, bs, N, lim)
+    assert torch.equal(counts.cpu(), torch.from_numpy(rc))
+    ent = entries.cpu().numpy()
+    for h in range(H):
+        for p in range(rc.shape[1]):
+            assert np.array_equal(ent[h, p, :rc[h, p]], re[h, p, :rc[h, p]])
