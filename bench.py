@@ -1,0 +1,402 @@
+#!/usr/bin/env python3
+"""Benchmark of the MOD-DiT attention layer (mask prediction + block-sparse attention) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload hunyuan]
+
+One "step" is one attention-layer call at the workload's shape: pooled mask prediction (Q/K block
+pooling, pooled map, M^T S, solve, line selection, mask, work lists) followed by the block-sparse
+forward, all through the public `SparseAttentionWithMap` API.  Rank 0 prints one JSON line.
+
+  value      kept-block TFLOP/s of the whole job with q/k/v resident in HBM (inputs, 2.1 GB at the
+             HunyuanVideo shape, are far larger than L2, so nothing stays cached between steps)
+  e2e        the same metric with q/k/v in pinned host memory: every step copies them to the device
+             and copies the output back, inside the timed region
+  roofline   the block-sparse forward kernel alone (CUDA events around its launches in the timed
+             region) against the measured bf16 tensor peak
+  cpu_baseline  the CPU oracle (`oracle/`) timed on the host cores on a bounded sample of the workload
+
+With N > 1 (torchrun) heads are sharded over ranks: every rank holds a sequence shard of q/k/v, an
+all-to-all turns it into a head shard, the path runs on the local heads and the output goes back
+through a second all-to-all; total work is fixed ("strong" scaling).
+
+`--impl reference` times the reference's own CPU path for this hot path (the oracle port of it: the
+reference itself is Python that needs its checkout, which does not exist on the benchmark box).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import logging
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "mod-dit_b200"))
+
+import torch  # noqa: E402
+
+METRIC = "MOD-DiT attn layer effective TFLOP/s on kept blocks @115k tok bf16 (ms_per_step = layer ms; mask_pred_pct = mask-pred overhead %)"
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_state(cfg, heads_local):
+    from MoD.mod.state import create_adaptive_mask_state
+    T, Hh, Ww = cfg["grid"]
+    video = T * Hh * Ww
+    state = create_adaptive_mask_state(cfg["model_type"], heads_local, video, cfg["text_tokens"], Hh * Ww, T,
+                                       warmup_steps=2, top_k=cfg["top_k"], predict_T=cfg["predict_T"],
+                                       threshold=1e-4, block_size=cfg["block_size"])
+    state["score_producer"] = "pooled"
+    return state
+
+
+def kept_flops(mask: torch.Tensor, block_size: int, head_dim: int) -> float:
+    return float(mask.sum().item()) * 4.0 * block_size * block_size * head_dim
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from MoD.mod.attn_mask import SparseAttentionWithMap
+    from moddit_b200 import dist as mdist
+    from moddit_b200 import ops, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1")) if args.gpus > 1 else 1
+    rank = int(os.environ.get("RANK", "0")) if world > 1 else 0
+    local_rank = int(os.environ.get("LOCAL_RANK", "0")) if world > 1 else 0
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = synth.WORKLOADS[args.workload]
+    H, D, bs = cfg["heads"], cfg["head_dim"], cfg["block_size"]
+    if H % world:
+        raise SystemExit(f"{H} heads do not divide over {world} GPUs")
+    hb, he = mdist.shard_bounds(H, world, rank)
+    logger = logging.getLogger("bench")
+    logger.setLevel(logging.WARNING)
+
+    q, k, v = synth.make_qkv(heads=H, grid=cfg["grid"], head_dim=D, text_tokens=cfg["text_tokens"],
+                             text_first=cfg["text_first"], seed=1, gain=args.gain, corr=1.0, device=dev,
+                             head_begin=hb, head_end=he)
+    N = q.shape[2]
+    if world > 1:
+        # what a sequence-parallel caller holds: its sequence shard of all heads
+        q_in, k_in, v_in = (mdist.head_to_seq(t) for t in (q, k, v))
+        del q, k, v
+    else:
+        q_in, k_in, v_in = q, k, v
+    state = make_state(cfg, he - hb)
+
+    def layer(qs, ks, vs, step):
+        if world > 1:
+            qs, ks, vs = mdist.seq_to_head(qs), mdist.seq_to_head(ks), mdist.seq_to_head(vs)
+        out, _ = SparseAttentionWithMap(qs, ks, vs, state, logger, current_step=step)
+        if world > 1:
+            out = mdist.head_to_seq(out)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # two untimed priming steps fill the feature history (the first one runs dense attention)
+    for step in range(2):
+        layer(q_in, k_in, v_in, step)
+    for i in range(args.warmup):
+        layer(q_in, k_in, v_in, 2 + i)
+    ops.raise_on_status(dev)
+
+    # ---- value: inputs resident in HBM ------------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    ops.stage_timing(True)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        layer(q_in, k_in, v_in, 2 + args.warmup + i)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = ev0.elapsed_time(ev1)
+    records = ops.stage_records()
+    launches = ops.launches_recorded()
+    ops.stage_timing(False)
+    ops.raise_on_status(dev)
+
+    mask = state["mask"]
+    flops_local = kept_flops(mask, bs, D)
+    sparsity_local = 1.0 - float(mask.float().mean().item())
+    stage_ms = {}
+    for name, ms in records:
+        stage_ms[name] = stage_ms.get(name, 0.0) + ms
+    attn_ms = stage_ms.get("moddit_sparse_attn_fwd", 0.0) / args.steps
+    pred_ms = sum(ms for name, ms in stage_ms.items() if name != "moddit_sparse_attn_fwd") / args.steps
+
+    # ---- e2e: inputs in pinned host memory, output copied back ----------------------------------
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    host_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in (q_in, k_in, v_in)]
+    host_out = torch.empty(q_in.shape, dtype=q_in.dtype, pin_memory=True)
+    dev_in = [torch.empty_like(t) for t in (q_in, k_in, v_in)]
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step(step):
+        for d, h in zip(dev_in, host_in):
+            d.copy_(h, non_blocking=True)
+        out = layer(dev_in[0], dev_in[1], dev_in[2], step)
+        host_out.copy_(out, non_blocking=True)
+
+    e2e_step(100)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(101 + i)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    # ---- reduce over ranks ------------------------------------------------------------------------
+    vals = torch.tensor([total_ms, e2e_ms, attn_ms, pred_ms], device=dev, dtype=torch.float64)
+    sums = torch.tensor([flops_local, sparsity_local, float(launches), float(h2d), float(d2h)], device=dev,
+                        dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    total_ms, e2e_ms, attn_ms, pred_ms = vals.tolist()
+    flops_total, sparsity_sum, launches_total, h2d_total, d2h_total = sums.tolist()
+
+    if rank == 0:
+        peaks = load_peaks()
+        ms_per_step = total_ms / args.steps
+        value = flops_total / (ms_per_step * 1e-3) / 1e12
+        e2e_value = flops_total / (e2e_ms / e2e_steps * 1e-3) / 1e12
+        # roofline of the dominant kernel: kept flops of one launch on this rank / its average duration
+        achieved = flops_local / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else 0.0
+        peak = float(peaks["bf16_tflops"])
+        roof = {"bound": "tensor", "kernel": "sparse_attn_fwd_kernel", "achieved": round(achieved, 2), "peak": peak,
+                "peak_source": f"of {peaks['_source']} (burst)", "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
+                "frac_of_sustained": round(achieved / float(peaks["bf16_tflops_sustained"]), 4),
+                "frac_of_nominal_2250": round(achieved / 2250.0, 4), "kernel_ms": round(attn_ms, 3),
+                "flops_per_launch": flops_local, "traffic": load_traffic(args.workload)}
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: B=1 H={H} D={D} N={N} block={bs} top_k={cfg['top_k']} "
+                                   f"pooled mask prediction every step",
+                       "sparsity": round(sparsity_sum / world, 4), "parallelism": f"head-sharded x{world}",
+                       "l2": "inputs larger than L2", "gain": args.gain, "seed": 1},
+            "mask_pred_ms": round(pred_ms, 3), "mask_pred_pct": round(100.0 * pred_ms / max(pred_ms + attn_ms, 1e-9), 2),
+            "attn_ms": round(attn_ms, 3),
+            "stage_ms_per_step": {n: round(ms / args.steps, 4) for n, ms in sorted(stage_ms.items())},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms / e2e_steps, 3),
+                    "steps": e2e_steps, "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total)},
+            "gpu_launches": int(launches_total),
+            "roofline": roof,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args.workload, args.gain, blocks=args.cpu_blocks)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def load_traffic(workload):
+    """DRAM bytes per launch of the sparse forward from the committed ncu summary, or None."""
+    path = os.path.join(ROOT, "profiles", f"sparse_attn_fwd_{workload}_traffic.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return json.load(fh).get("dram_bytes_per_launch")
+    return None
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference path on the host cores
+# ---------------------------------------------------------------------------------------------
+
+def _load_synth():
+    """The synthetic generator alone (pure torch), without importing the kernel package."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "moddit_synth_standalone", os.path.join(ROOT, "mod-dit_b200", "moddit_b200", "synth.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def cpu_sample(workload: str, gain: float, blocks: int):
+    """One head of the workload on the CPU: full mask prediction, then `blocks` query blocks of fp32
+    block-masked attention.  Returns (kept flops of those blocks, seconds, description)."""
+    synth = _load_synth()
+    from oracle import moddit_oracle as orc
+    cfg = synth.WORKLOADS[workload]
+    D, bs = cfg["head_dim"], cfg["block_size"]
+    T, Hh, Ww = cfg["grid"]
+    q, k, v = synth.make_qkv(heads=cfg["heads"], grid=cfg["grid"], head_dim=D, text_tokens=cfg["text_tokens"],
+                             text_first=cfg["text_first"], seed=1, gain=gain, device="cpu", dtype=torch.bfloat16,
+                             head_begin=0, head_end=1)
+    N = q.shape[2]
+    video = T * Hh * Ww
+    n = video // bs
+    bpf = (Hh * Ww) // bs
+    off = cfg["text_tokens"] // bs if cfg["text_first"] else 0
+    t0 = time.perf_counter()
+    feats = []
+    for rep in range(2):   # two feature sets are needed before a mask exists; both are part of the path
+        dark = orc.pooled_darkness_map(orc.pool_blocks(q, bs), orc.pool_blocks(k, bs), q_block_offset=off,
+                                       k_block_offset=off, video_blocks=n, scale=D ** -0.5)[0]
+        f = orc.solve_features(orc.compute_mts(dark, bpf), n, bpf, 1.0)
+        feats.append({key: f[key] for key in ("c", "d", "b_d")})
+    lines = orc.choose_topk_lines(feats[0], feats[1], cfg["top_k"], cfg["predict_T"])
+    mask = orc.generate_mask_from_lines(model_type=cfg["model_type"], block_size=bs, video_token_num=video,
+                                        text_token_num=cfg["text_tokens"], seq_len=N, blocks_per_frame=bpf,
+                                        selected_lines=lines, mode=orc.check_bd_values(feats[1]["b_d"], 1.0))
+    t_pred = (time.perf_counter() - t0) / 2.0          # one prediction per step
+    nbt = mask.shape[-1]
+    rows = [int(i * nbt / blocks) for i in range(blocks)]
+    t1 = time.perf_counter()
+    orc.masked_attention(q, k, v, mask, bs, row_blocks=rows)
+    t_attn = time.perf_counter() - t1
+    flops = float(mask[0, rows].sum().item()) * 4.0 * bs * bs * D
+    seconds = t_attn + t_pred * blocks / nbt
+    desc = (f"1 of {cfg['heads']} heads: mask prediction ({t_pred:.2f} s per head, charged {blocks}/{nbt}) + {blocks} of "
+            f"{nbt} query blocks of fp32 block-masked attention ({t_attn:.2f} s); oracle port of the reference CPU path")
+    return flops, seconds, desc
+
+
+def cpu_baseline(workload, gain, blocks):
+    torch.set_num_threads(os.cpu_count() or 1)
+    flops, seconds, desc = cpu_sample(workload, gain, blocks)
+    return {"value": round(flops / seconds / 1e12, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+            "kind": "port", "sample": desc, "seconds": round(seconds, 2)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = _load_synth().WORKLOADS[args.workload]
+    for _ in range(args.warmup):
+        cpu_sample(args.workload, args.gain, 1)
+    tot_f, tot_s, desc = 0.0, 0.0, ""
+    for _ in range(args.steps):
+        f, s, desc = cpu_sample(args.workload, args.gain, args.ref_blocks)
+        tot_f += f
+        tot_s += s
+    value = tot_f / tot_s / 1e12
+    T, Hh, Ww = cfg["grid"]
+    N = T * Hh * Ww + cfg["text_tokens"]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 5), "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(tot_s / args.steps * 1e3, 2),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: B=1 H={cfg['heads']} D={cfg['head_dim']} N={N} "
+                               f"block={cfg['block_size']} top_k={cfg['top_k']} pooled mask prediction every step",
+                   "note": "each step is a bounded sample of the workload on the host cores"},
+        "cpu_baseline": {"value": round(value, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": desc},
+        "e2e": {"value": round(value, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", default="hunyuan")
+    ap.add_argument("--gain", type=float, default=2.0, help="strength of the positional term of the synthetic q/k")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--cpu-blocks", type=int, default=48, help="query blocks in the cpu_baseline sample")
+    ap.add_argument("--ref-blocks", type=int, default=8, help="query blocks per step of --impl reference")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

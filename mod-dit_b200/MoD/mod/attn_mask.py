@@ -1,0 +1,364 @@
+"""Adaptive sparse attention state machine on the sm_100a kernels.
+
+Keeps the processor-facing function `SparseAttentionWithMap` and the helper names of the reference's
+MoD/mod/attn_mask.py (update_warmup :117-146, compute_block_sparse_map_triton :252-263,
+AttentionSparseEngine :266-331, check_bd_values :336-349, choose_topk_lines :351-370,
+predict_mask_from_warmup :373-436, generate_mask_from_lines :440-559, SparseAttentionWithMap :567-729).
+
+Differences that are deliberate:
+  * every stage runs on this build's kernels; there is no third-party attention kernel, no Triton and
+    no CPU path;
+  * the block mask is honoured at its native block_size x block_size granularity (the reference's
+    third-party sparse kernel coarsens it to 128-row x 64-column tiles);
+  * two optional state keys, `score_producer='pooled'` and `selector='cumulative_mass'`, enable the
+    mean-pooled map producer and the cumulative-mass selector; their defaults keep reference behaviour;
+  * 'radial' and 'spargeattn' baselines are not part of this build and raise NotImplementedError.
+"""
+import logging
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from MoD.mod.cuda_lstsq import features_from_solution, solve_lstsq
+from MoD.mod.state import is_warmup_complete
+from MoD.mod.triton_flash_sparsity import dense_attention_with_lse, flash_attn_with_sparsity_map
+from moddit_b200 import _lib
+from moddit_b200 import ops as _ops
+
+
+# ------------------------------------------------------------------------------------------------
+# feature extraction
+# ------------------------------------------------------------------------------------------------
+
+def extract_attention_features(warmup_state: Dict, S_T: torch.Tensor, blocks_per_frame: int, layer_idx: int = 0,
+                               regularization: float = 1, use_cuda: bool = True) -> Dict[str, torch.Tensor]:
+    """Fit S_T (H, n, n) onto the line basis; regularisation 1 by default as in the reference (:76-115)."""
+    num_heads, n = S_T.shape[0], S_T.shape[1]
+    assert S_T.shape == (num_heads, n, n), f"S_T shape mismatch: {S_T.shape} vs ({num_heads}, {n}, {n})"
+    return solve_lstsq(warmup_state=warmup_state, S_T=S_T, step=warmup_state['current_steps'], layer_idx=layer_idx,
+                       blocks_per_frame=blocks_per_frame, regularization=regularization, use_cuda=use_cuda)
+
+
+def update_warmup(warmup_state: Dict, step: int, block_sparse_map: torch.Tensor):
+    """Append the features of this step's map to the history (:117-146)."""
+    if step == warmup_state['warmup_steps'] - 2:
+        warmup_state['features_history'] = []
+        warmup_state['current_steps'] = step
+        warmup_state['prev_full_maps'] = block_sparse_map
+    features = extract_attention_features(warmup_state=warmup_state, S_T=block_sparse_map,
+                                          blocks_per_frame=warmup_state['blocks_per_frame'],
+                                          use_cuda=warmup_state['use_cuda'])
+    warmup_state['features_history'].append(features)
+    warmup_state['current_steps'] = step + 1
+    warmup_state['prev_full_maps'] = block_sparse_map
+
+
+# ------------------------------------------------------------------------------------------------
+# map producers
+# ------------------------------------------------------------------------------------------------
+
+def compute_block_sparse_map_triton(query, key, value, warmup_state):
+    """Dense output and exact sparsity map (name kept from the reference, :252-263)."""
+    return flash_attn_with_sparsity_map(
+        query, key, value,
+        block_size=warmup_state['block_size'],
+        video_token_num=warmup_state['video_token_num'],
+        text_token_num=warmup_state['text_token_num'],
+        threshold=warmup_state['threshold'],
+        model_type=warmup_state['model_type'])
+
+
+compute_block_sparse_map = compute_block_sparse_map_triton
+
+
+def compute_pooled_map(query, key, warmup_state) -> torch.Tensor:
+    """Mean-pooled stand-in for the sparsity map: (B,H,n,n) float16, same polarity as the exact map."""
+    bs = warmup_state['block_size']
+    n = _video_blocks(warmup_state, query.shape[2])
+    off = warmup_state['text_token_num'] // bs if warmup_state['model_type'] == 'cogvideox' else 0
+    qbar = _ops.pool_blocks(query, bs)
+    kbar = _ops.pool_blocks(key, bs)
+    return _ops.pooled_map(qbar, kbar, q_block_offset=off, k_block_offset=off, video_blocks=n,
+                           scale=query.shape[3] ** -0.5)
+
+
+def _video_blocks(warmup_state, seq_len):
+    if warmup_state['model_type'] == 'wan':
+        return seq_len // warmup_state['block_size']
+    return warmup_state['video_token_num'] // warmup_state['block_size']
+
+
+# ------------------------------------------------------------------------------------------------
+# sparse engine
+# ------------------------------------------------------------------------------------------------
+
+def _valid_kv(pre_defined_mask: Optional[torch.Tensor], seq_len: int) -> int:
+    """Number of valid (unpadded) keys; reads one row of the caller's mask (one host sync, as :270,281,310)."""
+    if pre_defined_mask is None:
+        return seq_len
+    return int(pre_defined_mask[0].sum().item())
+
+
+def _engine_lists(mask: torch.Tensor, block_size: int, seq_len: int):
+    if mask.dim() == 2:
+        mask = mask.unsqueeze(0)
+    nb = (seq_len + block_size - 1) // block_size
+    if mask.shape[-1] != nb or mask.shape[-2] != nb:
+        # a mask over the video region only (use_dense passes one): it can only be all-true
+        mask = torch.ones(1, nb, nb, device=mask.device, dtype=torch.bool)
+    return _ops.tile_lists(mask, block_size, seq_len)
+
+
+def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_token_num=0, block_size=128,
+                          _lists=None):
+    """Block-sparse attention of (B,H,S,D) tensors under a bool block mask (:266-331).
+
+    Video query rows (index < video_token_num) see the keys below the valid length rounded up to 64, text
+    rows see exactly the valid keys - the split the reference gets from its two third-party kernels.
+    One kernel launch covers both; the result is (B,H,S,D).
+    """
+    seq_len = query.shape[2]
+    query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
+    counts, entries = _lists if _lists is not None else _engine_lists(mask, block_size, seq_len)
+    if pre_defined_mask is None:
+        return _ops.sparse_attn_fwd(query, key, value, counts, entries, check_status=False)
+    valid = _valid_kv(pre_defined_mask, seq_len)
+    border = min(seq_len, (valid + 63) // 64 * 64)
+    return _ops.sparse_attn_fwd(query, key, value, counts, entries, q_split=video_token_num, kv_len_lo=border,
+                                kv_len_hi=valid, check_status=False)
+
+
+# ------------------------------------------------------------------------------------------------
+# mask prediction
+# ------------------------------------------------------------------------------------------------
+
+def check_bd_values(values: torch.Tensor, mode: List[str], threshold: float = -7.5e-2) -> List[str]:
+    """Heads whose last block-diagonal coefficient is <= threshold switch to 'block_diagonal' (:336-349)."""
+    codes = _ops.head_modes(values[:, -1], threshold).tolist()
+    for i, code in enumerate(codes):
+        if mode[i] == 'sparse' and code == _lib.MODE_BLOCK_DIAGONAL:
+            mode[i] = 'block_diagonal'
+    return mode
+
+
+def choose_topk_lines(history: List[Dict[str, torch.Tensor]], top_k: int = 10, predict_T: int = None) -> torch.Tensor:
+    """Indices (H, k) of the k smallest extrapolated line intensities, verticals first (:351-370)."""
+    last, cur = history[-2], history[-1]
+    return _ops.select_lines(cur['c'], cur['d'], last['c'], last['d'], top_k, predict_T)
+
+
+def _mode_codes(mode, device) -> torch.Tensor:
+    if torch.is_tensor(mode):
+        return mode.to(device=device, dtype=torch.int32)
+    return torch.tensor([_lib.MODE_CODE[m] for m in mode], device=device, dtype=torch.int32)
+
+
+def generate_mask_from_lines(warmup_state: Dict, num_heads: int, n: int, blocks_per_frame: int,
+                             selected_lines: torch.Tensor, mode, device: torch.device) -> torch.Tensor:
+    """Bool block mask from the selected lines (:440-559); `n` is the sequence length in tokens."""
+    block_size = warmup_state['block_size']
+    video_blocks = warmup_state['video_token_num'] // block_size
+    model_type = warmup_state.get('model_type')
+    if model_type not in _lib.LAYOUT:
+        return torch.ones(num_heads, n // block_size, n // block_size, dtype=torch.bool, device=device)
+    if model_type == 'wan' and video_blocks == 0:
+        video_blocks = n // block_size
+    selected_lines = torch.as_tensor(selected_lines, device=device)
+    if selected_lines.dim() == 1:
+        selected_lines = selected_lines.unsqueeze(1)
+    return _ops.mask_from_lines(selected_lines.long(), _mode_codes(mode, device), n=video_blocks,
+                                blocks_per_frame=blocks_per_frame, model_type=model_type,
+                                text_blocks=warmup_state['text_token_num'] // block_size,
+                                total_blocks=n // block_size)
+
+
+def predict_mask_from_warmup(warmup_state: Dict, n: int, top_k: int = 10, layer_idx: int = 0) -> Dict:
+    """First mask after warm-up: modes from the block-diagonal coefficients, then top-k lines (:373-436)."""
+    num_heads = warmup_state['num_heads']
+    blocks_per_frame = warmup_state['blocks_per_frame']
+    if not is_warmup_complete(warmup_state):
+        device = torch.device("cuda")
+        nb = n // warmup_state['block_size']
+        return {'mode': ['full'] * num_heads, 'block_diagonal': [False] * num_heads, 'selected_lines': [],
+                'mask': torch.ones(num_heads, nb, nb, dtype=torch.bool, device=device)}
+    history = warmup_state['features_history']
+    device = history[0]['c'].device
+    b_d_values = torch.stack([f['b_d'] for f in history], dim=0).to(device).permute(1, 0)
+    mode = check_bd_values(b_d_values, threshold=1, mode=['sparse'] * num_heads)
+    selected_lines = choose_topk_lines(history, top_k=top_k, predict_T=warmup_state.get('predict_T', None))
+    mask = generate_mask_from_lines(warmup_state, num_heads, n, blocks_per_frame, selected_lines, mode, device)
+    return {'mode': mode, 'selected_lines': selected_lines, 'mask': mask}
+
+
+def _store_mask(warmup_state: Dict, mask: torch.Tensor, seq_len: int):
+    """Keep the mask and the work lists built from it together, so sparse steps rebuild nothing."""
+    warmup_state['mask'] = mask
+    full = mask
+    bs = warmup_state['block_size']
+    nb = (seq_len + bs - 1) // bs
+    if mask.shape[-1] != nb:                      # wan: the mask covers the whole (video-only) sequence
+        raise ValueError(f"mask of {mask.shape[-1]} blocks does not cover a sequence of {nb} blocks")
+    warmup_state['_tile_lists'] = (mask, _ops.tile_lists(full, bs, seq_len))
+
+
+def _lists_for(warmup_state: Dict, seq_len: int):
+    cached = warmup_state.get('_tile_lists')
+    if cached is not None and cached[0] is warmup_state['mask']:
+        return cached[1]
+    _store_mask(warmup_state, warmup_state['mask'], seq_len)
+    return warmup_state['_tile_lists'][1]
+
+
+def _video_region(warmup_state: Dict, mask: torch.Tensor) -> Tuple[torch.Tensor, int]:
+    """(full mask, first video block) so the history merge can index the video region in place."""
+    bs = warmup_state['block_size']
+    if warmup_state['model_type'] == 'cogvideox':
+        return mask, warmup_state['text_token_num'] // bs
+    return mask, 0
+
+
+def _select_and_build(warmup_state: Dict, num_heads: int, seq_len: int, device, dark_map=None):
+    if warmup_state.get('selector', 'topk_lines') == 'cumulative_mass':
+        keep = _ops.select_mass(dark_map, float(warmup_state.get('mass_threshold', 0.9)))
+        return _embed_video_mask(warmup_state, keep, seq_len)
+    lines = choose_topk_lines(warmup_state['features_history'], top_k=warmup_state['top_k'],
+                              predict_T=warmup_state.get('predict_T', None))
+    return generate_mask_from_lines(warmup_state, num_heads, seq_len, warmup_state['blocks_per_frame'], lines,
+                                    warmup_state['mode'], device=device)
+
+
+def _embed_video_mask(warmup_state: Dict, video_mask: torch.Tensor, seq_len: int) -> torch.Tensor:
+    model_type = warmup_state['model_type']
+    if model_type == 'wan':
+        return video_mask
+    bs = warmup_state['block_size']
+    nb = seq_len // bs
+    n = video_mask.shape[-1]
+    off = warmup_state['text_token_num'] // bs if model_type == 'cogvideox' else 0
+    mask = torch.ones(video_mask.shape[0], nb, nb, dtype=torch.bool, device=video_mask.device)
+    mask[:, off:off + n, off:off + n] = video_mask
+    return mask
+
+
+# ------------------------------------------------------------------------------------------------
+# main entry point
+# ------------------------------------------------------------------------------------------------
+
+def SparseAttentionWithMap(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    warmup_state: Dict,
+    logger: logging.Logger,
+    pre_defined_mask: Optional[torch.Tensor] = None,
+    current_step: int = 0,
+    layer_idx: int = 0,
+    use_dense: bool = False,
+    in_test: bool = False,
+    **kwargs
+) -> Tuple[torch.Tensor, Optional[Dict]]:
+    """Adaptive sparse attention of (1, H, S, D) fp16/bf16 tensors (:567-729).
+
+    Steps warmup-2 and warmup-1 collect features (dense output); afterwards every predict_T-th step
+    refreshes the map, the features and the mask (dense output) and all other steps run the block-sparse
+    forward under the stored mask.  Returns (output (1,H,S,D), mask info) like the reference.
+    """
+    seq_len = query.size(2)
+    num_heads = query.size(1)
+    block_size = warmup_state['block_size']
+    video_token_num = warmup_state.get('video_token_num', 0)
+
+    if use_dense:
+        query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
+        valid = _valid_kv(pre_defined_mask, seq_len)
+        output, _ = dense_attention_with_lse(query, key, value, kv_len=valid)
+        return output, {'mode': 'warmup', 'mask': None}
+    sparse_type = warmup_state['sparse_type']
+    if sparse_type in ('spargeattn', 'radial', 'svg'):
+        raise NotImplementedError(f"sparse_type '{sparse_type}' is a third-party baseline that this build does not include")
+
+    pooled = warmup_state.get('score_producer', 'replay') == 'pooled'
+    warmup_steps = warmup_state['warmup_steps']
+    query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
+
+    if pooled:
+        return _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx)
+
+    if current_step < warmup_steps:
+        if current_step >= warmup_steps - 2:
+            output, block_sparse_map = compute_block_sparse_map_triton(query, key, value, warmup_state)
+            update_warmup(warmup_state, current_step, block_sparse_map.squeeze(0))
+        else:
+            output, _ = dense_attention_with_lse(query, key, value, kv_len=_valid_kv(pre_defined_mask, seq_len))
+        if current_step == warmup_steps - 1:
+            mask_info = predict_mask_from_warmup(warmup_state, seq_len, top_k=warmup_state['top_k'],
+                                                 layer_idx=layer_idx)
+            warmup_state['mode'] = mask_info['mode']
+            mask = mask_info['mask']
+            if warmup_state.get('selector', 'topk_lines') == 'cumulative_mass':
+                mask = _select_and_build(warmup_state, num_heads, seq_len, query.device,
+                                         dark_map=warmup_state['prev_full_maps'])
+            _store_mask(warmup_state, mask, seq_len)
+            logger.info(f"Layer {layer_idx}, Mask Sparsity: {1 - warmup_state['mask'].float().mean():.3%}")
+        return output, warmup_state['mask']
+
+    if warmup_state.get('mask', None) is None:
+        raise RuntimeError("SparseAttentionWithMap called after warm-up without a mask: the two feature-collection "
+                           "steps (warmup_steps-2 and warmup_steps-1) have not run for this layer")
+    predict_T = warmup_state['predict_T']
+    if (current_step - warmup_steps) % predict_T == predict_T - 1:
+        # refresh: dense output + exact map, merged into the history where the current mask kept blocks
+        output, current_sparse_map = compute_block_sparse_map_triton(query, key, value, warmup_state)
+        current_sparse_map = current_sparse_map.squeeze(0)
+        full_mask, off = _video_region(warmup_state, warmup_state['mask'])
+        n = current_sparse_map.shape[-1]
+        mts, merged = _ops.mts(current_sparse_map, warmup_state['blocks_per_frame'],
+                               prev=warmup_state['prev_full_maps'], keep_mask=full_mask, mask_off=off)
+        warmup_state['prev_full_maps'] = merged
+        X = _ops.solve(mts, n, warmup_state['blocks_per_frame'], 1.0)
+        warmup_state['features_history'].append(features_from_solution(X, n))
+        warmup_state['features_history'].pop(0)
+        next_mask = _select_and_build(warmup_state, num_heads, seq_len, query.device, dark_map=merged)
+        _store_mask(warmup_state, next_mask, seq_len)
+        _ops.raise_on_status(query.device)          # one synchronising health check per refresh
+    else:
+        output = AttentionSparseEngine(query, key, value, warmup_state['mask'], pre_defined_mask=pre_defined_mask,
+                                       video_token_num=video_token_num, block_size=block_size,
+                                       _lists=_lists_for(warmup_state, seq_len))
+    return output, {'mask': warmup_state['mask']}
+
+
+def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx):
+    """Variant with the mean-pooled map producer: the mask is re-predicted on every step from the pooled map
+    of that step, so no dense pass is needed after the first feature-collection step."""
+    seq_len, num_heads = query.size(2), query.size(1)
+    warmup_steps = warmup_state['warmup_steps']
+    bs = warmup_state['block_size']
+    if current_step < warmup_steps - 2:
+        output, _ = dense_attention_with_lse(query, key, value, kv_len=_valid_kv(pre_defined_mask, seq_len))
+        return output, {'mode': 'warmup', 'mask': None}
+    dark = compute_pooled_map(query, key, warmup_state).squeeze(0)
+    n = dark.shape[-1]
+    mts, _ = _ops.mts(dark, warmup_state['blocks_per_frame'])
+    X = _ops.solve(mts, n, warmup_state['blocks_per_frame'], 1.0)
+    feats = features_from_solution(X, n)
+    history = warmup_state.get('features_history') or []
+    if current_step == warmup_steps - 2 or not history:
+        warmup_state['features_history'] = [feats]
+        warmup_state['current_steps'] = current_step + 1
+        warmup_state['prev_full_maps'] = dark
+        output, _ = dense_attention_with_lse(query, key, value, kv_len=_valid_kv(pre_defined_mask, seq_len))
+        return output, {'mode': 'warmup', 'mask': None}
+    history.append(feats)
+    if len(history) > 2:
+        history.pop(0)
+    warmup_state['features_history'] = history
+    warmup_state['current_steps'] = current_step + 1
+    warmup_state['prev_full_maps'] = dark
+    warmup_state['mode'] = _ops.head_modes(feats['b_d'], 1.0)     # device-side modes: no host sync per step
+    mask = _select_and_build(warmup_state, num_heads, seq_len, query.device, dark_map=dark)
+    _store_mask(warmup_state, mask, seq_len)
+    output = AttentionSparseEngine(query, key, value, mask, pre_defined_mask=pre_defined_mask,
+                                   video_token_num=warmup_state.get('video_token_num', 0), block_size=bs,
+                                   _lists=warmup_state['_tile_lists'][1])
+    return output, {'mask': mask}

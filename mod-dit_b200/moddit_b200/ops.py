@@ -17,6 +17,54 @@ from ._lib import check, lib
 
 _DTYPE = {torch.bfloat16: _lib.MODDIT_BF16, torch.float16: _lib.MODDIT_FP16}
 
+# ---------------------------------------------------------------------------------------------
+# optional per-entry-point timing (CUDA events on the launching stream); off by default
+# ---------------------------------------------------------------------------------------------
+_TIMING = {"on": False, "records": [], "launches": 0}
+# kernels launched by one call of each entry point (for launch accounting in benchmarks)
+KERNELS_PER_CALL = {"moddit_pool_blocks": 1, "moddit_pooled_map": 1, "moddit_replay_map": 1, "moddit_mts": 2,
+                    "moddit_mtm": 1, "moddit_solve": 3, "moddit_select_lines": 1, "moddit_head_modes": 1,
+                    "moddit_mask_from_lines": 1, "moddit_select_mass": 1, "moddit_tile_lists": 1,
+                    "moddit_sparse_attn_fwd": 1, "moddit_replay_status": 0}
+
+
+def stage_timing(enable: bool) -> None:
+    """Turn event timing of every entry-point call on or off and clear the records."""
+    _TIMING["on"] = bool(enable)
+    _TIMING["records"] = []
+    _TIMING["launches"] = 0
+
+
+def stage_records():
+    """[(entry point, milliseconds)] since the last `stage_timing(True)`; synchronises the device."""
+    torch.cuda.synchronize()
+    return [(name, a.elapsed_time(b)) for name, a, b in _TIMING["records"]]
+
+
+def launches_recorded() -> int:
+    return _TIMING["launches"]
+
+
+class _timed:
+    __slots__ = ("name", "dev", "start")
+
+    def __init__(self, name, dev):
+        self.name, self.dev = name, dev
+
+    def __enter__(self):
+        if _TIMING["on"]:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record(torch.cuda.current_stream(self.dev))
+        return self
+
+    def __exit__(self, *exc):
+        if _TIMING["on"]:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record(torch.cuda.current_stream(self.dev))
+            _TIMING["records"].append((self.name, self.start, end))
+            _TIMING["launches"] += KERNELS_PER_CALL.get(self.name, 1)
+        return False
+
 
 def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
@@ -59,7 +107,7 @@ def pool_blocks(x: torch.Tensor, block_size: int) -> torch.Tensor:
     B, H, N, D = x.shape
     nb = (N + block_size - 1) // block_size
     out = torch.empty(B, H, nb, D, device=dev, dtype=torch.float32)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_pool_blocks", dev):
         check(lib.moddit_pool_blocks(_ptr(x), _qkv_dtype(x), B * H, N, D, block_size, _ptr(out), _stream(dev)),
               "moddit_pool_blocks")
     return out
@@ -74,7 +122,7 @@ def pooled_map(qbar: torch.Tensor, kbar: torch.Tensor, *, q_block_offset: int, k
         raise ValueError("qbar and kbar must be float32 tensors of the same shape")
     B, H, nb, D = qbar.shape
     out = torch.empty(B, H, video_blocks, video_blocks, device=dev, dtype=torch.float16)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_pooled_map", dev):
         check(lib.moddit_pooled_map(_ptr(qbar), _ptr(kbar), B * H, nb, D, q_block_offset, k_block_offset,
                                     video_blocks, float(scale), _ptr(out), _stream(dev)), "moddit_pooled_map")
     return out
@@ -104,7 +152,7 @@ def replay_map(q: torch.Tensor, k: torch.Tensor, lse: torch.Tensor, *, softmax_s
         raise RuntimeError("LSE must be float32")
     B, H, N, D = q.shape
     out = torch.empty(B, H, video_blocks, video_blocks, device=dev, dtype=torch.float16)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_replay_map", dev):
         rc = lib.moddit_replay_map(_ptr(q), _ptr(k), _ptr(lse), _DTYPE[q.dtype], B * H, N, D, block_size,
                                    float(softmax_scale), float(log_threshold), int(q_video_offset),
                                    int(k_video_offset), int(video_blocks), _ptr(out), _stream(dev))
@@ -115,7 +163,7 @@ def replay_map(q: torch.Tensor, k: torch.Tensor, lse: torch.Tensor, *, softmax_s
 
 def replay_status(device: torch.device) -> Tuple[int, int, int, int]:
     host = (ctypes.c_int32 * 4)()
-    with torch.cuda.device(device):
+    with torch.cuda.device(device), _timed("moddit_replay_status", device):
         check(lib.moddit_replay_status(host, _stream(device)), "moddit_replay_status")
     return tuple(int(x) for x in host)
 
@@ -148,7 +196,7 @@ def mts(S_T: torch.Tensor, blocks_per_frame: int, *, prev: Optional[torch.Tensor
     wsb = lib.moddit_mts_workspace_bytes(H, n)
     ws = torch.empty(wsb, device=dev, dtype=torch.uint8)
     out = torch.empty(H, 3 * n, device=dev, dtype=torch.float32)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_mts", dev):
         check(lib.moddit_mts(_ptr(S_T), _ptr(prev), _ptr(keep_mask), hs, rs, mask_off, _ptr(merged), H, n,
                              blocks_per_frame, _ptr(out), _ptr(ws), wsb, _stream(dev)), "moddit_mts")
     return out, merged
@@ -157,7 +205,7 @@ def mts(S_T: torch.Tensor, blocks_per_frame: int, *, prev: Optional[torch.Tensor
 def mtm(n: int, blocks_per_frame: int, regularization: float, device) -> torch.Tensor:
     device = torch.device(device)
     out = torch.empty(3 * n, 3 * n, device=device, dtype=torch.float32)
-    with torch.cuda.device(device):
+    with torch.cuda.device(device), _timed("moddit_mtm", device):
         check(lib.moddit_mtm(n, blocks_per_frame, float(regularization), _ptr(out), _stream(device)), "moddit_mtm")
     return out
 
@@ -182,7 +230,7 @@ def solve_factor(n: int, blocks_per_frame: int, regularization: float, device) -
         wb = lib.moddit_solve_prepare_workspace_bytes(n)
         fac = torch.empty(fb, device=device, dtype=torch.uint8)
         ws = torch.empty(wb, device=device, dtype=torch.uint8)
-        with torch.cuda.device(device):
+        with torch.cuda.device(device), _timed("moddit_solve_prepare", device):
             check(lib.moddit_solve_prepare(n, blocks_per_frame, float(regularization), _ptr(fac), _ptr(ws), wb,
                                            _stream(device)), "moddit_solve_prepare")
         # other streams may use the factor later: make it globally visible once
@@ -201,7 +249,7 @@ def solve(mts_: torch.Tensor, n: int, blocks_per_frame: int, regularization: flo
     wb = lib.moddit_solve_workspace_bytes(H, n)
     ws = torch.empty(wb, device=dev, dtype=torch.uint8)
     X = torch.empty(H, 3 * n, device=dev, dtype=torch.float32)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_solve", dev):
         check(lib.moddit_solve(_ptr(mts_), _ptr(fac), H, n, blocks_per_frame, float(regularization), _ptr(X),
                                _ptr(ws), wb, _stream(dev)), "moddit_solve")
     return X
@@ -219,7 +267,7 @@ def select_lines(cur_c, cur_d, last_c, last_d, top_k: int, predict_T: float) -> 
         raise ValueError("feature shapes must be c:(H,n) d:(H,2n-1)")
     k = min(int(top_k), 3 * n - 1)
     out = torch.empty(H, k, device=dev, dtype=torch.int64)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_select_lines", dev):
         check(lib.moddit_select_lines(_ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]), _ptr(ts[3]), H, n, int(top_k),
                                       float(predict_T), _ptr(out), _stream(dev)), "moddit_select_lines")
     return out
@@ -229,7 +277,7 @@ def head_modes(b_d: torch.Tensor, threshold: float = 1.0) -> torch.Tensor:
     dev = _need_cuda(b_d)
     b_d = b_d.to(torch.float32).contiguous()
     out = torch.empty(b_d.shape[0], device=dev, dtype=torch.int32)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_head_modes", dev):
         check(lib.moddit_head_modes(_ptr(b_d), b_d.shape[0], float(threshold), _ptr(out), _stream(dev)),
               "moddit_head_modes")
     return out
@@ -245,7 +293,7 @@ def mask_from_lines(selected: torch.Tensor, modes: torch.Tensor, *, n: int, bloc
     H, k = selected.shape
     nbt = n if model_type == "wan" else total_blocks
     mask = torch.empty(H, nbt, nbt, device=dev, dtype=torch.bool)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_mask_from_lines", dev):
         check(lib.moddit_mask_from_lines(_ptr(selected), k, _ptr(modes), H, n, blocks_per_frame,
                                          _lib.LAYOUT[model_type], text_blocks, nbt, _ptr(mask), _stream(dev)),
               "moddit_mask_from_lines")
@@ -257,7 +305,7 @@ def select_mass(dark_map: torch.Tensor, tau: float) -> torch.Tensor:
     dark_map = dark_map.to(torch.float16).contiguous()
     H, n, _ = dark_map.shape
     keep = torch.empty(H, n, n, device=dev, dtype=torch.bool)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_select_mass", dev):
         check(lib.moddit_select_mass(_ptr(dark_map), H, n, float(tau), _ptr(keep), _stream(dev)),
               "moddit_select_mass")
     return keep
@@ -275,7 +323,7 @@ def tile_lists(mask: torch.Tensor, block_size: int, n_tokens: int, kv_block_limi
     counts = torch.empty(Hm, npairs, device=dev, dtype=torch.int32)
     entries = torch.empty(Hm, npairs, ntq, device=dev, dtype=torch.int32)
     lim = nbk if kv_block_limit is None else int(kv_block_limit)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_tile_lists", dev):
         check(lib.moddit_tile_lists(_ptr(mask), Hm, nbq, nbk, block_size, n_tokens, lim, _ptr(counts),
                                     _ptr(entries), _stream(dev)), "moddit_tile_lists")
     return counts, entries
@@ -330,7 +378,7 @@ def sparse_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, counts: t
         out = torch.empty_like(q)
     lse = torch.empty(B, H, N, device=dev, dtype=torch.float32) if return_lse else None
     st = _status_words(dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _timed("moddit_sparse_attn_fwd", dev):
         check(lib.moddit_sparse_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _qkv_dtype(q), B * H, N, D, _ptr(counts),
                                          _ptr(entries), Hm, scale, N if q_split is None else int(q_split),
                                          N if kv_len_lo is None else int(kv_len_lo),

@@ -1,0 +1,226 @@
+"""GPU tests of the drop-in `MoD.mod` API: validation, public map API, and the step-indexed state machine."""
+import logging
+import math
+import os
+
+import pytest
+import torch
+
+from oracle import moddit_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+LOG = logging.getLogger("moddit-test")
+
+
+@pytest.fixture(scope="module")
+def mod():
+    import MoD.mod.attn_mask as am
+    import MoD.mod.cuda_flash_sparsity as cf
+    import MoD.mod.cuda_lstsq as ls
+    import MoD.mod.state as st
+    import MoD.mod.triton_flash_sparsity as tf
+    return dict(am=am, cf=cf, ls=ls, st=st, tf=tf)
+
+
+def _layout(model_type, block_size):
+    if model_type == "wan":
+        return block_size * 2, block_size * 2, 0
+    return block_size * 3, block_size * 2, block_size
+
+
+@pytest.mark.parametrize("model_type", ["hunyuan", "cogvideox", "wan"])
+@pytest.mark.parametrize("block_size", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_public_api_matches_probability_reference(mod, monkeypatch, model_type, block_size, dtype):
+    torch.manual_seed(11)
+    monkeypatch.setenv("MOD_DIT_SPARSITY_BACKEND", "triton")
+    S, video, text = _layout(model_type, block_size)
+    q = torch.randn(1, 2, S, 64, device="cuda", dtype=dtype)
+    k, v = torch.randn_like(q), torch.randn_like(q)
+    out, sp = mod["tf"].flash_attn_with_sparsity_map(
+        q, k, v, 1e-3, block_size, model_type=model_type,
+        video_token_num=video if model_type != "wan" else 0, text_token_num=text)
+    ref_out, ref_map = orc.attn_with_sparsity_map_probs(
+        q.cpu(), k.cpu(), v.cpu(), threshold=1e-3, block_size=block_size, model_type=model_type,
+        video_token_num=video if model_type != "wan" else 0, text_token_num=text)
+    assert out.shape == q.shape and sp.shape == ref_map.shape and sp.dtype == torch.float16
+    # the reference's own bound for this comparison: 8.1 elements per block
+    assert ((sp.cpu().float() - ref_map.float()).abs() * block_size ** 2).max().item() <= 8.1
+    assert (out.float().cpu() - ref_out).abs().max().item() < 2e-2
+
+
+def test_non_positive_threshold_produces_zero_map(mod):
+    q = torch.randn(1, 1, 128, 64, device="cuda", dtype=torch.float16)
+    out, sp = mod["tf"].flash_attn_with_sparsity_map(q, q, q, 0.0, 64, model_type="wan")
+    assert out.shape == q.shape and torch.count_nonzero(sp).item() == 0
+
+
+def test_backend_env_is_validated(mod, monkeypatch):
+    q = torch.randn(1, 1, 128, 64, device="cuda", dtype=torch.float16)
+    lse, scale = orc.replay_lse(q.cpu(), q.cpu())
+    kw = dict(softmax_scale=scale, log_threshold=math.log(1e-3), q_video_offset=0, k_video_offset=0,
+              video_blocks=2, block_size=64)
+    for name in ("triton", "cuda", "auto"):
+        monkeypatch.setenv("MOD_DIT_SPARSITY_BACKEND", name)
+        assert mod["tf"]._compute_sparsity_map(q, q, lse.cuda(), **kw).shape == (1, 1, 2, 2)
+    monkeypatch.setenv("MOD_DIT_SPARSITY_BACKEND", "invalid")
+    with pytest.raises(ValueError, match="MOD_DIT_SPARSITY_BACKEND"):
+        mod["tf"]._compute_sparsity_map(q, q, lse.cuda(), **kw)
+    assert mod["cf"].cuda_backend_supported() and mod["cf"].extension_error() is None
+
+
+@pytest.mark.parametrize("mutation,error_type,match", [
+    ({"block_size": 32}, ValueError, "block_size"),
+    ({"video_token_num": 65}, ValueError, "divisible"),
+    ({"model_type": "unknown"}, ValueError, "Unknown model_type"),
+    ({"threshold": float("nan")}, ValueError, "NaN"),
+])
+def test_input_validation(mod, mutation, error_type, match):
+    q = torch.empty(1, 1, 128, 64, device="cuda", dtype=torch.float16)
+    args = dict(query=q, key=q, value=q, threshold=1e-3, block_size=64, model_type="hunyuan",
+                video_token_num=64, text_token_num=64)
+    args.update(mutation)
+    with pytest.raises(error_type, match=match):
+        mod["tf"]._validate_inputs(**args)
+
+
+def test_state_keys_match_reference(mod, golden_dir):
+    state = mod["st"].create_adaptive_mask_state("hunyuan", 24, 115200, 256, 3840, 30)
+    ref = [ln.split("=", 1) for ln in open(os.path.join(golden_dir, "state_keys.txt")).read().splitlines()]
+    assert list(state.keys()) == [k for k, _ in ref]
+    for k_, v_ in ref:
+        assert repr(state[k_]) == v_
+    with pytest.raises(ValueError, match="not support"):
+        mod["st"].create_adaptive_mask_state("hunyuan", 24, 115200, 256, 3840, 30, sparse_type="bogus")
+
+
+def _locality(seed, H, T, Hh, Ww, D, text, text_first, gain=2.0):
+    from tests.golden.make_golden import locality_inputs
+    q, k, v = locality_inputs(seed, H=H, T=T, Hh=Hh, Ww=Ww, D=D, gain=gain, text=text, text_first=text_first)
+    return q.bfloat16(), k.bfloat16(), v.bfloat16()
+
+
+@pytest.mark.parametrize("model_type,bs,text", [("hunyuan", 64, 128), ("cogvideox", 64, 128), ("wan", 128, 0),
+                                                ("hunyuan", 128, 256)])
+def test_state_machine_against_oracle(mod, model_type, bs, text):
+    am, st = mod["am"], mod["st"]
+    H, T, Hh, Ww, D = 2, 4, 16, 16, 64
+    video = T * Hh * Ww                      # 1024 tokens, 256 per frame
+    q0, k0, v0 = _locality(50, H, T, Hh, Ww, D, text, model_type == "cogvideox")
+    S = video + text
+    bpf = (Hh * Ww) // bs
+    top_k, pT, warm = 6, 3, 4
+    state = st.create_adaptive_mask_state(model_type, H, video, text, Hh * Ww, T, warmup_steps=warm, top_k=top_k,
+                                          predict_T=pT, threshold=1e-3, block_size=bs)
+    pdm = None
+    valid = S
+    if model_type == "hunyuan":
+        valid = video + text - 37
+        pdm = (torch.arange(S) < valid).unsqueeze(0).expand(S, S).contiguous().cuda()
+    n = video // bs
+    hist = []
+    prev_map = None
+    ref_mask = None
+    for step in range(warm - 2, warm + 2 * pT):
+        g = torch.Generator().manual_seed(1000 + step)
+        q = (q0 + 0.05 * torch.randn(q0.shape, generator=g).bfloat16())
+        k = (k0 + 0.05 * torch.randn(k0.shape, generator=g).bfloat16())
+        out, info = am.SparseAttentionWithMap(q.cuda(), k.cuda(), v0.cuda(), state, LOG, pre_defined_mask=pdm,
+                                              current_step=step)
+        assert out.shape == q.shape
+        refresh = step >= warm and (step - warm) % pT == pT - 1
+        if step < warm or refresh:
+            # dense output (all keys, as the reference's refresh pass does)
+            ref = orc.masked_attention(q, k, v0, torch.ones(1, (S + bs - 1) // bs, (S + bs - 1) // bs, dtype=torch.bool), bs)
+            assert (out.float().cpu() - ref).abs().max().item() < 2e-2
+            cur_map = state["prev_full_maps"].cpu()
+            if step >= warm:
+                vm = ref_mask if model_type == "wan" else (
+                    ref_mask[:, :n, :n] if model_type == "hunyuan" else ref_mask[:, text // bs:, text // bs:])
+                # merged = where(mask, current, previous): where the mask was off, history must be unchanged
+                assert torch.equal(cur_map[~vm], prev_map[~vm])
+            prev_map = cur_map
+            if step == warm - 2:
+                zeros = {"c": torch.zeros(H, n), "d": torch.zeros(H, 2 * n - 1), "b_d": torch.zeros(H)}
+                hist = [zeros]
+            else:
+                f = orc.solve_features(orc.compute_mts(cur_map, bpf), n, bpf, 1.0)
+                hist.append({k_: f[k_] for k_ in ("c", "d", "b_d")})
+                hist = hist[-2:]
+                gpu_f = state["features_history"][-1]
+                for k_ in ("c", "d", "b_d"):
+                    assert torch.allclose(gpu_f[k_].cpu(), hist[-1][k_], atol=5e-4, rtol=1e-3)
+                if step == warm - 1:
+                    modes = orc.check_bd_values(hist[-1]["b_d"], 1.0)
+                    assert state["mode"] == modes
+                # bit-exact mask given identical selection inputs (the GPU's own features)
+                gh = [{k_: v_.cpu() for k_, v_ in f_.items()} for f_ in state["features_history"][-2:]]
+                lines = orc.choose_topk_lines(gh[0], gh[1], top_k, pT)
+                ref_mask = orc.generate_mask_from_lines(
+                    model_type=model_type, block_size=bs, video_token_num=video, text_token_num=text, seq_len=S,
+                    blocks_per_frame=bpf, selected_lines=lines, mode=state["mode"])
+                assert torch.equal(state["mask"].cpu(), ref_mask)
+                # end to end (oracle features from the same map): at least 99.9 % of blocks agree
+                lines2 = orc.choose_topk_lines(hist[0], hist[1], top_k, pT)
+                mask2 = orc.generate_mask_from_lines(
+                    model_type=model_type, block_size=bs, video_token_num=video, text_token_num=text, seq_len=S,
+                    blocks_per_frame=bpf, selected_lines=lines2, mode=state["mode"])
+                assert (mask2 == ref_mask).float().mean().item() >= 0.999
+        else:
+            kw = {}
+            if pdm is not None:
+                kw = dict(q_split=video, kv_len_lo=min(S, (valid + 63) // 64 * 64), kv_len_hi=valid)
+            ref = orc.masked_attention(q, k, v0, ref_mask, bs, **kw)
+            err = (out.float().cpu() - ref).abs()
+            assert err.max().item() <= 2e-2
+            assert ((out.float().cpu() - ref).norm() / ref.norm()).item() <= 1e-2
+    from moddit_b200 import ops
+    ops.raise_on_status(torch.device("cuda"))
+
+
+def test_pooled_producer_and_mass_selector(mod):
+    am, st = mod["am"], mod["st"]
+    H, T, Hh, Ww, D, bs = 2, 4, 16, 16, 128, 128
+    video = T * Hh * Ww
+    q0, k0, v0 = _locality(60, H, T, Hh, Ww, D, 0, False)
+    n, bpf = video // bs, (Hh * Ww) // bs
+    for selector in ("topk_lines", "cumulative_mass"):
+        state = st.create_adaptive_mask_state("wan", H, video, 0, Hh * Ww, T, warmup_steps=2, top_k=5, predict_T=4,
+                                              block_size=bs)
+        state["score_producer"] = "pooled"
+        state["selector"] = selector
+        state["mass_threshold"] = 0.9
+        for step in range(0, 4):
+            out, info = am.SparseAttentionWithMap(q0.cuda(), k0.cuda(), v0.cuda(), state, LOG, current_step=step)
+            dark = orc.pooled_darkness_map(orc.pool_blocks(q0, bs), orc.pool_blocks(k0, bs), q_block_offset=0,
+                                           k_block_offset=0, video_blocks=n, scale=D ** -0.5)[0]
+            assert (state["prev_full_maps"].cpu().float() - dark.float()).abs().max().item() <= 2e-3
+            if step == 0:
+                ref = orc.masked_attention(q0, k0, v0, torch.ones(1, n, n, dtype=torch.bool), bs)
+            else:
+                gpu_dark = state["prev_full_maps"].cpu()
+                if selector == "cumulative_mass":
+                    ref_mask = orc.select_mass(gpu_dark, 0.9)
+                else:
+                    gh = [{k_: v_.cpu() for k_, v_ in f_.items()} for f_ in state["features_history"][-2:]]
+                    lines = orc.choose_topk_lines(gh[0], gh[1], 5, 4)
+                    modes = orc.check_bd_values(gh[1]["b_d"], 1.0)
+                    ref_mask = orc.generate_mask_from_lines(
+                        model_type="wan", block_size=bs, video_token_num=video, text_token_num=0, seq_len=video,
+                        blocks_per_frame=bpf, selected_lines=lines, mode=modes)
+                assert torch.equal(state["mask"].cpu(), ref_mask)
+                ref = orc.masked_attention(q0, k0, v0, ref_mask, bs)
+            assert (out.float().cpu() - ref).abs().max().item() <= 2e-2
+
+
+def test_use_dense_and_unsupported_types(mod):
+    am, st = mod["am"], mod["st"]
+    q = torch.randn(1, 2, 512, 64, device="cuda", dtype=torch.bfloat16)
+    state = st.create_adaptive_mask_state("wan", 2, 512, 0, 128, 4, block_size=64)
+    out, info = am.SparseAttentionWithMap(q, q, q, state, LOG, use_dense=True, use_cuda=True)
+    ref = orc.masked_attention(q.cpu(), q.cpu(), q.cpu(), torch.ones(1, 8, 8, dtype=torch.bool), 64)
+    assert (out.float().cpu() - ref).abs().max().item() <= 2e-2 and info["mask"] is None
+    state["sparse_type"] = "radial"
+    with pytest.raises(NotImplementedError):
+        am.SparseAttentionWithMap(q, q, q, state, LOG, current_step=0)
