@@ -102,6 +102,24 @@ int moddit_mts(const void* map_f16, const void* prev_f16, const uint8_t* keep_ma
                int H, int n, int blocks_per_frame, float* mts, void* workspace, size_t workspace_bytes,
                void* stream);
 
+/* moddit_mts for callers that cannot hand over a workspace and cannot allocate one.  (No counterpart in
+ * the reference.)  Such callers exist: a plug-in run by a host that gives it nothing but input and output
+ * buffers and forbids device allocation inside the call, or a process whose framework has already
+ * reserved all device memory for its own pool, so that a cudaMalloc from a library would fail.
+ * The scratch for the per-tile partial sums is an 8 MiB array built into the library's device image
+ * (moddit_mts_noalloc_max_bytes()); every GPU that loads the library holds it until the process exits.
+ *   - no history merge: map (H, n, n) float16 in, mts (H, 3n) float32 out, same values as moddit_mts;
+ *   - sizes whose scratch need, moddit_mts_workspace_bytes(H, n), exceeds the array are refused with
+ *     MODDIT_E_UNSUPPORTED (HunyuanVideo's H=24, n=900 needs 5.1 MB and fits);
+ *   - the call allocates and frees nothing.  The first call on each device looks up the array's device
+ *     address (cudaGetSymbolAddress); make that first call outside any stream capture;
+ *   - all calls on a device share the one array and it keeps the last call's contents.  Nothing in it
+ *     has to start at zero (each call overwrites what it later reads), but two calls whose kernels can
+ *     overlap on the GPU (different streams without an ordering between them) race on it.
+ */
+size_t moddit_mts_noalloc_max_bytes(void);
+int moddit_mts_noalloc(const void* map_f16, int H, int n, int blocks_per_frame, float* mts, void* stream);
+
 /* Structural Gram matrix M^T M + reg*I, (3n x 3n) float32.  Replaces `compute_mtm(S_T, bpf, reg)` of
  * MoD/mod/cuda_lstsq_kernel.cu:319-418 and `compute_mtm_pytorch` (MoD/mod/cuda_lstsq.py:42-89). */
 int moddit_mtm(int n, int blocks_per_frame, float regularization, float* mtm, void* stream);

@@ -14,6 +14,8 @@
 //            two scans, one (n+1)^2 matrix-vector product per head and an elementwise back-substitution.
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace moddit {
@@ -426,6 +428,62 @@ extern "C" int moddit_mts(const void* map_f16, const void* prev_f16, const uint8
   mts_partial_kernel<<<dim3(tiles, H), kMtsThreads, smem, st>>>(
       static_cast<const __half*>(map_f16), static_cast<const __half*>(prev_f16), keep_mask, mask_head_stride,
       mask_row_stride, mask_off, static_cast<__half*>(merged_out_f16), n, blocks_per_frame, part_f, part_blk);
+  MODDIT_CHECK_LAUNCH("mts_partial_kernel");
+  mts_finish_kernel<<<dim3(ceil_div(3 * n, 256), H), 256, 0, st>>>(part_f, part_blk, n, tiles, mts);
+  MODDIT_CHECK_LAUNCH("mts_finish_kernel");
+  return MODDIT_OK;
+}
+
+// ---- variant of moddit_mts whose scratch lives in a static device array ----------------------------
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;   // 8 MiB per device that loads the library
+static __device__ __align__(256) unsigned char g_mts_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle for the runtime's symbol table, not a device address;
+// the address the kernels need is looked up once per device (with that device current) and kept here.
+static std::mutex g_static_scratch_mutex;
+static void* g_static_scratch_addr[64] = {};
+
+extern "C" size_t moddit_mts_noalloc_max_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int moddit_mts_noalloc(const void* map_f16, int H, int n, int blocks_per_frame, float* mts, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(map_f16 && mts, "mts_noalloc: null pointer");
+  MODDIT_CHECK_ARG(H > 0 && H <= 65535, "mts_noalloc: H=%d outside [1, 65535]", H);
+  if (int rc = check_n("mts_noalloc", n)) return rc;
+  MODDIT_CHECK_ARG(blocks_per_frame > 0, "mts_noalloc: blocks_per_frame=%d must be positive", blocks_per_frame);
+  const size_t need = moddit_mts_workspace_bytes(H, n);
+  if (need > kStaticScratchBytes)
+    return fail(MODDIT_E_UNSUPPORTED,
+                "mts_noalloc: H=%d, n=%d needs %zu bytes of scratch but the built-in array holds %zu; use moddit_mts "
+                "with a caller-provided workspace",
+                H, n, need, kStaticScratchBytes);
+  const size_t smem = static_cast<size_t>(kTileRows) * n * sizeof(__half);
+  if (smem > 200 * 1024) return fail(MODDIT_E_UNSUPPORTED, "mts_noalloc: n=%d rows do not fit shared memory", n);
+  if (int rc = require_sm100()) return rc;
+  int dev = 0;
+  MODDIT_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(MODDIT_E_UNSUPPORTED, "mts_noalloc: device index %d not supported", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> guard(g_static_scratch_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+      void* addr = nullptr;
+      MODDIT_CHECK_CUDA(cudaGetSymbolAddress(&addr, g_mts_static_scratch));
+      g_static_scratch_addr[dev] = addr;
+    }
+    scratch = g_static_scratch_addr[dev];
+  }
+  const int tiles = ceil_div(n, kTileRows);
+  const size_t f = static_cast<size_t>(H) * tiles * (2 * static_cast<size_t>(n) + kTileRows - 1) * sizeof(float);
+  float* part_f = static_cast<float*>(scratch);
+  double* part_blk = reinterpret_cast<double*>(static_cast<unsigned char*>(scratch) + (f + 15) / 16 * 16);
+  cudaStream_t st = as_stream(stream);
+  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(mts_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)));
+  // every partial that the second kernel reads is written by the first, so nothing has to start at zero
+  mts_partial_kernel<<<dim3(tiles, H), kMtsThreads, smem, st>>>(static_cast<const __half*>(map_f16), nullptr, nullptr,
+                                                                 0, 0, 0, nullptr, n, blocks_per_frame, part_f,
+                                                                 part_blk);
   MODDIT_CHECK_LAUNCH("mts_partial_kernel");
   mts_finish_kernel<<<dim3(ceil_div(3 * n, 256), H), 256, 0, st>>>(part_f, part_blk, n, tiles, mts);
   MODDIT_CHECK_LAUNCH("mts_finish_kernel");

@@ -25,7 +25,8 @@ _TIMING = {"on": False, "records": [], "launches": 0}
 KERNELS_PER_CALL = {"moddit_pool_blocks": 1, "moddit_pooled_map": 1, "moddit_replay_map": 1, "moddit_mts": 2,
                     "moddit_mtm": 1, "moddit_solve": 3, "moddit_select_lines": 1, "moddit_head_modes": 1,
                     "moddit_mask_from_lines": 1, "moddit_select_mass": 1, "moddit_tile_lists": 1,
-                    "moddit_sparse_attn_fwd": 1, "moddit_replay_status": 0}
+                    "moddit_sparse_attn_fwd": 1, "moddit_replay_status": 0,
+                    "moddit_mts_noalloc": 2}
 
 
 def stage_timing(enable: bool) -> None:
@@ -200,6 +201,27 @@ def mts(S_T: torch.Tensor, blocks_per_frame: int, *, prev: Optional[torch.Tensor
         check(lib.moddit_mts(_ptr(S_T), _ptr(prev), _ptr(keep_mask), hs, rs, mask_off, _ptr(merged), H, n,
                              blocks_per_frame, _ptr(out), _ptr(ws), wsb, _stream(dev)), "moddit_mts")
     return out, merged
+
+
+def mts_noalloc(S_T: torch.Tensor, blocks_per_frame: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """M^T S through the entry point that allocates nothing: its scratch is an array built into the library.
+
+    For callers that may not allocate device memory inside the call (pass a preallocated `out`); sizes are
+    limited by `lib.moddit_mts_noalloc_max_bytes()`.  Calls on one device share the scratch, so calls that
+    could overlap on the GPU must be ordered by the caller.
+    """
+    dev = _need_cuda(S_T)
+    if S_T.dtype != torch.float16 or not S_T.is_contiguous():
+        raise ValueError("mts_noalloc takes a contiguous float16 (H, n, n) map (converting would allocate)")
+    H, n, _ = S_T.shape
+    if out is None:
+        out = torch.empty(H, 3 * n, device=dev, dtype=torch.float32)
+    elif out.dtype != torch.float32 or tuple(out.shape) != (H, 3 * n) or not out.is_contiguous() or out.device != dev:
+        raise ValueError("out must be a contiguous float32 (H, 3n) tensor on the map's device")
+    with torch.cuda.device(dev), _timed("moddit_mts_noalloc", dev):
+        check(lib.moddit_mts_noalloc(_ptr(S_T), H, n, blocks_per_frame, _ptr(out), _stream(dev)),
+              "moddit_mts_noalloc")
+    return out
 
 
 def mtm(n: int, blocks_per_frame: int, regularization: float, device) -> torch.Tensor:
