@@ -209,27 +209,29 @@ def run_ours(args):
 
     # ---- e2e: inputs in pinned host memory, output copied back ----------------------------------
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    host_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in (q_in, k_in, v_in)]
-    host_out = torch.empty(q_in.shape, dtype=q_in.dtype, pin_memory=True)
-    dev_in = [torch.empty_like(t) for t in (q_in, k_in, v_in)]
-    h2d = sum(t.numel() * t.element_size() for t in host_in)
-    d2h = host_out.numel() * host_out.element_size()
+    e2e_ms, h2d, d2h = 0.0, 0, 0
+    if not args.no_e2e:
+        host_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in (q_in, k_in, v_in)]
+        host_out = torch.empty(q_in.shape, dtype=q_in.dtype, pin_memory=True)
+        dev_in = [torch.empty_like(t) for t in (q_in, k_in, v_in)]
+        h2d = sum(t.numel() * t.element_size() for t in host_in)
+        d2h = host_out.numel() * host_out.element_size()
 
-    def e2e_step(step):
-        for d, h in zip(dev_in, host_in):
-            d.copy_(h, non_blocking=True)
-        out = layer(dev_in[0], dev_in[1], dev_in[2], step)
-        host_out.copy_(out, non_blocking=True)
+        def e2e_step(step):
+            for d, h in zip(dev_in, host_in):
+                d.copy_(h, non_blocking=True)
+            out = layer(dev_in[0], dev_in[1], dev_in[2], step)
+            host_out.copy_(out, non_blocking=True)
 
-    e2e_step(100)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(e2e_steps):
-        e2e_step(101 + i)
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+        e2e_step(100)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(e2e_steps):
+            e2e_step(101 + i)
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
 
     # ---- reduce over ranks ------------------------------------------------------------------------
     vals = torch.tensor([total_ms, e2e_ms, attn_ms, pred_ms], device=dev, dtype=torch.float64)
@@ -245,7 +247,7 @@ def run_ours(args):
         peaks = load_peaks()
         ms_per_step = total_ms / args.steps
         value = flops_total / (ms_per_step * 1e-3) / 1e12
-        e2e_value = flops_total / (e2e_ms / e2e_steps * 1e-3) / 1e12
+        e2e_value = flops_total / (e2e_ms / e2e_steps * 1e-3) / 1e12 if e2e_ms > 0 else None
         # roofline of the dominant kernel: kept flops of one launch on this rank / its average duration
         achieved = flops_local / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else 0.0
         peak = float(peaks["bf16_tflops"])
@@ -266,8 +268,9 @@ def run_ours(args):
             "attn_ms": round(attn_ms, 3),
             "stage_ms_per_step": {n: round(ms / args.steps, 4) for n, ms in sorted(stage_ms.items())},
             "clocks": clocks,
-            "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms / e2e_steps, 3),
-                    "steps": e2e_steps, "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total)},
+            "e2e": None if e2e_value is None else {
+                "value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms / e2e_steps, 3),
+                "steps": e2e_steps, "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total)},
             "gpu_launches": int(launches_total),
             "roofline": roof,
         }
@@ -382,7 +385,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", default="hunyuan")
@@ -391,6 +394,7 @@ def main():
     ap.add_argument("--cpu-blocks", type=int, default=48, help="query blocks in the cpu_baseline sample")
     ap.add_argument("--ref-blocks", type=int, default=8, help="query blocks per step of --impl reference")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -76,6 +76,8 @@ WORKLOADS = {
                 text_first=False, top_k=350, predict_T=10),
     "cogvideox": dict(model_type="cogvideox", heads=48, head_dim=64, block_size=64, grid=(11, 48, 84),
                       text_tokens=256, text_first=True, top_k=100, predict_T=5),
+    "medium": dict(model_type="hunyuan", heads=8, head_dim=128, block_size=128, grid=(8, 64, 64), text_tokens=256,
+                   text_first=False, top_k=80, predict_T=5),
     "small": dict(model_type="hunyuan", heads=4, head_dim=128, block_size=128, grid=(8, 32, 32), text_tokens=256,
                   text_first=False, top_k=30, predict_T=5),
 }
