@@ -124,6 +124,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
 
+  // Register budget: the softmax warpgroups hold a 128-value row per thread, the control warps need little.
+  // The control branch and the softmax branch are disjoint in the control-flow graph so that each gets
+  // its own register allocation.
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -230,7 +235,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
       }
       ptx::tc_commit(bar(kOFinal));
     }
-  } else if (warp >= 4) {
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ------------------------------------------------------------------ softmax + epilogue
     const int x = (warp - 4) / 4;                 // 0: tile A, 1: tile B
     const int wq = warp % 4;                      // tensor-memory lane quarter of this warp
@@ -274,9 +281,16 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
           v[c] = valid ? v[c] : -INFINITY;
         }
       }
-      float mx = v[0];
+      // row maximum with eight independent chains (a single chain of 128 dependent max ops is latency-bound)
+      float mxa[8];
 #pragma unroll
-      for (int c = 1; c < kTile; ++c) mx = fmaxf(mx, v[c]);
+      for (int a = 0; a < 8; ++a) mxa[a] = fmaxf(v[a], v[a + 8]);
+#pragma unroll
+      for (int c = 16; c < kTile; c += 16)
+#pragma unroll
+        for (int a = 0; a < 8; ++a) mxa[a] = fmaxf(mxa[a], fmaxf(v[c + a], v[c + a + 8]));
+      const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
+                             fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
       const float m_new = fmaxf(m, mx * scale_log2);
       if (done == 0) {
         m = m_new;
@@ -295,7 +309,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
         }
       }
       const float mm = (m == -INFINITY) ? 0.f : m;
-      float sum = 0.f;
+      float suma[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t pk[32];
@@ -303,12 +317,12 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
         for (int i = 0; i < 32; ++i) {
           const float p0 = ptx::ex2(fmaf(v[half * 64 + 2 * i], scale_log2, -mm));
           const float p1 = ptx::ex2(fmaf(v[half * 64 + 2 * i + 1], scale_log2, -mm));
-          sum += p0 + p1;
+          suma[i & 3] += p0 + p1;
           pk[i] = pack2<kBF16>(p0, p1);
         }
         ptx::tmem_st32(tS + half * 32, pk);
       }
-      l += sum;
+      l += (suma[0] + suma[1]) + (suma[2] + suma[3]);
       ptx::tmem_st_wait();
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(kPFullA + x));
