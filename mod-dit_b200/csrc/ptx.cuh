@@ -177,5 +177,43 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Packed fp32 pairs in one 64-bit register: one instruction does two lanes of work.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// 2^x on the FMA/ALU pipes (no MUFU): floor(x) goes to the exponent field, a cubic approximates 2^frac
+// (relative error below 1e-4, far under the 16-bit rounding of the probabilities that use it).
+// Valid for x <= 127; inputs below -127 (including -inf) give a denormal, i.e. effectively zero.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -127.f);
+  float t;
+  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(x), "f"(12582912.f));   // 1.5 * 2^23: integer part lands in the low bits
+  const float n = t - 12582912.f;
+  const float f = x - n;   // [0, 1)
+  const float p = fmaf(fmaf(fmaf(0.077119f, f, 0.227564f), f, 0.695146f), f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 }  // namespace ptx
 }  // namespace moddit

@@ -15,15 +15,16 @@ __device__ __forceinline__ uint32_t order_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-constexpr int kSelectThreads = 1024;
+constexpr int kSelectThreads = 256;
 
-// One CTA per head.  keys[] in shared memory; the rank of element i is the number of elements that
-// sort before it under (key, index); ranks < k are written to selected[h][rank].
+// ceil(L / 256) CTAs per head.  Every CTA builds all keys[] in shared memory and ranks its own slice of
+// the elements: the rank of element i is the number of elements that sort before it under (key, index);
+// ranks < k are written to selected[h][rank].
 __global__ void __launch_bounds__(kSelectThreads) select_lines_kernel(
     const float* __restrict__ cur_c, const float* __restrict__ cur_d, const float* __restrict__ last_c,
     const float* __restrict__ last_d, int n, int k, float predict_T, int64_t* __restrict__ selected) {
   extern __shared__ uint32_t keys[];
-  const int h = blockIdx.x;
+  const int h = blockIdx.y;
   const int nd = 2 * n - 1;
   const int L = n + nd;
   for (int i = threadIdx.x; i < L; i += kSelectThreads) {
@@ -40,10 +41,16 @@ __global__ void __launch_bounds__(kSelectThreads) select_lines_kernel(
     keys[i] = order_key(pred);
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < L; i += kSelectThreads) {
+  for (int i = blockIdx.x * kSelectThreads + threadIdx.x; i < L; i += gridDim.x * kSelectThreads) {
     const uint32_t ki = keys[i];
     int rank = 0;
-    for (int j = 0; j < L; ++j) {
+    int j = 0;
+    for (; j + 3 < L; j += 4) {          // four independent compares per iteration
+      const uint32_t k0 = keys[j], k1 = keys[j + 1], k2 = keys[j + 2], k3 = keys[j + 3];
+      rank += ((k0 < ki) || (k0 == ki && j < i)) + ((k1 < ki) || (k1 == ki && j + 1 < i)) +
+              ((k2 < ki) || (k2 == ki && j + 2 < i)) + ((k3 < ki) || (k3 == ki && j + 3 < i));
+    }
+    for (; j < L; ++j) {
       const uint32_t kj = keys[j];
       rank += (kj < ki) || (kj == ki && j < i);
     }
@@ -236,7 +243,8 @@ extern "C" int moddit_select_lines(const float* cur_c, const float* cur_d, const
   if (int rc = require_sm100()) return rc;
   const int L = 3 * n - 1;
   const int k = top_k < L ? top_k : L;
-  select_lines_kernel<<<H, kSelectThreads, sizeof(uint32_t) * L, as_stream(stream)>>>(cur_c, cur_d, last_c, last_d, n,
+  const int split = ceil_div(L, kSelectThreads);     // one element per thread
+  select_lines_kernel<<<dim3(split, H), kSelectThreads, sizeof(uint32_t) * L, as_stream(stream)>>>(cur_c, cur_d, last_c, last_d, n,
                                                                                       k, predict_T, selected);
   MODDIT_CHECK_LAUNCH("select_lines_kernel");
   return MODDIT_OK;

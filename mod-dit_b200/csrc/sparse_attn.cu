@@ -38,7 +38,8 @@ enum BarrierIndex {
   kQFull = 0,
   kKFull0, kKFull1, kKEmpty0, kKEmpty1,
   kVFull0, kVFull1, kVEmpty0, kVEmpty1,
-  kSFullA, kSFullB, kPFullA, kPFullB,
+  kSFullA, kSFullB,
+  kPLoA, kPHiA, kPLoB, kPHiB,   // first / second half row of P stored, per query tile
   kOFinal,
   kNumBarriers
 };
@@ -62,6 +63,16 @@ __device__ __forceinline__ void report(int32_t* status, int code, int role, int 
     status[3] = where;
   }
 }
+
+#ifdef MODDIT_PROFILE
+// Experiment-only build: cycle totals per role, summed over all CTAs.
+__device__ unsigned long long g_prof[32];
+#define PROF_T() clock64()
+#define PROF_ADD(i, v) atomicAdd(&g_prof[i], static_cast<unsigned long long>(v))
+#else
+#define PROF_T() 0ll
+#define PROF_ADD(i, v) ((void)0)
+#endif
 
 template <bool kBF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -108,7 +119,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
   const int32_t* ent = entries + (static_cast<int64_t>(mh) * npairs + pair) * ntk;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kNumBarriers; ++i) ptx::mbar_init(bar(i), (i == kPFullA || i == kPFullB) ? 128u : 1u);
+    for (int i = 0; i < kNumBarriers; ++i) ptx::mbar_init(bar(i), (i >= kPLoA && i <= kPHiB) ? 128u : 1u);
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tm_q);
@@ -172,22 +183,49 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      // Descriptor bases are built once; inside the loops an MMA costs one 32-bit add per operand (the
+      // issuing thread shares its scheduler with two busy softmax warps, so every instruction counts).
+      const uint64_t dq[2] = {ptx::smem_desc_sw128(sQ, 16, 1024), ptx::smem_desc_sw128(sQ + kTileBytes, 16, 1024)};
+      const uint64_t dk[2] = {ptx::smem_desc_sw128(sK, 16, 1024), ptx::smem_desc_sw128(sK + kTileBytes, 16, 1024)};
+      const uint64_t dv[2] = {ptx::smem_desc_sw128(sV, kChunkBytes, 1024),
+                              ptx::smem_desc_sw128(sV + kTileBytes, kChunkBytes, 1024)};
+      auto advance = [](uint64_t desc, uint32_t bytes) -> uint64_t {
+        // the start-address field (bits 0-13, units of 16 bytes) never carries out for shared-memory addresses
+        return (desc & 0xffffffff00000000ull) | static_cast<uint32_t>(static_cast<uint32_t>(desc) + (bytes >> 4));
+      };
       auto issue_qk = [&](int x, int s) {
+        const uint64_t a0 = dq[x], b0 = dk[s];
+        const uint32_t d = tmem + x * 128;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          const uint64_t a = ptx::smem_desc_sw128(sQ + x * kTileBytes + off, 16, 1024);
-          const uint64_t b = ptx::smem_desc_sw128(sK + s * kTileBytes + off, 16, 1024);
-          ptx::mma_ss(tmem + x * 128, a, b, kIdescQK, kk > 0 ? 1u : 0u);
+          ptx::mma_ss(d, advance(a0, off), advance(b0, off), kIdescQK, kk > 0 ? 1u : 0u);
         }
         ptx::tc_commit(bar(kSFullA + x));
       };
-      auto issue_pv = [&](int x, int s, uint32_t acc) {
+      // P*V for one half of the key tile (keys [64*half, 64*half+64))
+      auto issue_pv_half = [&](int x, int s, int half, uint32_t acc) {
+        const uint64_t b0 = dv[s];
+        const uint32_t d = tmem + 256 + x * D, a = tmem + x * 128;
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          const uint64_t b = ptx::smem_desc_sw128(sV + s * kTileBytes + kk * 2048, kChunkBytes, 1024);
-          ptx::mma_ts(tmem + 256 + x * D, tmem + x * 128 + kk * 8, b, kIdescPV, (acc || kk > 0) ? 1u : 0u);
+        for (int kq = 0; kq < kTile / 32; ++kq) {
+          const int kk = half * (kTile / 32) + kq;
+          ptx::mma_ts(d, a + kk * 8, advance(b0, kk * 2048), kIdescPV, (acc || kq > 0) ? 1u : 0u);
         }
+      };
+      // waits for the two half rows of P in turn; returns false if a wait gave up
+      auto pv_when_ready = [&](int x, int s, uint32_t acc, uint32_t parity, long long& waited) -> bool {
+        long long t = PROF_T();
+        if (!ptx::mbar_wait(bar(kPLoA + 2 * x), parity, abort_flag)) return false;
+        waited += PROF_T() - t;
+        ptx::tc_fence_after();
+        issue_pv_half(x, s, 0, acc);
+        t = PROF_T();
+        if (!ptx::mbar_wait(bar(kPHiA + 2 * x), parity, abort_flag)) return false;
+        waited += PROF_T() - t;
+        ptx::tc_fence_after();
+        issue_pv_half(x, s, 1, 1u);
+        return true;
       };
       bool ok = ptx::mbar_wait(bar(kQFull), 0, abort_flag);
       if (!ok) report(status, 2, 1, -1);
@@ -204,40 +242,58 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
           ptx::tc_commit(bar(kKEmpty0));
         }
       }
+      long long pt_kv = 0, pt_p = 0, pt_qk = 0, pt_pv = 0;
+      const long long pt_begin = PROF_T();
       for (int e = 0; e < cnt && ok; ++e) {
         const int s = e & 1;
         const int fl = ent[e] & 0xff;
         const bool next = (e + 1) < cnt;
         const int fln = next ? (ent[e + 1] & 0xff) : 0;
+        long long pt0 = PROF_T();
         if (next) ok = ptx::mbar_wait(bar(kKFull0 + (s ^ 1)), ((e + 1) >> 1) & 1, abort_flag);
         if (ok) ok = ptx::mbar_wait(bar(kVFull0 + s), (e >> 1) & 1, abort_flag);
+        pt_kv += PROF_T() - pt0;
         if (!ok) { report(status, 2, 1, e); break; }
         if (fl & 0x0f) {
-          ok = ptx::mbar_wait(bar(kPFullA), par_p[0], abort_flag);
+          pt0 = PROF_T();
+          long long waited = 0;
+          ok = pv_when_ready(0, s, acc[0], par_p[0], waited);
+          pt_p += waited;
+          pt_pv += PROF_T() - pt0 - waited;
           if (!ok) { report(status, 3, 1, e); break; }
           par_p[0] ^= 1;
-          ptx::tc_fence_after();
-          issue_pv(0, s, acc[0]);
           acc[0] = 1;
         }
+        pt0 = PROF_T();
         if (fln & 0x0f) issue_qk(0, s ^ 1);
+        pt_qk += PROF_T() - pt0;
         if (fl & 0xf0) {
-          ok = ptx::mbar_wait(bar(kPFullB), par_p[1], abort_flag);
+          pt0 = PROF_T();
+          long long waited = 0;
+          ok = pv_when_ready(1, s, acc[1], par_p[1], waited);
+          pt_p += waited;
+          pt_pv += PROF_T() - pt0 - waited;
           if (!ok) { report(status, 3, 1, e); break; }
           par_p[1] ^= 1;
-          ptx::tc_fence_after();
-          issue_pv(1, s, acc[1]);
           acc[1] = 1;
         }
         ptx::tc_commit(bar(kVEmpty0 + s));
+        pt0 = PROF_T();
         if (fln & 0xf0) issue_qk(1, s ^ 1);
+        pt_qk += PROF_T() - pt0;
         if (next) ptx::tc_commit(bar(kKEmpty0 + (s ^ 1)));
       }
       ptx::tc_commit(bar(kOFinal));
+      PROF_ADD(0, PROF_T() - pt_begin);   // MMA loop total
+      PROF_ADD(1, pt_kv);                 // waiting for K/V tiles
+      PROF_ADD(2, pt_p);                  // waiting for P
+      PROF_ADD(3, cnt);
+      PROF_ADD(4, pt_qk);                 // issuing QK^T MMAs
+      PROF_ADD(5, pt_pv);                 // issuing PV MMAs
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // ------------------------------------------------------------------ softmax + epilogue
     const int x = (warp - 4) / 4;                 // 0: tile A, 1: tile B
     const int wq = warp % 4;                      // tensor-memory lane quarter of this warp
@@ -255,21 +311,28 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
     uint32_t par_s = 0;
     int done = 0;
     bool ok = true;
+    long long ps_wait = 0, ps_ld = 0, ps_comp = 0, ps_st = 0;
+    const long long ps_begin = PROF_T();
     for (int e = 0; e < cnt; ++e) {
       const int en = ent[e];
       const int sub = (en >> (4 * x)) & 0xf;
       if (!sub) continue;
       const int col0 = (en >> 8) * kTile;
+      const long long ps0 = PROF_T();
       ok = ptx::mbar_wait(bar(kSFullA + x), par_s, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report(status, 4, 2 + x, e); break; }
       par_s ^= 1;
       ptx::tc_fence_after();
+      const long long ps0b = PROF_T();
+      ps_wait += ps0b - ps0;
 
       float v[kTile];
 #pragma unroll
       for (int c = 0; c < 4; ++c) ptx::tmem_ld32(tS + c * 32, reinterpret_cast<uint32_t*>(v) + c * 32);
       ptx::tmem_ld_wait();
+      const long long ps1 = PROF_T();
+      ps_ld += ps1 - ps0b;
 
       if (sub != 0xf || col0 + kTile > kvl_min) {
         const int lim = kvl - col0;               // columns >= lim are beyond the valid keys
@@ -281,17 +344,20 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
           v[c] = valid ? v[c] : -INFINITY;
         }
       }
-      // row maximum with eight independent chains (a single chain of 128 dependent max ops is latency-bound)
+      // P = exp2(S*scale - ref) for the whole row, packed to 16 bits and stored over the first 64 columns
+      // of S; returns the row sum.
+      // row maximum: eight independent chains of three-input max
       float mxa[8];
 #pragma unroll
-      for (int a = 0; a < 8; ++a) mxa[a] = fmaxf(v[a], v[a + 8]);
+      for (int a = 0; a < 8; ++a) mxa[a] = ptx::max3(v[a], v[a + 8], v[a + 16]);
 #pragma unroll
-      for (int c = 16; c < kTile; c += 16)
+      for (int c = 24; c + 16 <= kTile; c += 16)
 #pragma unroll
-        for (int a = 0; a < 8; ++a) mxa[a] = fmaxf(mxa[a], fmaxf(v[c + a], v[c + a + 8]));
-      const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
-                             fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
-      const float m_new = fmaxf(m, mx * scale_log2);
+        for (int a = 0; a < 8; ++a) mxa[a] = ptx::max3(mxa[a], v[c + a], v[c + a + 8]);
+#pragma unroll
+      for (int a = 0; a < 8; ++a) mxa[a] = fmaxf(mxa[a], v[kTile - 8 + a]);
+      const float mx = fmaxf(ptx::max3(mxa[0], mxa[1], mxa[2]), ptx::max3(mxa[3], mxa[4], mxa[5]));
+      const float m_new = fmaxf(m, ptx::max3(mx, mxa[6], mxa[7]) * scale_log2);
       if (done == 0) {
         m = m_new;
       } else if (__any_sync(0xffffffffu, m_new > m + kRescaleThreshold)) {
@@ -307,28 +373,53 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
           for (int i = 0; i < 32; ++i) o[i] *= alpha;
           ptx::tmem_st32(tO + c * 32, reinterpret_cast<const uint32_t*>(o));
         }
+        PROF_ADD(13 + 8 * x, lane == 0 && wq == 0 ? 1 : 0);
       }
-      const float mm = (m == -INFINITY) ? 0.f : m;
-      float suma[4] = {0.f, 0.f, 0.f, 0.f};
+      // P = exp2(S*scale - m), two fp32 lanes per instruction where the hardware has packed forms; each
+      // half row is handed to the MMA warp as soon as it is stored, so P*V starts while the other half
+      // is still being computed.
+      const float ref = (m == -INFINITY) ? 0.f : m;
+      const uint64_t scale2 = ptx::pack_f32x2(scale_log2, scale_log2);
+      const uint64_t nref2 = ptx::pack_f32x2(-ref, -ref);
+      uint64_t sum2a = 0, sum2b = 0;    // bit pattern of (0.f, 0.f)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float p0 = ptx::ex2(fmaf(v[half * 64 + 2 * i], scale_log2, -mm));
-          const float p1 = ptx::ex2(fmaf(v[half * 64 + 2 * i + 1], scale_log2, -mm));
-          suma[i & 3] += p0 + p1;
+          const uint64_t x2 = ptx::fma_f32x2(ptx::pack_f32x2(v[half * 64 + 2 * i], v[half * 64 + 2 * i + 1]), scale2, nref2);
+          float x0, x1;
+          ptx::unpack_f32x2(x2, x0, x1);
+          const float p0 = ptx::ex2(x0), p1 = ptx::ex2(x1);
+          const uint64_t p2 = ptx::pack_f32x2(p0, p1);
+          if (i & 1) sum2b = ptx::add_f32x2(sum2b, p2); else sum2a = ptx::add_f32x2(sum2a, p2);
           pk[i] = pack2<kBF16>(p0, p1);
         }
         ptx::tmem_st32(tS + half * 32, pk);
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar(kPLoA + 2 * x + half));
       }
-      l += (suma[0] + suma[1]) + (suma[2] + suma[3]);
-      ptx::tmem_st_wait();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(bar(kPFullA + x));
+      float s0, s1, s2, s3;
+      ptx::unpack_f32x2(sum2a, s0, s1);
+      ptx::unpack_f32x2(sum2b, s2, s3);
+      const float sum = (s0 + s1) + (s2 + s3);
+      l += sum;
+      const long long ps2 = PROF_T();
+      const long long ps3 = ps2;
+      ps_comp += ps2 - ps1;
+      ps_st += ps3 - ps2;
       ++done;
     }
 
+    if (lane == 0 && wq == 0) {
+      PROF_ADD(8 + 8 * x, PROF_T() - ps_begin);   // softmax loop total (warp 0 of the group)
+      PROF_ADD(9 + 8 * x, ps_wait);               // waiting for S
+      PROF_ADD(10 + 8 * x, ps_ld);                // tensor-memory loads
+      PROF_ADD(11 + 8 * x, ps_comp);              // max / exp / pack / store issue
+      PROF_ADD(12 + 8 * x, ps_st);                // store completion + arrive
+      PROF_ADD(14 + 8 * x, done);
+    }
     if (ok) {
       ok = ptx::mbar_wait(bar(kOFinal), 0, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -400,6 +491,16 @@ int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N
 }  // namespace moddit
 
 using namespace moddit;
+
+#ifdef MODDIT_PROFILE
+extern "C" int moddit_debug_profile(unsigned long long* host32) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(host32, g_prof, sizeof(unsigned long long) * 32);
+  unsigned long long zeros[32] = {};
+  cudaMemcpyToSymbol(g_prof, zeros, sizeof(zeros));
+  return 0;
+}
+#endif
 
 extern "C" int moddit_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
                                       const int32_t* counts, const int32_t* entries, int Hm, float softmax_scale,

@@ -10,7 +10,8 @@ import os
 from ctypes import c_char_p, c_double, c_float, c_int, c_int64, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmoddit.so")
+# MODDIT_LIB_PATH lets a developer load another build of the same ABI (e.g. an instrumented one)
+LIB_PATH = os.environ.get("MODDIT_LIB_PATH") or os.path.join(_HERE, "libmoddit.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
