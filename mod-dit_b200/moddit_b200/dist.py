@@ -23,19 +23,47 @@ def shard_bounds(total: int, world: int, rank: int):
     return rank * per, (rank + 1) * per
 
 
+def _exchange(world: int, rank: int, send_view, recv_view, local_copy, group):
+    """One grouped exchange: `send_view(peer)` / `recv_view(peer)` give lists of contiguous tensors."""
+    ops = []
+    for peer in range(world):
+        if peer == rank:
+            continue
+        gpeer = dist.get_global_rank(group, peer) if group is not None else peer
+        for t in recv_view(peer):
+            ops.append(dist.P2POp(dist.irecv, t, gpeer, group=group))
+        for t in send_view(peer):
+            ops.append(dist.P2POp(dist.isend, t, gpeer, group=group))
+    reqs = dist.batch_isend_irecv(ops) if ops else []
+    local_copy()
+    for r in reqs:
+        r.wait()
+
+
 def seq_to_head(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
-    """(1, H, N/P, D) sequence shard -> (1, H/P, N, D) head shard (heads [rank*H/P, (rank+1)*H/P))."""
+    """(1, H, N/P, D) sequence shard -> (1, H/P, N, D) head shard (heads [rank*H/P, (rank+1)*H/P)).
+
+    Each (head, sequence shard) piece is contiguous on both sides, so pieces travel straight into their
+    final place in one grouped send/recv: no staging buffer and no repacking pass.
+    """
     world = dist.get_world_size(group)
     if world == 1:
         return x
+    rank = dist.get_rank(group)
     _, H, ns, D = x.shape
     if H % world:
         raise ValueError(f"{H} heads do not divide over {world} ranks")
+    if not x.is_contiguous():
+        x = x.contiguous()
     hp = H // world
-    send = x.reshape(world, hp, ns, D).contiguous()            # chunk p = heads of rank p
-    recv = torch.empty_like(send)                              # chunk r = my heads, sequence shard of rank r
-    dist.all_to_all_single(recv, send, group=group)
-    return recv.permute(1, 0, 2, 3).reshape(1, hp, world * ns, D).contiguous()
+    out = torch.empty(1, hp, world * ns, D, device=x.device, dtype=x.dtype)
+    _exchange(
+        world, rank,
+        send_view=lambda peer: [x[0, peer * hp + h] for h in range(hp)],                   # hp pieces of (ns, D)
+        recv_view=lambda peer: [out[0, h, peer * ns:(peer + 1) * ns] for h in range(hp)],  # hp pieces of (ns, D)
+        local_copy=lambda: out[0, :, rank * ns:(rank + 1) * ns].copy_(x[0, rank * hp:(rank + 1) * hp]),
+        group=group)
+    return out
 
 
 def head_to_seq(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
@@ -43,11 +71,18 @@ def head_to_seq(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> t
     world = dist.get_world_size(group)
     if world == 1:
         return x
+    rank = dist.get_rank(group)
     _, hp, N, D = x.shape
     if N % world:
         raise ValueError(f"sequence length {N} does not divide over {world} ranks")
+    if not x.is_contiguous():
+        x = x.contiguous()
     ns = N // world
-    send = x.reshape(hp, world, ns, D).permute(1, 0, 2, 3).contiguous()   # chunk p = sequence shard of rank p
-    recv = torch.empty_like(send)                                        # chunk r = heads of rank r
-    dist.all_to_all_single(recv, send, group=group)
-    return recv.reshape(1, world * hp, ns, D)
+    out = torch.empty(1, world * hp, ns, D, device=x.device, dtype=x.dtype)
+    _exchange(
+        world, rank,
+        send_view=lambda peer: [x[0, h, peer * ns:(peer + 1) * ns] for h in range(hp)],
+        recv_view=lambda peer: [out[0, peer * hp + h] for h in range(hp)],
+        local_copy=lambda: out[0, rank * hp:(rank + 1) * hp].copy_(x[0, :, rank * ns:(rank + 1) * ns]),
+        group=group)
+    return out
