@@ -159,10 +159,23 @@ def run_ours(args):
         q_in, k_in, v_in = q, k, v
     state = make_state(cfg, he - hb)
 
+    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    value_group = dist.new_group(backend="nccl") if world > 1 else None   # own communicator: runs beside q/k
+
     def layer(qs, ks, vs, step):
+        ready = None
         if world > 1:
-            qs, ks, vs = mdist.seq_to_head(qs), mdist.seq_to_head(ks), mdist.seq_to_head(vs)
-        out, _ = SparseAttentionWithMap(qs, ks, vs, state, logger, current_step=step)
+            main = torch.cuda.current_stream(dev)
+            comm_stream.wait_stream(main)
+            with torch.cuda.stream(comm_stream):
+                # value is not needed until the attention kernel: it travels while the mask is predicted
+                vs_h = mdist.seq_to_head(vs, group=value_group)
+                ready = torch.cuda.Event()
+                ready.record(comm_stream)
+            qs, ks = mdist.seq_to_head(qs), mdist.seq_to_head(ks)
+            vs = vs_h
+            vs.record_stream(main)
+        out, _ = SparseAttentionWithMap(qs, ks, vs, state, logger, current_step=step, value_ready=ready)
         if world > 1:
             out = mdist.head_to_seq(out)
         return out

@@ -175,26 +175,29 @@ int moddit_select_mass(const void* map_f16, int H, int n, float tau, uint8_t* ke
  * (2*row_half + col_half) marks a kept 64x64 quarter (block_size 128: 0 or 0xF).
  *   mask    : (Hm, nbq, nbk) bool bytes, blocks of `block_size` tokens on the grid that starts at token 0
  *   counts  : (Hm, npairs) int32      entries : (Hm, npairs, ntiles) int32,
+ *   order   : NULL or (Hm, npairs) int32: the pairs of each head sorted by list length, longest first
+ *             (ties by index); the sparse forward starts its blocks in this order
  *   npairs = ceil(ceil(N/128)/2), ntiles = ceil(N/128); key blocks >= kv_block_limit are dropped.
  * Re-encodes the mask that MoD/mod/attn_mask.py:297-317 hands to the third-party sparse kernel.
  */
 int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, int block_size, int N,
-                      int kv_block_limit, int32_t* counts, int32_t* entries, void* stream);
+                      int kv_block_limit, int32_t* counts, int32_t* entries, int32_t* order, void* stream);
 
 /* Block-sparse flash-attention forward.  Replaces `AttentionSparseEngine` (MoD/mod/attn_mask.py:266-331:
  * block_sparse_sage2_attn_cuda for video rows, flashinfer prefill for text rows, sageattn for all-true
  * masks) and, with all-true lists and `lse` non-null, the dense pass of
  * MoD/mod/triton_flash_sparsity.py:314-324.
  *   q,k,v,out : (BH, N, D); head bh uses lists of mask head bh % Hm
+ *   order     : NULL (pairs in index order) or the (Hm, npairs) order from moddit_tile_lists
  *   rows < q_split attend keys < kv_len_lo, other rows keys < kv_len_hi
  *   lse       : NULL or (BH, N) float32 natural-log row log-sum-exp
  *   status    : device int32[4], zeroed by the caller; non-zero afterwards means a bounded wait
  *               expired inside the kernel (status[0]=code, [1]=block, [2]=role) and `out` is invalid
  */
 int moddit_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
-                           const int32_t* counts, const int32_t* entries, int Hm, float softmax_scale,
-                           int q_split, int kv_len_lo, int kv_len_hi, void* out, float* lse,
-                           int32_t* status, void* stream);
+                           const int32_t* counts, const int32_t* entries, const int32_t* order, int Hm,
+                           float softmax_scale, int q_split, int kv_len_lo, int kv_len_hi, void* out,
+                           float* lse, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -110,7 +110,7 @@ def _engine_lists(mask: torch.Tensor, block_size: int, seq_len: int):
 
 
 def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_token_num=0, block_size=128,
-                          _lists=None):
+                          _lists=None, _value_ready=None):
     """Block-sparse attention of (B,H,S,D) tensors under a bool block mask (:266-331).
 
     Video query rows (index < video_token_num) see the keys below the valid length rounded up to 64, text
@@ -119,13 +119,16 @@ def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_
     """
     seq_len = query.shape[2]
     query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
-    counts, entries = _lists if _lists is not None else _engine_lists(mask, block_size, seq_len)
+    lists = _lists if _lists is not None else _engine_lists(mask, block_size, seq_len)
+    counts, entries, order = lists.counts, lists.entries, lists.order
+    if _value_ready is not None:       # value produced on another stream (e.g. still arriving from peers)
+        torch.cuda.current_stream(query.device).wait_event(_value_ready)
     if pre_defined_mask is None:
-        return _ops.sparse_attn_fwd(query, key, value, counts, entries, check_status=False)
+        return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, check_status=False)
     valid = _valid_kv(pre_defined_mask, seq_len)
     border = min(seq_len, (valid + 63) // 64 * 64)
-    return _ops.sparse_attn_fwd(query, key, value, counts, entries, q_split=video_token_num, kv_len_lo=border,
-                                kv_len_hi=valid, check_status=False)
+    return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, q_split=video_token_num,
+                                kv_len_lo=border, kv_len_hi=valid, check_status=False)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -259,6 +262,10 @@ def SparseAttentionWithMap(
 ) -> Tuple[torch.Tensor, Optional[Dict]]:
     """Adaptive sparse attention of (1, H, S, D) fp16/bf16 tensors (:567-729).
 
+    Optional keyword `value_ready` (a torch.cuda.Event): `value` is produced on another stream and only
+    becomes valid once the event has fired; mask prediction, which needs query and key only, starts at
+    once and the wait happens right before the attention kernel.
+
     Steps warmup-2 and warmup-1 collect features (dense output); afterwards every predict_T-th step
     refreshes the map, the features and the mask (dense output) and all other steps run the block-sparse
     forward under the stored mask.  Returns (output (1,H,S,D), mask info) like the reference.
@@ -279,10 +286,15 @@ def SparseAttentionWithMap(
 
     pooled = warmup_state.get('score_producer', 'replay') == 'pooled'
     warmup_steps = warmup_state['warmup_steps']
-    query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
+    value_ready = kwargs.get('value_ready')
+    query, key = query.contiguous(), key.contiguous()
 
     if pooled:
-        return _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx)
+        return _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx,
+                            value_ready)
+    if value_ready is not None:
+        torch.cuda.current_stream(query.device).wait_event(value_ready)
+    value = value.contiguous()
 
     if current_step < warmup_steps:
         if current_step >= warmup_steps - 2:
@@ -328,13 +340,20 @@ def SparseAttentionWithMap(
     return output, {'mask': warmup_state['mask']}
 
 
-def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx):
+def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx,
+                 value_ready=None):
     """Variant with the mean-pooled map producer: the mask is re-predicted on every step from the pooled map
     of that step, so no dense pass is needed after the first feature-collection step."""
     seq_len, num_heads = query.size(2), query.size(1)
     warmup_steps = warmup_state['warmup_steps']
     bs = warmup_state['block_size']
+
+    def wait_value():
+        if value_ready is not None:
+            torch.cuda.current_stream(query.device).wait_event(value_ready)
+
     if current_step < warmup_steps - 2:
+        wait_value()
         output, _ = dense_attention_with_lse(query, key, value, kv_len=_valid_kv(pre_defined_mask, seq_len))
         return output, {'mode': 'warmup', 'mask': None}
     dark = compute_pooled_map(query, key, warmup_state).squeeze(0)
@@ -347,6 +366,7 @@ def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, curr
         warmup_state['features_history'] = [feats]
         warmup_state['current_steps'] = current_step + 1
         warmup_state['prev_full_maps'] = dark
+        wait_value()
         output, _ = dense_attention_with_lse(query, key, value, kv_len=_valid_kv(pre_defined_mask, seq_len))
         return output, {'mode': 'warmup', 'mask': None}
     history.append(feats)
@@ -360,5 +380,5 @@ def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, curr
     _store_mask(warmup_state, mask, seq_len)
     output = AttentionSparseEngine(query, key, value, mask, pre_defined_mask=pre_defined_mask,
                                    video_token_num=warmup_state.get('video_token_num', 0), block_size=bs,
-                                   _lists=warmup_state['_tile_lists'][1])
+                                   _lists=warmup_state['_tile_lists'][1], _value_ready=value_ready)
     return output, {'mask': mask}

@@ -33,6 +33,6 @@ int require_sm100() {
 
 }  // namespace moddit
 
-extern "C" int moddit_abi_version(void) { return 1; }
+extern "C" int moddit_abi_version(void) { return 2; }
 
 extern "C" const char* moddit_last_error_string(void) { return moddit::g_error; }

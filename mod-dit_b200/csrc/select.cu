@@ -228,6 +228,27 @@ __global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t*
   if (threadIdx.x == 0) counts[static_cast<int64_t>(h) * npairs + p] = base_s;
 }
 
+// Longest-first order of the query-tile pairs of one mask head (rank by counting; ties by index, so the
+// result is deterministic).  A pair with a long list (text rows keep every key tile) started last would
+// leave the other SMs idle at the end of the launch.
+__global__ void __launch_bounds__(256) order_pairs_kernel(const int32_t* __restrict__ counts, int npairs,
+                                                          int32_t* __restrict__ order) {
+  extern __shared__ int32_t cnt_s[];
+  const int h = blockIdx.x;
+  const int32_t* c = counts + static_cast<int64_t>(h) * npairs;
+  for (int i = threadIdx.x; i < npairs; i += blockDim.x) cnt_s[i] = c[i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+    const int ci = cnt_s[i];
+    int rank = 0;
+    for (int j = 0; j < npairs; ++j) {
+      const int cj = cnt_s[j];
+      rank += (cj > ci) || (cj == ci && j < i);
+    }
+    order[static_cast<int64_t>(h) * npairs + rank] = i;
+  }
+}
+
 }  // namespace
 }  // namespace moddit
 
@@ -302,7 +323,8 @@ extern "C" int moddit_select_mass(const void* map_f16, int H, int n, float tau, 
 }
 
 extern "C" int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, int block_size, int N,
-                                 int kv_block_limit, int32_t* counts, int32_t* entries, void* stream) {
+                                 int kv_block_limit, int32_t* counts, int32_t* entries, int32_t* order,
+                                 void* stream) {
   clear_error();
   MODDIT_CHECK_ARG(mask && counts && entries, "tile_lists: null pointer");
   MODDIT_CHECK_ARG(Hm > 0 && Hm <= 65535 && nbq > 0 && nbk > 0 && N > 0 && kv_block_limit >= 0, "tile_lists: bad sizes");
@@ -315,5 +337,9 @@ extern "C" int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, 
   tile_lists_kernel<<<dim3(npairs, Hm), kListThreads, 0, as_stream(stream)>>>(mask, nbq, nbk, 128 / block_size, ntq,
                                                                               ntq, kv_block_limit, counts, entries);
   MODDIT_CHECK_LAUNCH("tile_lists_kernel");
+  if (order != nullptr) {
+    order_pairs_kernel<<<Hm, 256, sizeof(int32_t) * npairs, as_stream(stream)>>>(counts, npairs, order);
+    MODDIT_CHECK_LAUNCH("order_pairs_kernel");
+  }
   return MODDIT_OK;
 }

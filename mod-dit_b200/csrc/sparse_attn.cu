@@ -89,7 +89,7 @@ template <int D, bool kBF16>
 __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
     const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
     const __grid_constant__ CUtensorMap tm_v, const int32_t* __restrict__ counts,
-    const int32_t* __restrict__ entries, int Hm, int ntk, int N, float scale_log2, int q_split, int kvl_lo,
+    const int32_t* __restrict__ entries, const int32_t* __restrict__ order, int Hm, int ntk, int N, float scale_log2, int q_split, int kvl_lo,
     int kvl_hi, void* __restrict__ out_raw, float* __restrict__ lse, int32_t* __restrict__ status) {
   constexpr int kTileBytes = kTile * D * 2;       // one Q, K or V tile
   constexpr int kChunks = D / 64;                 // 64-element (128-byte) column chunks per tile
@@ -109,12 +109,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
-  const int pair = blockIdx.x;
   const int bh = blockIdx.y;
   const int npairs = gridDim.x;
+  const int mh = bh % Hm;
+  // blocks start in increasing blockIdx.x: `order` puts the longest lists of the head first
+  const int pair = order ? order[static_cast<int64_t>(mh) * npairs + blockIdx.x] : static_cast<int>(blockIdx.x);
   const int ntq = (N + kTile - 1) / kTile;
   const bool has_b = (2 * pair + 1) < ntq;
-  const int mh = bh % Hm;
   const int cnt = counts[static_cast<int64_t>(mh) * npairs + pair];
   const int32_t* ent = entries + (static_cast<int64_t>(mh) * npairs + pair) * ntk;
 
@@ -469,7 +470,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
 
 template <int D, bool kBF16>
 int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N, const int32_t* counts,
-           const int32_t* entries, int Hm, float softmax_scale, int q_split, int kvl_lo, int kvl_hi, void* out,
+           const int32_t* entries, const int32_t* order, int Hm, float softmax_scale, int q_split, int kvl_lo, int kvl_hi, void* out,
            float* lse, int32_t* status, cudaStream_t st) {
   CUtensorMap tq, tk, tv;
   if (int rc = make_tmap_rows(&tq, q, dtype, BH, N, D, kTile)) return rc;
@@ -481,7 +482,7 @@ int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N
   const size_t smem = smem_bytes<D>();
   MODDIT_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   const float scale_log2 = softmax_scale * 1.4426950408889634f;
-  kernel<<<dim3(npairs, BH), kThreads, smem, st>>>(tq, tk, tv, counts, entries, Hm, ntq, N, scale_log2, q_split,
+  kernel<<<dim3(npairs, BH), kThreads, smem, st>>>(tq, tk, tv, counts, entries, order, Hm, ntq, N, scale_log2, q_split,
                                                    kvl_lo, kvl_hi, out, lse, status);
   MODDIT_CHECK_LAUNCH("sparse_attn_fwd_kernel");
   return MODDIT_OK;
@@ -503,7 +504,8 @@ extern "C" int moddit_debug_profile(unsigned long long* host32) {
 #endif
 
 extern "C" int moddit_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
-                                      const int32_t* counts, const int32_t* entries, int Hm, float softmax_scale,
+                                      const int32_t* counts, const int32_t* entries, const int32_t* order, int Hm,
+                                      float softmax_scale,
                                       int q_split, int kv_len_lo, int kv_len_hi, void* out, float* lse,
                                       int32_t* status, void* stream) {
   clear_error();
@@ -521,13 +523,13 @@ extern "C" int moddit_sparse_attn_fwd(const void* q, const void* k, const void* 
   cudaStream_t st = as_stream(stream);
   if (D == 128) {
     return dtype == MODDIT_BF16
-               ? launch<128, true>(q, k, v, dtype, BH, N, counts, entries, Hm, softmax_scale, q_split, kv_len_lo,
+               ? launch<128, true>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split, kv_len_lo,
                                    kv_len_hi, out, lse, status, st)
-               : launch<128, false>(q, k, v, dtype, BH, N, counts, entries, Hm, softmax_scale, q_split, kv_len_lo,
+               : launch<128, false>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split, kv_len_lo,
                                     kv_len_hi, out, lse, status, st);
   }
-  return dtype == MODDIT_BF16 ? launch<64, true>(q, k, v, dtype, BH, N, counts, entries, Hm, softmax_scale, q_split,
+  return dtype == MODDIT_BF16 ? launch<64, true>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split,
                                                  kv_len_lo, kv_len_hi, out, lse, status, st)
-                              : launch<64, false>(q, k, v, dtype, BH, N, counts, entries, Hm, softmax_scale, q_split,
+                              : launch<64, false>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split,
                                                   kv_len_lo, kv_len_hi, out, lse, status, st);
 }

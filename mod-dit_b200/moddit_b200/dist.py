@@ -40,16 +40,43 @@ def _exchange(world: int, rank: int, send_view, recv_view, local_copy, group):
         r.wait()
 
 
+# Measured on 8 B200s (89 MB per tensor per GPU): one all_to_all_single plus a repacking copy takes 0.29 ms,
+# the grouped per-piece send/recv 0.60 ms; on 2 GPUs (355 MB) it is 0.97 ms against 0.79 ms.
+_PIECEWISE_MAX_WORLD = 2
+
+
+def _seq_to_head_a2a(x: torch.Tensor, world: int, group) -> torch.Tensor:
+    _, H, ns, D = x.shape
+    hp = H // world
+    send = x.reshape(world, hp, ns, D)                         # chunk p = heads of rank p (a view)
+    recv = torch.empty_like(send)                              # chunk r = my heads, sequence shard of rank r
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.permute(1, 0, 2, 3).reshape(1, hp, world * ns, D).contiguous()
+
+
+def _head_to_seq_a2a(x: torch.Tensor, world: int, group) -> torch.Tensor:
+    _, hp, N, D = x.shape
+    ns = N // world
+    send = x.reshape(hp, world, ns, D).permute(1, 0, 2, 3).contiguous()   # chunk p = sequence shard of rank p
+    recv = torch.empty_like(send)                                        # chunk r = heads of rank r
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.reshape(1, world * hp, ns, D)
+
+
 def seq_to_head(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """(1, H, N/P, D) sequence shard -> (1, H/P, N, D) head shard (heads [rank*H/P, (rank+1)*H/P)).
 
-    Each (head, sequence shard) piece is contiguous on both sides, so pieces travel straight into their
-    final place in one grouped send/recv: no staging buffer and no repacking pass.
+    Up to 2 ranks every (head, sequence shard) piece, contiguous on both sides, travels straight into its
+    final place in one grouped send/recv; with more ranks one all-to-all plus a repacking copy is faster.
     """
     world = dist.get_world_size(group)
     if world == 1:
         return x
     rank = dist.get_rank(group)
+    if x.shape[1] % world:
+        raise ValueError(f"{x.shape[1]} heads do not divide over {world} ranks")
+    if world > _PIECEWISE_MAX_WORLD:
+        return _seq_to_head_a2a(x.contiguous(), world, group)
     _, H, ns, D = x.shape
     if H % world:
         raise ValueError(f"{H} heads do not divide over {world} ranks")
@@ -75,6 +102,8 @@ def head_to_seq(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> t
     _, hp, N, D = x.shape
     if N % world:
         raise ValueError(f"sequence length {N} does not divide over {world} ranks")
+    if world > _PIECEWISE_MAX_WORLD:
+        return _head_to_seq_a2a(x.contiguous(), world, group)
     if not x.is_contiguous():
         x = x.contiguous()
     ns = N // world

@@ -24,7 +24,7 @@ _TIMING = {"on": False, "records": [], "launches": 0}
 # kernels launched by one call of each entry point (for launch accounting in benchmarks)
 KERNELS_PER_CALL = {"moddit_pool_blocks": 1, "moddit_pooled_map": 1, "moddit_replay_map": 1, "moddit_mts": 2,
                     "moddit_mtm": 1, "moddit_solve": 3, "moddit_select_lines": 1, "moddit_head_modes": 1,
-                    "moddit_mask_from_lines": 1, "moddit_select_mass": 1, "moddit_tile_lists": 1,
+                    "moddit_mask_from_lines": 1, "moddit_select_mass": 1, "moddit_tile_lists": 2,
                     "moddit_sparse_attn_fwd": 1, "moddit_replay_status": 0,
                     "moddit_mts_noalloc": 2}
 
@@ -333,8 +333,19 @@ def select_mass(dark_map: torch.Tensor, tau: float) -> torch.Tensor:
     return keep
 
 
+class TileLists(tuple):
+    """(counts, entries, order) produced by `tile_lists`; unpacks like the 2-tuple (counts, entries)."""
+
+    def __new__(cls, counts, entries, order):
+        obj = super().__new__(cls, (counts, entries))
+        obj.counts, obj.entries, obj.order = counts, entries, order
+        return obj
+
+
 def tile_lists(mask: torch.Tensor, block_size: int, n_tokens: int, kv_block_limit: Optional[int] = None
-               ) -> Tuple[torch.Tensor, torch.Tensor]:
+               ) -> TileLists:
+    """Work lists of the sparse forward for a bool (H, nbq, nbk) block mask, plus the longest-first order of
+    the query-tile pairs of every head."""
     dev = _need_cuda(mask)
     if mask.dtype != torch.bool or mask.dim() != 3:
         raise ValueError("mask must be a bool (H, nbq, nbk) tensor")
@@ -344,11 +355,12 @@ def tile_lists(mask: torch.Tensor, block_size: int, n_tokens: int, kv_block_limi
     npairs = (ntq + 1) // 2
     counts = torch.empty(Hm, npairs, device=dev, dtype=torch.int32)
     entries = torch.empty(Hm, npairs, ntq, device=dev, dtype=torch.int32)
+    order = torch.empty(Hm, npairs, device=dev, dtype=torch.int32)
     lim = nbk if kv_block_limit is None else int(kv_block_limit)
     with torch.cuda.device(dev), _timed("moddit_tile_lists", dev):
         check(lib.moddit_tile_lists(_ptr(mask), Hm, nbq, nbk, block_size, n_tokens, lim, _ptr(counts),
-                                    _ptr(entries), _stream(dev)), "moddit_tile_lists")
-    return counts, entries
+                                    _ptr(entries), _ptr(order), _stream(dev)), "moddit_tile_lists")
+    return TileLists(counts, entries, order)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -380,7 +392,8 @@ def raise_on_status(device) -> None:
 
 
 def sparse_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, counts: torch.Tensor,
-                    entries: torch.Tensor, *, softmax_scale: Optional[float] = None,
+                    entries: torch.Tensor, *, order: Optional[torch.Tensor] = None,
+                    softmax_scale: Optional[float] = None,
                     q_split: Optional[int] = None, kv_len_lo: Optional[int] = None,
                     kv_len_hi: Optional[int] = None, return_lse: bool = False, check_status: bool = True,
                     out: Optional[torch.Tensor] = None):
@@ -395,6 +408,9 @@ def sparse_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, counts: t
     if counts.dtype != torch.int32 or entries.dtype != torch.int32 or \
             tuple(counts.shape) != (Hm, (ntq + 1) // 2) or tuple(entries.shape) != (Hm, (ntq + 1) // 2, ntq):
         raise ValueError("counts/entries do not match the sequence length (see tile_lists)")
+    if order is not None and (order.dtype != torch.int32 or tuple(order.shape) != tuple(counts.shape)
+                              or not order.is_contiguous() or order.device != dev):
+        raise ValueError("order must be the contiguous int32 (Hm, npairs) tensor from tile_lists")
     scale = float(D ** -0.5 if softmax_scale is None else softmax_scale)
     if out is None:
         out = torch.empty_like(q)
@@ -402,7 +418,7 @@ def sparse_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, counts: t
     st = _status_words(dev)
     with torch.cuda.device(dev), _timed("moddit_sparse_attn_fwd", dev):
         check(lib.moddit_sparse_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _qkv_dtype(q), B * H, N, D, _ptr(counts),
-                                         _ptr(entries), Hm, scale, N if q_split is None else int(q_split),
+                                         _ptr(entries), _ptr(order), Hm, scale, N if q_split is None else int(q_split),
                                          N if kv_len_lo is None else int(kv_len_lo),
                                          N if kv_len_hi is None else int(kv_len_hi), _ptr(out), _ptr(lse),
                                          _ptr(st), _stream(dev)), "moddit_sparse_attn_fwd")

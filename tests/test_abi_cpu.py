@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(_lib.lib, name), f"{name} declared in include/moddit.h but not exported"
         assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
-    assert _lib.lib.moddit_abi_version() == 1
+    assert _lib.lib.moddit_abi_version() == 2
 
 
 def test_argument_errors_do_not_touch_the_device():

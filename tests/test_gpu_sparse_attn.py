@@ -41,9 +41,11 @@ def _run(ops, *, D, dtype, bs, N, H, density, seed, B=1, Hm=None, q_split=None, 
     if ensure_diag:
         idx = torch.arange(nb)
         mask[:, idx, idx] = True
-    counts, entries = ops.tile_lists(mask.cuda(), bs, N)
-    out, lse = ops.sparse_attn_fwd(q.cuda(), k.cuda(), v.cuda(), counts, entries, q_split=q_split, kv_len_lo=kv_lo,
-                                   kv_len_hi=kv_hi, return_lse=True)
+    lists = ops.tile_lists(mask.cuda(), bs, N)
+    counts, entries = lists
+    # alternate between index order and the longest-first order: results must not depend on it
+    out, lse = ops.sparse_attn_fwd(q.cuda(), k.cuda(), v.cuda(), counts, entries, order=lists.order if seed % 2 else None,
+                                   q_split=q_split, kv_len_lo=kv_lo, kv_len_hi=kv_hi, return_lse=True)
     refs, lses = [], []
     for b in range(B):
         r, l = orc.masked_attention(q[b:b + 1], k[b:b + 1], v[b:b + 1], mask if Hm == H else mask.repeat(H // Hm, 1, 1),
@@ -112,10 +114,17 @@ def test_two_calls_are_bitwise_identical(ops):
     g = torch.Generator().manual_seed(11)
     q, k, v = (torch.randn(1, 2, 1024, 128, generator=g).to(torch.bfloat16).cuda() for _ in range(3))
     mask = (torch.rand(2, 8, 8, generator=g) < 0.5).cuda()
-    counts, entries = ops.tile_lists(mask, 128, 1024)
+    lists = ops.tile_lists(mask, 128, 1024)
+    counts, entries = lists
     a = ops.sparse_attn_fwd(q, k, v, counts, entries)
     b = ops.sparse_attn_fwd(q, k, v, counts, entries)
-    assert torch.equal(a, b)
+    c = ops.sparse_attn_fwd(q, k, v, counts, entries, order=lists.order)
+    assert torch.equal(a, b) and torch.equal(a, c)
+    cnt = counts.cpu()
+    for h in range(cnt.shape[0]):
+        o = lists.order[h].cpu().long()
+        assert sorted(o.tolist()) == list(range(cnt.shape[1]))
+        assert (cnt[h][o][:-1] >= cnt[h][o][1:]).all()
 
 
 def test_medium_shape_against_chunked_oracle(ops):
