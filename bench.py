@@ -16,8 +16,9 @@ forward, all through the public `SparseAttentionWithMap` API.  Rank 0 prints one
   cpu_baseline  the CPU oracle (`oracle/`) timed on the host cores on a bounded sample of the workload
 
 With N > 1 (torchrun) heads are sharded over ranks: every rank holds a sequence shard of q/k/v, an
-all-to-all turns it into a head shard, the path runs on the local heads and the output goes back
-through a second all-to-all; total work is fixed ("strong" scaling).
+exchange over NVLink (this library's copy kernel storing straight into peer-mapped buffers) turns it into
+a head shard, the path runs on the local heads and the output goes back the same way; total work is fixed
+("strong" scaling).
 
 `--impl reference` times the reference's own CPU path for this hot path (the oracle port of it: the
 reference itself is Python that needs its checkout, which does not exist on the benchmark box).
@@ -160,7 +161,7 @@ def run_ours(args):
     state = make_state(cfg, he - hb)
 
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
-    value_group = dist.new_group(backend="nccl") if world > 1 else None   # own communicator: runs beside q/k
+    resharder = mdist.PeerResharder(H, N, D, q_in.dtype, dev) if world > 1 else None
 
     def layer(qs, ks, vs, step):
         ready = None
@@ -169,15 +170,13 @@ def run_ours(args):
             comm_stream.wait_stream(main)
             with torch.cuda.stream(comm_stream):
                 # value is not needed until the attention kernel: it travels while the mask is predicted
-                vs_h = mdist.seq_to_head(vs, group=value_group)
+                vs = resharder.seq_to_head(vs, 2, channel=1)
                 ready = torch.cuda.Event()
                 ready.record(comm_stream)
-            qs, ks = mdist.seq_to_head(qs), mdist.seq_to_head(ks)
-            vs = vs_h
-            vs.record_stream(main)
+            qs, ks = resharder.seq_to_head_many([qs, ks], [0, 1], channel=0)
         out, _ = SparseAttentionWithMap(qs, ks, vs, state, logger, current_step=step, value_ready=ready)
         if world > 1:
-            out = mdist.head_to_seq(out)
+            out = resharder.head_to_seq(out, channel=0)
         return out
 
     def barrier():
@@ -218,7 +217,9 @@ def run_ours(args):
     for name, ms in records:
         stage_ms[name] = stage_ms.get(name, 0.0) + ms
     attn_ms = stage_ms.get("moddit_sparse_attn_fwd", 0.0) / args.steps
-    pred_ms = sum(ms for name, ms in stage_ms.items() if name != "moddit_sparse_attn_fwd") / args.steps
+    comm_ms = stage_ms.get("moddit_copy_rows", 0.0) / args.steps       # re-shard copies (N > 1 only)
+    pred_ms = sum(ms for name, ms in stage_ms.items()
+                  if name not in ("moddit_sparse_attn_fwd", "moddit_copy_rows")) / args.steps
 
     # ---- e2e: inputs in pinned host memory, output copied back ----------------------------------
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
@@ -247,13 +248,13 @@ def run_ours(args):
         e2e_ms = e0.elapsed_time(e1)
 
     # ---- reduce over ranks ------------------------------------------------------------------------
-    vals = torch.tensor([total_ms, e2e_ms, attn_ms, pred_ms], device=dev, dtype=torch.float64)
+    vals = torch.tensor([total_ms, e2e_ms, attn_ms, pred_ms, comm_ms], device=dev, dtype=torch.float64)
     sums = torch.tensor([flops_local, sparsity_local, float(launches), float(h2d), float(d2h)], device=dev,
                         dtype=torch.float64)
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
         dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-    total_ms, e2e_ms, attn_ms, pred_ms = vals.tolist()
+    total_ms, e2e_ms, attn_ms, pred_ms, comm_ms = vals.tolist()
     flops_total, sparsity_sum, launches_total, h2d_total, d2h_total = sums.tolist()
 
     if rank == 0:
@@ -278,7 +279,7 @@ def run_ours(args):
                        "sparsity": round(sparsity_sum / world, 4), "parallelism": f"head-sharded x{world}",
                        "l2": "inputs larger than L2", "gain": args.gain, "seed": 1},
             "mask_pred_ms": round(pred_ms, 3), "mask_pred_pct": round(100.0 * pred_ms / max(pred_ms + attn_ms, 1e-9), 2),
-            "attn_ms": round(attn_ms, 3),
+            "attn_ms": round(attn_ms, 3), "reshard_copy_ms": round(comm_ms, 3),
             "stage_ms_per_step": {n: round(ms / args.steps, 4) for n, ms in sorted(stage_ms.items())},
             "clocks": clocks,
             "e2e": None if e2e_value is None else {

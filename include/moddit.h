@@ -199,6 +199,16 @@ int moddit_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtyp
                            float softmax_scale, int q_split, int kv_len_lo, int kv_len_hi, void* out,
                            float* lse, int32_t* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Strided row copy: `rows` rows of `width_bytes` bytes from src (pitch src_pitch) to dst (pitch dst_pitch).
+ * `dst` may be a peer GPU's memory mapped into this process; the kernel uses plain loads and stores.  It is
+ * the building block of the sequence<->head re-shard (the reference has only dead hooks for that exchange,
+ * MoD/models/cogvideox/attention_processor.py:138-155,220-229).  All of pointers, pitches and width must be
+ * multiples of 16 bytes.
+ */
+int moddit_copy_rows(const void* src, void* dst, int64_t src_pitch, int64_t dst_pitch, int64_t width_bytes,
+                     int rows, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

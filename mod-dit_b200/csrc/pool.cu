@@ -238,3 +238,48 @@ extern "C" int moddit_pooled_map(const float* qbar, const float* kbar, int BH, i
   MODDIT_CHECK_LAUNCH("pooled_map_kernel");
   return MODDIT_OK;
 }
+
+// ---- strided row copy (used to place sequence/head shards directly into a peer GPU's buffer) ---------
+namespace moddit {
+namespace {
+
+// rows x width_bytes, 16 bytes per thread per step; plain loads from `src`, plain stores to `dst`
+// (which may be peer memory mapped into this process: ordinary P2P stores, no TMA, no multicast).
+__global__ void __launch_bounds__(256) copy_rows_kernel(const unsigned char* __restrict__ src,
+                                                        unsigned char* __restrict__ dst, int64_t src_pitch,
+                                                        int64_t dst_pitch, int64_t width16) {
+  const uint4* s = reinterpret_cast<const uint4*>(src + static_cast<int64_t>(blockIdx.y) * src_pitch);
+  uint4* d = reinterpret_cast<uint4*>(dst + static_cast<int64_t>(blockIdx.y) * dst_pitch);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < width16; i += 4 * stride) {
+    const uint4 a = __ldg(s + i), b = __ldg(s + i + stride), c = __ldg(s + i + 2 * stride), e = __ldg(s + i + 3 * stride);
+    d[i] = a;
+    d[i + stride] = b;
+    d[i + 2 * stride] = c;
+    d[i + 3 * stride] = e;
+  }
+  for (; i < width16; i += stride) d[i] = __ldg(s + i);
+}
+
+}  // namespace
+}  // namespace moddit
+
+extern "C" int moddit_copy_rows(const void* src, void* dst, int64_t src_pitch, int64_t dst_pitch, int64_t width_bytes,
+                                int rows, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(src && dst, "copy_rows: null pointer");
+  MODDIT_CHECK_ARG(rows > 0 && rows <= 65535 && width_bytes > 0, "copy_rows: rows=%d width=%lld out of range", rows,
+                   static_cast<long long>(width_bytes));
+  if (!aligned16(src) || !aligned16(dst) || (src_pitch & 15) || (dst_pitch & 15) || (width_bytes & 15))
+    return fail(MODDIT_E_ALIGN, "copy_rows: pointers, pitches and width must be multiples of 16 bytes");
+  const int64_t width16 = width_bytes / 16;
+  int64_t bx = (width16 + 256 * 4 - 1) / (256 * 4);
+  const int64_t cap = (148 * 8 + rows - 1) / rows;      // about eight CTAs per SM in total
+  if (bx > cap) bx = cap;
+  if (bx < 1) bx = 1;
+  copy_rows_kernel<<<dim3(static_cast<unsigned>(bx), rows), 256, 0, as_stream(stream)>>>(
+      static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst), src_pitch, dst_pitch, width16);
+  MODDIT_CHECK_LAUNCH("copy_rows_kernel");
+  return MODDIT_OK;
+}

@@ -50,6 +50,7 @@ SIGNATURES = {
     "moddit_select_mass": (c_int, [c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),
     "moddit_tile_lists": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                   c_void_p, c_void_p]),
+    "moddit_copy_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "moddit_sparse_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                        c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
                                        c_void_p, c_void_p]),

@@ -115,3 +115,75 @@ def head_to_seq(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> t
         local_copy=lambda: out[0, rank * hp:(rank + 1) * hp].copy_(x[0, :, rank * ns:(rank + 1) * ns]),
         group=group)
     return out
+
+
+class PeerResharder:
+    """Sequence<->head re-shard through peer-mapped (symmetric) buffers on one NVLink/NVSwitch node.
+
+    Every rank owns a head-shard staging buffer per input tensor and a sequence-shard staging buffer for
+    the output.  A re-shard is a set of strided row copies issued by this library's own copy kernel: each
+    rank stores its pieces straight into their final position in the owner's buffer (P2P stores), so there
+    is no repacking pass and no intermediate buffer; a device-side barrier of the symmetric-memory handle
+    separates writers from readers.  Buffers are reused every call: the barrier at the start of a call
+    guarantees that all ranks have finished reading the previous contents.
+    """
+
+    def __init__(self, heads: int, seq_len: int, head_dim: int, dtype: torch.dtype, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None, n_inputs: int = 3, timeout_ms: int = 20000):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import ops
+        self._ops = ops
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if heads % self.world or seq_len % self.world:
+            raise ValueError("heads and sequence length must divide over the ranks")
+        self.H, self.N, self.D = heads, seq_len, head_dim
+        self.hp, self.ns = heads // self.world, seq_len // self.world
+        self.dtype, self.device = dtype, device
+        self.esize = torch.empty((), dtype=dtype).element_size()
+        self.timeout_ms = timeout_ms
+        self.inputs, self.in_handles = [], []
+        for _ in range(n_inputs):
+            t = symm_mem.empty((1, self.hp, self.N, self.D), dtype=dtype, device=device)
+            self.inputs.append(t)
+            self.in_handles.append(symm_mem.rendezvous(t, self.group))
+        self.output = symm_mem.empty((1, self.H, self.ns, self.D), dtype=dtype, device=device)
+        self.out_handle = symm_mem.rendezvous(self.output, self.group)
+
+    def seq_to_head(self, x: torch.Tensor, slot: int, channel: int = 0) -> torch.Tensor:
+        """Push this rank's (1, H, N/P, D) shard into slot `slot` of every owner; returns the local head shard
+        (1, H/P, N, D), valid on the current stream once the call returns."""
+        return self.seq_to_head_many([x], [slot], channel)[0]
+
+    def seq_to_head_many(self, xs, slots, channel: int = 0):
+        """Several tensors between one pair of barriers (slot i receives xs[i])."""
+        for x in xs:
+            if tuple(x.shape) != (1, self.H, self.ns, self.D) or x.dtype != self.dtype or not x.is_contiguous():
+                raise ValueError("inputs must be contiguous (1, H, N/P, D) tensors of the configured dtype")
+        sync = self.in_handles[slots[0]]
+        sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # readers of the previous contents are done
+        row = self.ns * self.D * self.esize                            # bytes of one (head, sequence shard) piece
+        for step in range(self.world):
+            peer = (self.rank + step) % self.world                     # start with the local piece, spread the rest
+            for x, slot in zip(xs, slots):
+                src = x.data_ptr() + peer * self.hp * row
+                dst = int(self.in_handles[slot].buffer_ptrs[peer]) + self.rank * row
+                self._ops.copy_rows(src, dst, row, self.N * self.D * self.esize, row, self.hp, self.device)
+        sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # every rank's stores have landed
+        return [self.inputs[slot] for slot in slots]
+
+    def head_to_seq(self, x: torch.Tensor, channel: int = 0) -> torch.Tensor:
+        """Push this rank's (1, H/P, N, D) head shard back; returns the local (1, H, N/P, D) sequence shard."""
+        if tuple(x.shape) != (1, self.hp, self.N, self.D) or x.dtype != self.dtype or not x.is_contiguous():
+            raise ValueError("input must be a contiguous (1, H/P, N, D) tensor of the configured dtype")
+        hdl = self.out_handle
+        hdl.barrier(channel=channel, timeout_ms=self.timeout_ms)
+        row = self.ns * self.D * self.esize
+        for step in range(self.world):
+            peer = (self.rank + step) % self.world
+            src = x.data_ptr() + peer * row
+            dst = int(hdl.buffer_ptrs[peer]) + self.rank * self.hp * row
+            self._ops.copy_rows(src, dst, self.N * self.D * self.esize, row, row, self.hp, self.device)
+        hdl.barrier(channel=channel, timeout_ms=self.timeout_ms)
+        return self.output

@@ -363,6 +363,14 @@ def tile_lists(mask: torch.Tensor, block_size: int, n_tokens: int, kv_block_limi
     return TileLists(counts, entries, order)
 
 
+def copy_rows(src_ptr: int, dst_ptr: int, src_pitch: int, dst_pitch: int, width_bytes: int, rows: int,
+              device: torch.device) -> None:
+    """Raw strided row copy on `device`'s current stream; `dst_ptr` may point into a peer GPU's mapped buffer."""
+    with torch.cuda.device(device), _timed("moddit_copy_rows", device):
+        check(lib.moddit_copy_rows(ctypes.c_void_p(src_ptr), ctypes.c_void_p(dst_ptr), src_pitch, dst_pitch,
+                                   width_bytes, rows, _stream(device)), "moddit_copy_rows")
+
+
 # ---------------------------------------------------------------------------------------------
 # sparse forward
 # ---------------------------------------------------------------------------------------------
