@@ -174,9 +174,12 @@ def run_ours(args):
                 ready = torch.cuda.Event()
                 ready.record(comm_stream)
             qs, ks = resharder.seq_to_head_many([qs, ks], [0, 1], channel=0)
-        out, _ = SparseAttentionWithMap(qs, ks, vs, state, logger, current_step=step, value_ready=ready)
+        scatter = resharder.begin_output(channel=0) if world > 1 else None
+        out, _ = SparseAttentionWithMap(qs, ks, vs, state, logger, current_step=step, value_ready=ready,
+                                        output_scatter=scatter)
         if world > 1:
-            out = resharder.head_to_seq(out, channel=0)
+            # sparse steps wrote their rows straight into the peers' buffers; dense (priming) steps did not
+            out = resharder.finish_output(channel=0) if out is None else resharder.head_to_seq(out, channel=0)
         return out
 
     def barrier():

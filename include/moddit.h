@@ -208,6 +208,21 @@ int moddit_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtyp
  */
 int moddit_copy_rows(const void* src, void* dst, int64_t src_pitch, int64_t dst_pitch, int64_t width_bytes,
                      int rows, void* stream);
+/* The same copy for n_jobs (at most 24) source/destination pairs in one launch; `src` and `dst` are HOST
+ * arrays of device pointers. */
+int moddit_copy_rows_multi(const void* const* src, void* const* dst, int n_jobs, int64_t src_pitch,
+                           int64_t dst_pitch, int64_t width_bytes, int rows, void* stream);
+
+/* moddit_sparse_attn_fwd with the output re-shard fused into the epilogue: rows of sequence shard r
+ * ([r*N/n_peers, (r+1)*N/n_peers)) of local head bh are stored into peer_out[r], a (total_heads, N/n_peers, D)
+ * buffer of rank r mapped into this process, at head `head_base + bh` (plain peer stores).  `peer_out` is a
+ * HOST array of n_peers (at most 8) device pointers.  The caller separates these stores from the readers
+ * with its own cross-rank barrier.  No reference counterpart beyond the dead hooks cited above. */
+int moddit_sparse_attn_fwd_scatter(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
+                                   const int32_t* counts, const int32_t* entries, const int32_t* order, int Hm,
+                                   float softmax_scale, int q_split, int kv_len_lo, int kv_len_hi,
+                                   void* const* peer_out, int n_peers, int head_base, float* lse,
+                                   int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

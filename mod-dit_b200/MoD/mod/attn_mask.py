@@ -110,7 +110,7 @@ def _engine_lists(mask: torch.Tensor, block_size: int, seq_len: int):
 
 
 def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_token_num=0, block_size=128,
-                          _lists=None, _value_ready=None):
+                          _lists=None, _value_ready=None, _scatter=None):
     """Block-sparse attention of (B,H,S,D) tensors under a bool block mask (:266-331).
 
     Video query rows (index < video_token_num) see the keys below the valid length rounded up to 64, text
@@ -124,11 +124,12 @@ def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_
     if _value_ready is not None:       # value produced on another stream (e.g. still arriving from peers)
         torch.cuda.current_stream(query.device).wait_event(_value_ready)
     if pre_defined_mask is None:
-        return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, check_status=False)
+        return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, check_status=False,
+                                    scatter=_scatter)
     valid = _valid_kv(pre_defined_mask, seq_len)
     border = min(seq_len, (valid + 63) // 64 * 64)
     return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, q_split=video_token_num,
-                                kv_len_lo=border, kv_len_hi=valid, check_status=False)
+                                kv_len_lo=border, kv_len_hi=valid, check_status=False, scatter=_scatter)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -265,6 +266,9 @@ def SparseAttentionWithMap(
     Optional keyword `value_ready` (a torch.cuda.Event): `value` is produced on another stream and only
     becomes valid once the event has fired; mask prediction, which needs query and key only, starts at
     once and the wait happens right before the attention kernel.
+    Optional keyword `output_scatter` (from `moddit_b200.dist.PeerResharder.begin_output`): on sparse steps
+    the attention kernel stores its rows straight into the peers' sequence-shard buffers and the returned
+    output is None; steps that run dense attention ignore it and return the output tensor as usual.
 
     Steps warmup-2 and warmup-1 collect features (dense output); afterwards every predict_T-th step
     refreshes the map, the features and the mask (dense output) and all other steps run the block-sparse
@@ -291,7 +295,7 @@ def SparseAttentionWithMap(
 
     if pooled:
         return _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx,
-                            value_ready)
+                            value_ready, kwargs.get('output_scatter'))
     if value_ready is not None:
         torch.cuda.current_stream(query.device).wait_event(value_ready)
     value = value.contiguous()
@@ -336,12 +340,13 @@ def SparseAttentionWithMap(
     else:
         output = AttentionSparseEngine(query, key, value, warmup_state['mask'], pre_defined_mask=pre_defined_mask,
                                        video_token_num=video_token_num, block_size=block_size,
-                                       _lists=_lists_for(warmup_state, seq_len))
+                                       _lists=_lists_for(warmup_state, seq_len),
+                                       _scatter=kwargs.get('output_scatter'))
     return output, {'mask': warmup_state['mask']}
 
 
 def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx,
-                 value_ready=None):
+                 value_ready=None, output_scatter=None):
     """Variant with the mean-pooled map producer: the mask is re-predicted on every step from the pooled map
     of that step, so no dense pass is needed after the first feature-collection step."""
     seq_len, num_heads = query.size(2), query.size(1)
@@ -380,5 +385,6 @@ def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, curr
     _store_mask(warmup_state, mask, seq_len)
     output = AttentionSparseEngine(query, key, value, mask, pre_defined_mask=pre_defined_mask,
                                    video_token_num=warmup_state.get('video_token_num', 0), block_size=bs,
-                                   _lists=warmup_state['_tile_lists'][1], _value_ready=value_ready)
+                                   _lists=warmup_state['_tile_lists'][1], _value_ready=value_ready,
+                                   _scatter=output_scatter)
     return output, {'mask': mask}

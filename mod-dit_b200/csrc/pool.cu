@@ -262,8 +262,58 @@ __global__ void __launch_bounds__(256) copy_rows_kernel(const unsigned char* __r
   for (; i < width16; i += stride) d[i] = __ldg(s + i);
 }
 
+constexpr int kMaxCopyJobs = 24;
+struct CopyJobs {
+  const unsigned char* src[kMaxCopyJobs];
+  unsigned char* dst[kMaxCopyJobs];
+};
+
+// Same copy for up to 24 (source, destination) pairs in one launch: blockIdx.z selects the pair.
+__global__ void __launch_bounds__(256) copy_rows_multi_kernel(const __grid_constant__ CopyJobs jobs, int64_t src_pitch,
+                                                              int64_t dst_pitch, int64_t width16) {
+  const uint4* s = reinterpret_cast<const uint4*>(jobs.src[blockIdx.z] + static_cast<int64_t>(blockIdx.y) * src_pitch);
+  uint4* d = reinterpret_cast<uint4*>(jobs.dst[blockIdx.z] + static_cast<int64_t>(blockIdx.y) * dst_pitch);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < width16; i += 4 * stride) {
+    const uint4 a = __ldg(s + i), b = __ldg(s + i + stride), c = __ldg(s + i + 2 * stride), e = __ldg(s + i + 3 * stride);
+    d[i] = a;
+    d[i + stride] = b;
+    d[i + 2 * stride] = c;
+    d[i + 3 * stride] = e;
+  }
+  for (; i < width16; i += stride) d[i] = __ldg(s + i);
+}
+
 }  // namespace
 }  // namespace moddit
+
+extern "C" int moddit_copy_rows_multi(const void* const* src, void* const* dst, int n_jobs, int64_t src_pitch,
+                                      int64_t dst_pitch, int64_t width_bytes, int rows, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(src && dst, "copy_rows_multi: null pointer table");
+  MODDIT_CHECK_ARG(n_jobs >= 1 && n_jobs <= kMaxCopyJobs, "copy_rows_multi: n_jobs=%d outside [1, %d]", n_jobs, kMaxCopyJobs);
+  MODDIT_CHECK_ARG(rows > 0 && rows <= 65535 && width_bytes > 0, "copy_rows_multi: rows=%d width=%lld out of range", rows,
+                   static_cast<long long>(width_bytes));
+  if ((src_pitch & 15) || (dst_pitch & 15) || (width_bytes & 15))
+    return fail(MODDIT_E_ALIGN, "copy_rows_multi: pitches and width must be multiples of 16 bytes");
+  CopyJobs jobs = {};
+  for (int i = 0; i < n_jobs; ++i) {
+    if (!src[i] || !dst[i] || !aligned16(src[i]) || !aligned16(dst[i]))
+      return fail(MODDIT_E_ALIGN, "copy_rows_multi: job %d has a null or unaligned pointer", i);
+    jobs.src[i] = static_cast<const unsigned char*>(src[i]);
+    jobs.dst[i] = static_cast<unsigned char*>(dst[i]);
+  }
+  const int64_t width16 = width_bytes / 16;
+  int64_t bx = (width16 + 256 * 4 - 1) / (256 * 4);
+  const int64_t cap = (148 * 8 + static_cast<int64_t>(rows) * n_jobs - 1) / (static_cast<int64_t>(rows) * n_jobs);
+  if (bx > cap) bx = cap;
+  if (bx < 1) bx = 1;
+  copy_rows_multi_kernel<<<dim3(static_cast<unsigned>(bx), rows, n_jobs), 256, 0, as_stream(stream)>>>(
+      jobs, src_pitch, dst_pitch, width16);
+  MODDIT_CHECK_LAUNCH("copy_rows_multi_kernel");
+  return MODDIT_OK;
+}
 
 extern "C" int moddit_copy_rows(const void* src, void* dst, int64_t src_pitch, int64_t dst_pitch, int64_t width_bytes,
                                 int rows, void* stream) {

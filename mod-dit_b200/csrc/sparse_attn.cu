@@ -44,6 +44,18 @@ enum BarrierIndex {
   kNumBarriers
 };
 
+// Optional destination of the output rows on a multi-GPU run: instead of one local (BH, N, D) tensor the
+// rows of sequence shard r (rows [r*rows_per_peer, (r+1)*rows_per_peer)) are stored straight into rank r's
+// (total_heads, rows_per_peer, D) buffer at head `head_base + bh` - the output re-shard is fused into the
+// epilogue as plain peer stores.
+constexpr int kMaxPeers = 8;
+struct OutScatter {
+  void* peer[kMaxPeers];
+  int n_peers;          // 0: write `out` locally
+  int rows_per_peer;
+  int head_base;
+};
+
 struct __align__(8) Control {
   unsigned long long bars[kNumBarriers];
   uint32_t tmem_base;
@@ -90,7 +102,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
     const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
     const __grid_constant__ CUtensorMap tm_v, const int32_t* __restrict__ counts,
     const int32_t* __restrict__ entries, const int32_t* __restrict__ order, int Hm, int ntk, int N, float scale_log2, int q_split, int kvl_lo,
-    int kvl_hi, void* __restrict__ out_raw, float* __restrict__ lse, int32_t* __restrict__ status) {
+    int kvl_hi, void* __restrict__ out_raw, float* __restrict__ lse, int32_t* __restrict__ status,
+    const __grid_constant__ OutScatter scatter) {
   constexpr int kTileBytes = kTile * D * 2;       // one Q, K or V tile
   constexpr int kChunks = D / 64;                 // 64-element (128-byte) column chunks per tile
   constexpr int kChunkBytes = kTile * 128;
@@ -429,8 +442,16 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
     if (ok && tile < ntq) {
       ptx::tc_fence_after();
       const float inv = (done > 0 && l > 0.f) ? 1.f / l : 0.f;
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(out_raw) +
-                                            (static_cast<int64_t>(bh) * N + grow) * D * 2);
+      uint4* dst;
+      if (scatter.n_peers > 0) {
+        const int r = min(grow / scatter.rows_per_peer, scatter.n_peers - 1);
+        dst = reinterpret_cast<uint4*>(
+            static_cast<unsigned char*>(scatter.peer[r]) +
+            (static_cast<int64_t>(scatter.head_base + bh) * scatter.rows_per_peer + (grow - r * scatter.rows_per_peer)) * D * 2);
+      } else {
+        dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(out_raw) +
+                                       (static_cast<int64_t>(bh) * N + grow) * D * 2);
+      }
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         float o[32];
@@ -471,7 +492,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
 template <int D, bool kBF16>
 int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N, const int32_t* counts,
            const int32_t* entries, const int32_t* order, int Hm, float softmax_scale, int q_split, int kvl_lo, int kvl_hi, void* out,
-           float* lse, int32_t* status, cudaStream_t st) {
+           float* lse, int32_t* status, const OutScatter& scatter, cudaStream_t st) {
   CUtensorMap tq, tk, tv;
   if (int rc = make_tmap_rows(&tq, q, dtype, BH, N, D, kTile)) return rc;
   if (int rc = make_tmap_rows(&tk, k, dtype, BH, N, D, kTile)) return rc;
@@ -483,7 +504,7 @@ int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N
   MODDIT_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   const float scale_log2 = softmax_scale * 1.4426950408889634f;
   kernel<<<dim3(npairs, BH), kThreads, smem, st>>>(tq, tk, tv, counts, entries, order, Hm, ntq, N, scale_log2, q_split,
-                                                   kvl_lo, kvl_hi, out, lse, status);
+                                                   kvl_lo, kvl_hi, out, lse, status, scatter);
   MODDIT_CHECK_LAUNCH("sparse_attn_fwd_kernel");
   return MODDIT_OK;
 }
@@ -503,13 +524,12 @@ extern "C" int moddit_debug_profile(unsigned long long* host32) {
 }
 #endif
 
-extern "C" int moddit_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
-                                      const int32_t* counts, const int32_t* entries, const int32_t* order, int Hm,
-                                      float softmax_scale,
-                                      int q_split, int kv_len_lo, int kv_len_hi, void* out, float* lse,
-                                      int32_t* status, void* stream) {
-  clear_error();
-  MODDIT_CHECK_ARG(q && k && v && out && counts && entries && status, "sparse_attn_fwd: null pointer");
+static int sparse_attn_dispatch(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
+                                const int32_t* counts, const int32_t* entries, const int32_t* order, int Hm,
+                                float softmax_scale, int q_split, int kv_len_lo, int kv_len_hi, void* out, float* lse,
+                                int32_t* status, const OutScatter& scatter, void* stream) {
+  MODDIT_CHECK_ARG(q && k && v && counts && entries && status, "sparse_attn_fwd: null pointer");
+  MODDIT_CHECK_ARG(out || scatter.n_peers > 0, "sparse_attn_fwd: no output destination");
   MODDIT_CHECK_ARG(BH > 0 && BH <= 65535 && N > 0 && Hm > 0, "sparse_attn_fwd: BH=%d N=%d Hm=%d out of range", BH, N, Hm);
   MODDIT_CHECK_ARG(BH % Hm == 0, "sparse_attn_fwd: BH=%d is not a multiple of the mask heads Hm=%d", BH, Hm);
   MODDIT_CHECK_ARG(softmax_scale > 0.f, "sparse_attn_fwd: softmax_scale must be positive");
@@ -524,12 +544,46 @@ extern "C" int moddit_sparse_attn_fwd(const void* q, const void* k, const void* 
   if (D == 128) {
     return dtype == MODDIT_BF16
                ? launch<128, true>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split, kv_len_lo,
-                                   kv_len_hi, out, lse, status, st)
+                                   kv_len_hi, out, lse, status, scatter, st)
                : launch<128, false>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split, kv_len_lo,
-                                    kv_len_hi, out, lse, status, st);
+                                    kv_len_hi, out, lse, status, scatter, st);
   }
   return dtype == MODDIT_BF16 ? launch<64, true>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split,
-                                                 kv_len_lo, kv_len_hi, out, lse, status, st)
+                                                 kv_len_lo, kv_len_hi, out, lse, status, scatter, st)
                               : launch<64, false>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split,
-                                                  kv_len_lo, kv_len_hi, out, lse, status, st);
+                                                  kv_len_lo, kv_len_hi, out, lse, status, scatter, st);
+}
+
+extern "C" int moddit_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
+                                      const int32_t* counts, const int32_t* entries, const int32_t* order, int Hm,
+                                      float softmax_scale, int q_split, int kv_len_lo, int kv_len_hi, void* out,
+                                      float* lse, int32_t* status, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(out, "sparse_attn_fwd: null output pointer");
+  OutScatter none = {};
+  return sparse_attn_dispatch(q, k, v, dtype, BH, N, D, counts, entries, order, Hm, softmax_scale, q_split, kv_len_lo,
+                              kv_len_hi, out, lse, status, none, stream);
+}
+
+extern "C" int moddit_sparse_attn_fwd_scatter(const void* q, const void* k, const void* v, int dtype, int BH, int N,
+                                              int D, const int32_t* counts, const int32_t* entries,
+                                              const int32_t* order, int Hm, float softmax_scale, int q_split,
+                                              int kv_len_lo, int kv_len_hi, void* const* peer_out, int n_peers,
+                                              int head_base, float* lse, int32_t* status, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(peer_out, "sparse_attn_fwd_scatter: null peer table");
+  MODDIT_CHECK_ARG(n_peers >= 1 && n_peers <= kMaxPeers, "sparse_attn_fwd_scatter: n_peers=%d outside [1, %d]", n_peers,
+                   kMaxPeers);
+  MODDIT_CHECK_ARG(N % n_peers == 0, "sparse_attn_fwd_scatter: N=%d does not divide over %d peers", N, n_peers);
+  MODDIT_CHECK_ARG(head_base >= 0, "sparse_attn_fwd_scatter: head_base must be non-negative");
+  OutScatter sc = {};
+  for (int i = 0; i < n_peers; ++i) {
+    MODDIT_CHECK_ARG(peer_out[i] && aligned16(peer_out[i]), "sparse_attn_fwd_scatter: peer buffer %d null or unaligned", i);
+    sc.peer[i] = peer_out[i];
+  }
+  sc.n_peers = n_peers;
+  sc.rows_per_peer = N / n_peers;
+  sc.head_base = head_base;
+  return sparse_attn_dispatch(q, k, v, dtype, BH, N, D, counts, entries, order, Hm, softmax_scale, q_split, kv_len_lo,
+                              kv_len_hi, nullptr, lse, status, sc, stream);
 }

@@ -164,12 +164,15 @@ class PeerResharder:
         sync = self.in_handles[slots[0]]
         sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # readers of the previous contents are done
         row = self.ns * self.D * self.esize                            # bytes of one (head, sequence shard) piece
+        src, dst = [], []
         for step in range(self.world):
             peer = (self.rank + step) % self.world                     # start with the local piece, spread the rest
             for x, slot in zip(xs, slots):
-                src = x.data_ptr() + peer * self.hp * row
-                dst = int(self.in_handles[slot].buffer_ptrs[peer]) + self.rank * row
-                self._ops.copy_rows(src, dst, row, self.N * self.D * self.esize, row, self.hp, self.device)
+                src.append(x.data_ptr() + peer * self.hp * row)
+                dst.append(int(self.in_handles[slot].buffer_ptrs[peer]) + self.rank * row)
+        for i in range(0, len(src), 24):                               # one launch per 24 (peer, tensor) pairs
+            self._ops.copy_rows_multi(src[i:i + 24], dst[i:i + 24], row, self.N * self.D * self.esize, row, self.hp,
+                                      self.device)
         sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # every rank's stores have landed
         return [self.inputs[slot] for slot in slots]
 
@@ -180,10 +183,23 @@ class PeerResharder:
         hdl = self.out_handle
         hdl.barrier(channel=channel, timeout_ms=self.timeout_ms)
         row = self.ns * self.D * self.esize
+        src, dst = [], []
         for step in range(self.world):
             peer = (self.rank + step) % self.world
-            src = x.data_ptr() + peer * row
-            dst = int(hdl.buffer_ptrs[peer]) + self.rank * self.hp * row
-            self._ops.copy_rows(src, dst, self.N * self.D * self.esize, row, row, self.hp, self.device)
+            src.append(x.data_ptr() + peer * row)
+            dst.append(int(hdl.buffer_ptrs[peer]) + self.rank * self.hp * row)
+        self._ops.copy_rows_multi(src, dst, self.N * self.D * self.esize, row, row, self.hp, self.device)
         hdl.barrier(channel=channel, timeout_ms=self.timeout_ms)
+        return self.output
+
+    # ---- output re-shard fused into the attention kernel's epilogue ------------------------------------
+    def begin_output(self, channel: int = 0):
+        """Call before a kernel that stores its output rows straight into the peers' buffers; returns the
+        `scatter` argument for `ops.sparse_attn_fwd` (peer buffer pointers, first global head of this rank)."""
+        self.out_handle.barrier(channel=channel, timeout_ms=self.timeout_ms)   # previous output has been consumed
+        return [int(p) for p in self.out_handle.buffer_ptrs], self.rank * self.hp
+
+    def finish_output(self, channel: int = 0) -> torch.Tensor:
+        """Call after that kernel: once every rank's stores have landed the local (1, H, N/P, D) shard is valid."""
+        self.out_handle.barrier(channel=channel, timeout_ms=self.timeout_ms)
         return self.output

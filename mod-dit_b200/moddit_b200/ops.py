@@ -371,6 +371,17 @@ def copy_rows(src_ptr: int, dst_ptr: int, src_pitch: int, dst_pitch: int, width_
                                    width_bytes, rows, _stream(device)), "moddit_copy_rows")
 
 
+def copy_rows_multi(src_ptrs, dst_ptrs, src_pitch: int, dst_pitch: int, width_bytes: int, rows: int,
+                    device: torch.device) -> None:
+    """`copy_rows` for several (source, destination) pointer pairs in one launch."""
+    n = len(src_ptrs)
+    src = (ctypes.c_void_p * n)(*src_ptrs)
+    dst = (ctypes.c_void_p * n)(*dst_ptrs)
+    with torch.cuda.device(device), _timed("moddit_copy_rows", device):
+        check(lib.moddit_copy_rows_multi(src, dst, n, src_pitch, dst_pitch, width_bytes, rows, _stream(device)),
+              "moddit_copy_rows_multi")
+
+
 # ---------------------------------------------------------------------------------------------
 # sparse forward
 # ---------------------------------------------------------------------------------------------
@@ -404,7 +415,7 @@ def sparse_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, counts: t
                     softmax_scale: Optional[float] = None,
                     q_split: Optional[int] = None, kv_len_lo: Optional[int] = None,
                     kv_len_hi: Optional[int] = None, return_lse: bool = False, check_status: bool = True,
-                    out: Optional[torch.Tensor] = None):
+                    out: Optional[torch.Tensor] = None, scatter=None):
     """Block-sparse attention forward of (B,H,N,D) tensors over the work lists from `tile_lists`."""
     dev = _need_cuda(q, k, v, counts, entries)
     _need_contig(q=q, k=k, v=v, counts=counts, entries=entries)
@@ -420,10 +431,23 @@ def sparse_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, counts: t
                               or not order.is_contiguous() or order.device != dev):
         raise ValueError("order must be the contiguous int32 (Hm, npairs) tensor from tile_lists")
     scale = float(D ** -0.5 if softmax_scale is None else softmax_scale)
-    if out is None:
-        out = torch.empty_like(q)
     lse = torch.empty(B, H, N, device=dev, dtype=torch.float32) if return_lse else None
     st = _status_words(dev)
+    if scatter is not None:
+        # scatter = (peer buffer pointers, head_base): output rows go straight into the peers' buffers
+        peer_ptrs, head_base = scatter
+        table = (ctypes.c_void_p * len(peer_ptrs))(*peer_ptrs)
+        with torch.cuda.device(dev), _timed("moddit_sparse_attn_fwd", dev):
+            check(lib.moddit_sparse_attn_fwd_scatter(
+                _ptr(q), _ptr(k), _ptr(v), _qkv_dtype(q), B * H, N, D, _ptr(counts), _ptr(entries), _ptr(order), Hm,
+                scale, N if q_split is None else int(q_split), N if kv_len_lo is None else int(kv_len_lo),
+                N if kv_len_hi is None else int(kv_len_hi), table, len(peer_ptrs), int(head_base), _ptr(lse),
+                _ptr(st), _stream(dev)), "moddit_sparse_attn_fwd_scatter")
+        if check_status:
+            raise_on_status(dev)
+        return (None, lse) if return_lse else None
+    if out is None:
+        out = torch.empty_like(q)
     with torch.cuda.device(dev), _timed("moddit_sparse_attn_fwd", dev):
         check(lib.moddit_sparse_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _qkv_dtype(q), B * H, N, D, _ptr(counts),
                                          _ptr(entries), _ptr(order), Hm, scale, N if q_split is None else int(q_split),
