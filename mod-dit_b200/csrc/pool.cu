@@ -4,8 +4,9 @@
 // keeps eight fp32 column sums, row groups are combined through shared memory in a fixed order.
 // Algorithmic traffic: N*D*2 bytes read + ceil(N/bs)*D*4 bytes written per head.
 //
-// pooled_map: one CTA per (32 query blocks, head): fp32 logits against all key blocks are kept in
-// shared memory, then each warp normalises its rows and writes 1 - softmax as float16.
+// pooled_map: one CTA per (32 query blocks, head): fp32 logits against all key blocks (4x4 register
+// tiles, 128-bit shared-memory loads) are kept in shared memory, then each warp normalises its rows and
+// writes 1 - softmax as float16.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -87,87 +88,103 @@ __global__ void __launch_bounds__(kPoolThreads) pool_blocks_kernel(const T* __re
 }
 
 constexpr int kMapThreads = 256;
-constexpr int kMapCols = 64;   // key blocks per staged tile
+constexpr int kMapRows = 32;    // query blocks per CTA
+constexpr int kMapCols = 128;   // key blocks per staged tile
 
-// ROWS query blocks per CTA; every thread owns (ROWS/16) rows x 4 columns of the staged 64-column tile.
-template <int ROWS>
+// Every thread owns a 4 x 4 patch of the 32 x 128 logit tile and walks the head dimension four floats at
+// a time with 128-bit shared-memory loads (rows padded by four floats: conflict-free for the key tile,
+// broadcast for the query rows).
 __global__ void __launch_bounds__(kMapThreads) pooled_map_kernel(const float* __restrict__ qbar,
                                                                  const float* __restrict__ kbar, int nb, int D,
                                                                  int q_off, int k_off, int n, float scale,
                                                                  __half* __restrict__ map) {
-  constexpr int kRpt = ROWS / 16;               // rows per thread
-  extern __shared__ float smem[];
-  float* qs = smem;                             // [ROWS][D+1]
-  float* ks = qs + ROWS * (D + 1);              // [kMapCols][D+1]
-  float* lg = ks + kMapCols * (D + 1);          // [ROWS][n]
+  extern __shared__ __align__(16) float smem[];
+  const int ld = D + 4;
+  float* qs = smem;                             // [kMapRows][ld]
+  float* ks = qs + kMapRows * ld;               // [kMapCols][ld]
+  float* lg = ks + kMapCols * ld;               // [kMapRows][n]
 
   const int bh = blockIdx.y;
-  const int i0 = blockIdx.x * ROWS;
+  const int i0 = blockIdx.x * kMapRows;
   const int tid = threadIdx.x;
   const float* qh = qbar + (static_cast<int64_t>(bh) * nb + q_off) * D;
   const float* kh = kbar + (static_cast<int64_t>(bh) * nb + k_off) * D;
+  const int d4 = D / 4;
 
-  for (int e = tid; e < ROWS * D; e += kMapThreads) {
-    const int r = e / D, d = e - r * D;
-    qs[r * (D + 1) + d] = (i0 + r < n) ? qh[static_cast<int64_t>(i0 + r) * D + d] * scale : 0.f;
+  for (int e = tid; e < kMapRows * d4; e += kMapThreads) {
+    const int r = e / d4, c = e - r * d4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i0 + r < n) v = __ldg(reinterpret_cast<const float4*>(qh + static_cast<int64_t>(i0 + r) * D) + c);
+    v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+    *reinterpret_cast<float4*>(qs + r * ld + 4 * c) = v;
   }
-  const int tc = tid % 16;                      // column lane: columns tc, tc+16, tc+32, tc+48
-  const int tr = tid / 16;                      // row lane: rows tr, tr+16, ...
+  const int tc = tid % 32;                      // columns tc, tc+32, tc+64, tc+96 of the tile
+  const int tr = tid / 32;                      // rows 4*tr .. 4*tr+3
   for (int j0 = 0; j0 < n; j0 += kMapCols) {
     __syncthreads();
-    for (int e = tid; e < kMapCols * D; e += kMapThreads) {
-      const int c = e / D, d = e - c * D;
-      ks[c * (D + 1) + d] = (j0 + c < n) ? kh[static_cast<int64_t>(j0 + c) * D + d] : 0.f;
+    for (int e = tid; e < kMapCols * d4; e += kMapThreads) {
+      const int r = e / d4, c = e - r * d4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j0 + r < n) v = __ldg(reinterpret_cast<const float4*>(kh + static_cast<int64_t>(j0 + r) * D) + c);
+      *reinterpret_cast<float4*>(ks + r * ld + 4 * c) = v;
     }
     __syncthreads();
-    float acc[kRpt][4];
+    float acc[4][4];
 #pragma unroll
-    for (int a = 0; a < kRpt; ++a)
+    for (int a = 0; a < 4; ++a)
 #pragma unroll
       for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
-    for (int d = 0; d < D; ++d) {
-      float qv[kRpt], kv[4];
+    for (int d = 0; d < D; d += 4) {
+      float4 qv[4], kv[4];
 #pragma unroll
-      for (int a = 0; a < kRpt; ++a) qv[a] = qs[(tr + 16 * a) * (D + 1) + d];
+      for (int a = 0; a < 4; ++a) qv[a] = *reinterpret_cast<const float4*>(qs + (4 * tr + a) * ld + d);
 #pragma unroll
-      for (int b = 0; b < 4; ++b) kv[b] = ks[(tc + 16 * b) * (D + 1) + d];
+      for (int b = 0; b < 4; ++b) kv[b] = *reinterpret_cast<const float4*>(ks + (tc + 32 * b) * ld + d);
 #pragma unroll
-      for (int a = 0; a < kRpt; ++a)
+      for (int a = 0; a < 4; ++a)
 #pragma unroll
-        for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(qv[a], kv[b], acc[a][b]);
+        for (int b = 0; b < 4; ++b) {
+          acc[a][b] = fmaf(qv[a].x, kv[b].x, acc[a][b]);
+          acc[a][b] = fmaf(qv[a].y, kv[b].y, acc[a][b]);
+          acc[a][b] = fmaf(qv[a].z, kv[b].z, acc[a][b]);
+          acc[a][b] = fmaf(qv[a].w, kv[b].w, acc[a][b]);
+        }
     }
 #pragma unroll
-    for (int a = 0; a < kRpt; ++a)
+    for (int a = 0; a < 4; ++a)
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        const int j = j0 + tc + 16 * b;
-        if (j < n) lg[(tr + 16 * a) * n + j] = acc[a][b];
+        const int j = j0 + tc + 32 * b;
+        if (j < n) lg[(4 * tr + a) * n + j] = acc[a][b];
       }
   }
   __syncthreads();
-  // row softmax: warp w handles rows w, w+8, ...
+  // row softmax: warp w handles rows w, w+8, ...; the exponentials are kept in place for the second pass
   const int warp = tid / 32, lane = tid % 32;
-  for (int r = warp; r < ROWS; r += kMapThreads / 32) {
+  for (int r = warp; r < kMapRows; r += kMapThreads / 32) {
     const int i = i0 + r;
     if (i >= n) break;
-    const float* row = lg + r * n;
+    float* row = lg + r * n;
     float m = -INFINITY;
     for (int j = lane; j < n; j += 32) m = fmaxf(m, row[j]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     float s = 0.f;
-    for (int j = lane; j < n; j += 32) s += expf(row[j] - m);
+    for (int j = lane; j < n; j += 32) {
+      const float ex = expf(row[j] - m);
+      row[j] = ex;
+      s += ex;
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     const float inv = 1.f / s;
     __half* dst = map + (static_cast<int64_t>(bh) * n + i) * n;
-    for (int j = lane; j < n; j += 32) dst[j] = __float2half_rn(1.f - expf(row[j] - m) * inv);
+    for (int j = lane; j < n; j += 32) dst[j] = __float2half_rn(1.f - row[j] * inv);
   }
 }
 
-template <int ROWS>
 size_t pooled_map_smem(int D, int n) {
-  return sizeof(float) * (static_cast<size_t>(ROWS) * (D + 1) + kMapCols * (D + 1) + static_cast<size_t>(ROWS) * n);
+  return sizeof(float) * (static_cast<size_t>(kMapRows + kMapCols) * (D + 4) + static_cast<size_t>(kMapRows) * n);
 }
 
 }  // namespace
@@ -219,22 +236,15 @@ extern "C" int moddit_pooled_map(const float* qbar, const float* kbar, int BH, i
   if (int rc = require_sm100()) return rc;
   cudaStream_t st = as_stream(stream);
   __half* map = static_cast<__half*>(map_f16);
-  const size_t limit = 227 * 1024;
-  if (pooled_map_smem<32>(D, n) <= limit) {
-    const size_t sm = pooled_map_smem<32>(D, n);
-    MODDIT_CHECK_CUDA(cudaFuncSetAttribute(pooled_map_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(sm)));
-    pooled_map_kernel<32><<<dim3(ceil_div(n, 32), BH), kMapThreads, sm, st>>>(qbar, kbar, nb, D, q_block_offset,
-                                                                               k_block_offset, n, scale, map);
-  } else if (pooled_map_smem<16>(D, n) <= limit) {
-    const size_t sm = pooled_map_smem<16>(D, n);
-    MODDIT_CHECK_CUDA(cudaFuncSetAttribute(pooled_map_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(sm)));
-    pooled_map_kernel<16><<<dim3(ceil_div(n, 16), BH), kMapThreads, sm, st>>>(qbar, kbar, nb, D, q_block_offset,
-                                                                               k_block_offset, n, scale, map);
-  } else {
+  const size_t sm = pooled_map_smem(D, n);
+  if ((D & 3) != 0 || !aligned16(qbar) || !aligned16(kbar))
+    return fail(MODDIT_E_ALIGN, "pooled_map: head_dim must be a multiple of 4 and the inputs 16-byte aligned");
+  if (sm > 227 * 1024)
     return fail(MODDIT_E_UNSUPPORTED, "pooled_map: n=%d video blocks do not fit the shared-memory row buffer", n);
-  }
+  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(pooled_map_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(sm)));
+  pooled_map_kernel<<<dim3(ceil_div(n, kMapRows), BH), kMapThreads, sm, st>>>(qbar, kbar, nb, D, q_block_offset,
+                                                                               k_block_offset, n, scale, map);
   MODDIT_CHECK_LAUNCH("pooled_map_kernel");
   return MODDIT_OK;
 }
