@@ -269,7 +269,7 @@ __global__ void gj_update_kernel(double* __restrict__ A, int m, int k, const dou
 }
 
 // ---- per-call solve -----------------------------------------------------------------------------
-// workspace (doubles): g[H][n+1] | y[H][n+1]
+// workspace (doubles): g[H][n+1] | y[kGemvSplit][H][n+1] (partial products per slice of the inner index)
 
 constexpr int kSolveThreads = 512;
 
@@ -329,27 +329,34 @@ __global__ void __launch_bounds__(kSolveThreads) solve_rhs_kernel(const float* _
   if (threadIdx.x == 0) gh[n] = static_cast<double>(r[nd + n]) - dot;
 }
 
-// y = Sinv * g for one head; Sinv is symmetric, so thread i walks column i (coalesced across threads).
+// y_slice = Sinv[j0:j1, :]^T * g[j0:j1] for one head and one slice of the inner index (Sinv is symmetric, so
+// thread i walks column i and consecutive threads read consecutive addresses).  The inner index is split
+// over blockIdx.z so that the whole GPU takes part: a single pass over it is bound by load latency.
+constexpr int kGemvSplit = 16;
 __global__ void __launch_bounds__(128) solve_gemv_kernel(const double* __restrict__ Sinv,
                                                          const double* __restrict__ g, int m,
                                                          double* __restrict__ y) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* gs = reinterpret_cast<double*>(smem_raw);
   const int h = blockIdx.y;
-  for (int j = threadIdx.x; j < m; j += blockDim.x) gs[j] = g[static_cast<int64_t>(h) * m + j];
+  const int per = (m + kGemvSplit - 1) / kGemvSplit;
+  const int j0 = blockIdx.z * per;
+  const int j1 = min(m, j0 + per);
+  for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) gs[j - j0] = g[static_cast<int64_t>(h) * m + j];
   __syncthreads();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= m) return;
   double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
-  int j = 0;
-  for (; j + 3 < m; j += 4) {
-    a0 = fma(Sinv[static_cast<int64_t>(j) * m + i], gs[j], a0);
-    a1 = fma(Sinv[static_cast<int64_t>(j + 1) * m + i], gs[j + 1], a1);
-    a2 = fma(Sinv[static_cast<int64_t>(j + 2) * m + i], gs[j + 2], a2);
-    a3 = fma(Sinv[static_cast<int64_t>(j + 3) * m + i], gs[j + 3], a3);
+  int j = j0;
+  for (; j + 3 < j1; j += 4) {
+    a0 = fma(Sinv[static_cast<int64_t>(j) * m + i], gs[j - j0], a0);
+    a1 = fma(Sinv[static_cast<int64_t>(j + 1) * m + i], gs[j + 1 - j0], a1);
+    a2 = fma(Sinv[static_cast<int64_t>(j + 2) * m + i], gs[j + 2 - j0], a2);
+    a3 = fma(Sinv[static_cast<int64_t>(j + 3) * m + i], gs[j + 3 - j0], a3);
   }
-  for (; j < m; ++j) a0 = fma(Sinv[static_cast<int64_t>(j) * m + i], gs[j], a0);
-  y[static_cast<int64_t>(h) * m + i] = (a0 + a1) + (a2 + a3);
+  for (; j < j1; ++j) a0 = fma(Sinv[static_cast<int64_t>(j) * m + i], gs[j - j0], a0);
+  // slice partial: y is laid out [slice][head][m]; the back-substitution adds the slices in a fixed order
+  y[(static_cast<int64_t>(blockIdx.z) * gridDim.y + h) * m + i] = (a0 + a1) + (a2 + a3);
 }
 
 __global__ void __launch_bounds__(kSolveThreads) solve_back_kernel(const float* __restrict__ mts,
@@ -361,15 +368,22 @@ __global__ void __launch_bounds__(kSolveThreads) solve_back_kernel(const float* 
   double* pc = reinterpret_cast<double*>(smem_raw);  // [n] inclusive prefix of c
   double* carry = pc + n;                            // [kSolveThreads]
   const int h = blockIdx.x;
+  const int H = gridDim.x;
   const int nd = 2 * n - 1;
-  const double* yh = y + static_cast<int64_t>(h) * (n + 1);
+  const int m = n + 1;
   const float* r = mts + static_cast<int64_t>(h) * 3 * n;
   float* xh = X + static_cast<int64_t>(h) * 3 * n;
+  auto y_at = [&](int j) {          // sum of the gemv slices, always in the same order
+    double acc = 0.0;
+    for (int sl = 0; sl < kGemvSplit; ++sl) acc += y[(static_cast<int64_t>(sl) * H + h) * m + j];
+    return acc;
+  };
   for (int j = threadIdx.x; j < n; j += kSolveThreads) {
-    pc[j] = yh[j];
-    xh[nd + j] = static_cast<float>(yh[j]);
+    const double yj = y_at(j);
+    pc[j] = yj;
+    xh[nd + j] = static_cast<float>(yj);
   }
-  const double e = yh[n];
+  const double e = y_at(n);
   if (threadIdx.x == 0) xh[nd + n] = static_cast<float>(e);
   __syncthreads();
   block_scan_inclusive(pc, n, carry);
@@ -555,7 +569,7 @@ extern "C" int moddit_solve_prepare(int n, int blocks_per_frame, double regulari
 
 extern "C" size_t moddit_solve_workspace_bytes(int H, int n) {
   if (H <= 0 || n <= 0) return 0;
-  return sizeof(double) * 2 * static_cast<size_t>(H) * (static_cast<size_t>(n) + 1);
+  return sizeof(double) * (1 + kGemvSplit) * static_cast<size_t>(H) * (static_cast<size_t>(n) + 1);
 }
 
 extern "C" int moddit_solve(const float* mts, const void* factor, int H, int n, int blocks_per_frame,
@@ -585,7 +599,8 @@ extern "C" int moddit_solve(const float* mts, const void* factor, int H, int n, 
                                          static_cast<int>(sm_rhs)));
   solve_rhs_kernel<<<H, kSolveThreads, sm_rhs, st>>>(mts, w, wb, n, g);
   MODDIT_CHECK_LAUNCH("solve_rhs_kernel");
-  solve_gemv_kernel<<<dim3(ceil_div(m, 128), H), 128, sizeof(double) * m, st>>>(Sinv, g, m, y);
+  solve_gemv_kernel<<<dim3(ceil_div(m, 128), H, kGemvSplit), 128, sizeof(double) * ceil_div(m, kGemvSplit), st>>>(
+      Sinv, g, m, y);
   MODDIT_CHECK_LAUNCH("solve_gemv_kernel");
   solve_back_kernel<<<H, kSolveThreads, sm_back, st>>>(mts, w, wb, y, n, X);
   MODDIT_CHECK_LAUNCH("solve_back_kernel");

@@ -73,7 +73,7 @@ WORKLOADS = {
     "hunyuan": dict(model_type="hunyuan", heads=24, head_dim=128, block_size=128, grid=(30, 48, 80),
                     text_tokens=256, text_first=False, top_k=340, predict_T=5),
     "wan": dict(model_type="wan", heads=40, head_dim=128, block_size=128, grid=(18, 48, 80), text_tokens=0,
-                text_first=False, top_k=350, predict_T=10),
+                text_first=False, top_k=200, predict_T=10),
     "cogvideox": dict(model_type="cogvideox", heads=48, head_dim=64, block_size=64, grid=(11, 48, 84),
                       text_tokens=256, text_first=True, top_k=100, predict_T=5),
     "medium": dict(model_type="hunyuan", heads=8, head_dim=128, block_size=128, grid=(8, 64, 64), text_tokens=256,
