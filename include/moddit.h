@@ -58,9 +58,9 @@ const char* moddit_last_error_string(void);
 int moddit_pool_blocks(const void* x, int dtype, int BH, int N, int D, int block_size,
                        float* out, void* stream);
 
-/* Pooled stand-in for the sparsity map: map[h,i,j] = 1 - softmax_j(qbar[h,qo+i,:].kbar[h,ko+j,:]*scale)
- * over the n video blocks, written as float16 (no reference function; consumed exactly like the
- * reference map of MoD/mod/triton_flash_sparsity.py:275-341).
+/* Pooled stand-in for the sparsity map: with l_ij = qbar[h,qo+i,:].kbar[h,ko+j,:]*scale over the n video
+ * blocks, map[h,i,j] = 1 - exp(l_ij - max_j l_ij), written as float16 (no reference function; consumed
+ * exactly like the reference map of MoD/mod/triton_flash_sparsity.py:275-341: 1 = nothing there).
  *   qbar,kbar : (BH, nb, D) float32      map : (BH, n, n) float16
  */
 int moddit_pooled_map(const float* qbar, const float* kbar, int BH, int nb, int D,

@@ -6,7 +6,8 @@
 //
 // pooled_map: one CTA per (32 query blocks, head): fp32 logits against all key blocks (4x4 register
 // tiles, 128-bit shared-memory loads) are kept in shared memory, then each warp normalises its rows and
-// writes 1 - softmax as float16.
+// writes 1 - exp(logit - row maximum) as float16 (0 at the brightest block of a row, 1 where there is nothing;
+// relative to the row maximum so that the float16 grid resolves the bright blocks).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -159,27 +160,18 @@ __global__ void __launch_bounds__(kMapThreads) pooled_map_kernel(const float* __
       }
   }
   __syncthreads();
-  // row softmax: warp w handles rows w, w+8, ...; the exponentials are kept in place for the second pass
+  // per row: darkness = 1 - exp(logit - row maximum); warp w handles rows w, w+8, ...
   const int warp = tid / 32, lane = tid % 32;
   for (int r = warp; r < kMapRows; r += kMapThreads / 32) {
     const int i = i0 + r;
     if (i >= n) break;
-    float* row = lg + r * n;
+    const float* row = lg + r * n;
     float m = -INFINITY;
     for (int j = lane; j < n; j += 32) m = fmaxf(m, row[j]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    float s = 0.f;
-    for (int j = lane; j < n; j += 32) {
-      const float ex = expf(row[j] - m);
-      row[j] = ex;
-      s += ex;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    const float inv = 1.f / s;
     __half* dst = map + (static_cast<int64_t>(bh) * n + i) * n;
-    for (int j = lane; j < n; j += 32) dst[j] = __float2half_rn(1.f - row[j] * inv);
+    for (int j = lane; j < n; j += 32) dst[j] = __float2half_rn(1.f - expf(row[j] - m));
   }
 }
 

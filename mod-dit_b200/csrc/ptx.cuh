@@ -202,18 +202,5 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
-// 2^x on the FMA/ALU pipes (no MUFU): floor(x) goes to the exponent field, a cubic approximates 2^frac
-// (relative error below 1e-4, far under the 16-bit rounding of the probabilities that use it).
-// Valid for x <= 127; inputs below -127 (including -inf) give a denormal, i.e. effectively zero.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -127.f);
-  float t;
-  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(x), "f"(12582912.f));   // 1.5 * 2^23: integer part lands in the low bits
-  const float n = t - 12582912.f;
-  const float f = x - n;   // [0, 1)
-  const float p = fmaf(fmaf(fmaf(0.077119f, f, 0.227564f), f, 0.695146f), f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
 }  // namespace ptx
 }  // namespace moddit

@@ -116,7 +116,7 @@ def pool_blocks(x: torch.Tensor, block_size: int) -> torch.Tensor:
 
 def pooled_map(qbar: torch.Tensor, kbar: torch.Tensor, *, q_block_offset: int, k_block_offset: int,
                video_blocks: int, scale: float) -> torch.Tensor:
-    """(B,H,nb,D) float32 block means -> (B,H,n,n) float16 darkness map (1 - row softmax)."""
+    """(B,H,nb,D) float32 block means -> (B,H,n,n) float16 darkness map, 1 - exp(logit - row maximum)."""
     dev = _need_cuda(qbar, kbar)
     _need_contig(qbar=qbar, kbar=kbar)
     if qbar.dtype != torch.float32 or kbar.dtype != torch.float32 or qbar.shape != kbar.shape:

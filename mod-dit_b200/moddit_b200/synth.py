@@ -71,7 +71,7 @@ def make_qkv(*, heads: int, grid: Tuple[int, int, int], head_dim: int, text_toke
 WORKLOADS = {
     # name: model_type, heads, head_dim, block, grid (T,Hh,Ww), text tokens, text first, top_k, predict_T
     "hunyuan": dict(model_type="hunyuan", heads=24, head_dim=128, block_size=128, grid=(30, 48, 80),
-                    text_tokens=256, text_first=False, top_k=340, predict_T=5),
+                    text_tokens=256, text_first=False, top_k=300, predict_T=5),
     "wan": dict(model_type="wan", heads=40, head_dim=128, block_size=128, grid=(18, 48, 80), text_tokens=0,
                 text_first=False, top_k=200, predict_T=10),
     "cogvideox": dict(model_type="cogvideox", heads=48, head_dim=64, block_size=64, grid=(11, 48, 84),

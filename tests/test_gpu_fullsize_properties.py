@@ -1,0 +1,178 @@
+"""Checks at the benchmark's full HunyuanVideo shape (24 heads x 115,456 tokens x 128), where a full CPU
+oracle run would take hours: size-independent properties, torch-on-GPU restatements of the cheap stages,
+and a one-head end-to-end comparison of the predicted mask against the CPU oracle."""
+import pytest
+import torch
+
+from oracle import moddit_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+H, D, BS = 24, 128, 128
+GRID = (30, 48, 80)
+TEXT = 256
+VIDEO = GRID[0] * GRID[1] * GRID[2]
+N = VIDEO + TEXT
+NV = VIDEO // BS           # 900 video blocks
+NB = N // BS               # 902 blocks
+BPF = GRID[1] * GRID[2] // BS
+
+
+@pytest.fixture(scope="module")
+def env():
+    from moddit_b200 import ops, synth
+    q, k, v = synth.make_qkv(heads=H, grid=GRID, head_dim=D, text_tokens=TEXT, seed=1, gain=2.0)
+    return dict(ops=ops, q=q, k=k, v=v)
+
+
+@pytest.fixture(scope="module")
+def predicted(env):
+    """Pooled map -> fit -> selection -> mask -> lists on the device, for all 24 heads."""
+    ops = env["ops"]
+    qbar, kbar = ops.pool_blocks(env["q"], BS), ops.pool_blocks(env["k"], BS)
+    dark = ops.pooled_map(qbar, kbar, q_block_offset=0, k_block_offset=0, video_blocks=NV, scale=D ** -0.5)[0]
+    mts, _ = ops.mts(dark, BPF)
+    X = ops.solve(mts, NV, BPF, 1.0)
+    nd = 2 * NV - 1
+    feats = {"d": X[:, :nd].contiguous(), "c": (X[:, nd:nd + NV] / 2).contiguous(), "b_d": X[:, -1].contiguous()}
+    zero = {k_: torch.zeros_like(v_) for k_, v_ in feats.items()}
+    lines = ops.select_lines(feats["c"], feats["d"], zero["c"], zero["d"], 300, 5)
+    modes = ops.head_modes(feats["b_d"], 1.0)
+    mask = ops.mask_from_lines(lines, modes, n=NV, blocks_per_frame=BPF, model_type="hunyuan", text_blocks=TEXT // BS,
+                               total_blocks=NB)
+    lists = ops.tile_lists(mask, BS, N)
+    return dict(qbar=qbar, kbar=kbar, dark=dark, mts=mts, X=X, feats=feats, lines=lines, modes=modes, mask=mask,
+                lists=lists)
+
+
+def test_pooling_and_line_sums_match_torch_restatements(env, predicted):
+    x = env["q"]
+    ref = x[0].float().view(H, NB, BS, D).mean(dim=2)
+    assert torch.allclose(predicted["qbar"][0], ref, rtol=1e-5, atol=1e-6)
+    dark = predicted["dark"].float()
+    mts = predicted["mts"]
+    nd = 2 * NV - 1
+    assert torch.allclose(mts[:, nd:nd + NV], dark.sum(dim=1), rtol=1e-6, atol=1e-4)          # column sums
+    assert torch.allclose(mts[:, NV - 1], torch.diagonal(dark, dim1=1, dim2=2).sum(-1), rtol=1e-6, atol=1e-4)
+    assert torch.allclose(mts[:, :nd].sum(1), dark.sum(dim=(1, 2)), rtol=1e-5)                # diagonals partition the map
+    rows = torch.arange(NV, device=dark.device)
+    same = (rows.view(-1, 1) // BPF) == (rows.view(1, -1) // BPF)
+    assert torch.allclose(mts[:, -1], (dark * same).sum(dim=(1, 2)), rtol=1e-5)
+    # the solution satisfies the normal equations: M^T (M X) + X = M^T S, checked through the oracle's basis
+    X = predicted["X"].cpu().double()
+    rec = orc.reconstruct_map(X[:2], NV, BPF)
+    lhs = orc.compute_mts(rec, BPF).double() + X[:2]
+    assert torch.allclose(lhs, mts[:2].cpu().double(), rtol=1e-4, atol=2e-3)
+
+
+def test_selection_mask_and_lists_bit_exact_at_full_size(predicted):
+    f = {k_: v_.cpu() for k_, v_ in predicted["feats"].items()}
+    zero = {k_: torch.zeros_like(v_) for k_, v_ in f.items()}
+    lines = orc.choose_topk_lines(zero, f, 300, 5)
+    assert torch.equal(predicted["lines"].cpu(), lines)
+    mode = orc.check_bd_values(f["b_d"], 1.0)
+    mask = orc.generate_mask_from_lines(model_type="hunyuan", block_size=BS, video_token_num=VIDEO, text_token_num=TEXT,
+                                        seq_len=N, blocks_per_frame=BPF, selected_lines=lines, mode=mode)
+    assert torch.equal(predicted["mask"].cpu(), mask)
+    # work lists re-encode the mask (two heads through the slow oracle loops)
+    counts, entries = orc.build_tile_lists(mask[:2], BS, N)
+    assert torch.equal(predicted["lists"].counts[:2].cpu(), torch.from_numpy(counts))
+    got = predicted["lists"].entries[:2].cpu().numpy()
+    for h in range(2):
+        for p in range(counts.shape[1]):
+            assert (got[h, p, :counts[h, p]] == entries[h, p, :counts[h, p]]).all()
+    sparsity = 1.0 - mask.float().mean().item()
+    assert 0.80 <= sparsity <= 0.86, sparsity            # the band the benchmark configuration states
+
+
+def test_one_head_end_to_end_mask_agrees_with_cpu_oracle(env, predicted):
+    """Same input, whole prediction chain on the CPU oracle (fp32 dense solve) for one head: >= 99.9 % of blocks."""
+    h = 5
+    q1, k1 = env["q"][:, h:h + 1].cpu(), env["k"][:, h:h + 1].cpu()
+    dark = orc.pooled_darkness_map(orc.pool_blocks(q1, BS), orc.pool_blocks(k1, BS), q_block_offset=0,
+                                   k_block_offset=0, video_blocks=NV, scale=D ** -0.5)[0]
+    assert (dark.float() - predicted["dark"][h:h + 1].cpu().float()).abs().max().item() <= 2e-3
+    agree = {}
+    for precise in (False, True):
+        f = orc.solve_features(orc.compute_mts(dark, BPF), NV, BPF, 1.0, precise=precise)
+        f = {k_: f[k_].float() for k_ in ("c", "d", "b_d")}
+        zero = {k_: torch.zeros_like(f[k_]) for k_ in ("c", "d")}
+        lines = orc.choose_topk_lines(zero, f, 300, 5)
+        mask = orc.generate_mask_from_lines(model_type="hunyuan", block_size=BS, video_token_num=VIDEO,
+                                            text_token_num=TEXT, seq_len=N, blocks_per_frame=BPF, selected_lines=lines,
+                                            mode=orc.check_bd_values(f["b_d"], 1.0))
+        agree[precise] = (mask[0] == predicted["mask"][h].cpu()).float().mean().item()
+        same_lines = len(set(lines[0].tolist()) & set(predicted["lines"][h].tolist()))
+        print(f"oracle solve {'float64' if precise else 'float32 (reference arithmetic)'}: "
+              f"{same_lines}/300 lines shared, {agree[precise]:.5f} of blocks agree")
+    # The fitted values of the many short far-off diagonals are nearly equal, so which of them make the cut
+    # at rank 300 depends on the last bits of the solve: against a float64 solve of the same system the
+    # device agrees on at least 99.9 % of blocks; the reference's own float32 factorisation moves a few
+    # near-tied lines (each is one short diagonal, ~0.02 % of the blocks).
+    assert agree[True] >= 0.999, agree
+    assert agree[False] >= 0.995, agree
+
+
+def test_sparse_forward_properties_at_full_size(env, predicted):
+    ops = env["ops"]
+    q, k, v = env["q"], env["k"], env["v"]
+    lists = predicted["lists"]
+    kw = dict(order=lists.order)
+    # (1) rows of P sum to one: with V = 1 every output element is 1
+    ones = torch.ones_like(v)
+    out = ops.sparse_attn_fwd(q, k, ones, lists.counts, lists.entries, **kw)
+    assert (out.float() - 1.0).abs().max().item() <= 2 ** -7
+    # (2) with Q = 0 the probabilities are uniform over the kept keys: output = mean of V over the kept blocks
+    vbar = ops.pool_blocks(v, BS)[0]                                           # (H, NB, D) block means
+    keep = predicted["mask"].float()                                           # (H, NB, NB)
+    ref = torch.bmm(keep, vbar) / keep.sum(-1, keepdim=True)                   # (H, NB, D)
+    out0 = ops.sparse_attn_fwd(torch.zeros_like(q), k, v, lists.counts, lists.entries, **kw)
+    got = out0[0].float().view(H, NB, BS, D)
+    assert (got - ref.unsqueeze(2)).abs().max().item() <= 5e-3
+    assert (got[:, :, :1] - got).abs().max().item() <= 4e-3                    # every row of a block sees the same keys
+    # (3) linearity in V
+    out_v = ops.sparse_attn_fwd(q, k, v, lists.counts, lists.entries, **kw)
+    out_2v = ops.sparse_attn_fwd(q, k, (2 * v.float()).to(v.dtype), lists.counts, lists.entries, **kw)
+    assert (out_2v.float() - 2 * out_v.float()).abs().max().item() <= 3e-2
+    # (4) the launch order of the query-tile pairs does not change a single bit
+    assert torch.equal(out_v, ops.sparse_attn_fwd(q, k, v, lists.counts, lists.entries))
+    # (5) sample of rows against the fp32 oracle (one head, four query blocks incl. a text block)
+    hh = 7
+    blocks = [0, 431, 899, 901]
+    ref_rows = orc.masked_attention(q[:, hh:hh + 1].cpu(), k[:, hh:hh + 1].cpu(), v[:, hh:hh + 1].cpu(),
+                                    predicted["mask"][hh:hh + 1].cpu(), BS, row_blocks=blocks)
+    for b in blocks:
+        r = ref_rows[0, 0, b * BS:(b + 1) * BS]
+        g = out_v[0, hh, b * BS:(b + 1) * BS].float().cpu()
+        assert (g - r).abs().max().item() <= 2e-2
+        assert ((g - r).norm() / r.norm()).item() <= 1e-2
+    ops.raise_on_status(q.device)
+
+
+def test_dense_forward_lse_and_replay_at_full_size(env):
+    """Dense forward at 115k tokens: LSE against a float32 torch restatement on sampled rows; replay-map counts of
+    sampled blocks against the same restatement."""
+    from MoD.mod.triton_flash_sparsity import dense_attention_with_lse
+    ops = env["ops"]
+    q, k, v = env["q"], env["k"], env["v"]
+    out, lse = dense_attention_with_lse(q, k, v, D ** -0.5)
+    hh = 3
+    rows = torch.tensor([0, 1, 12345, 64000, 115199, 115200, 115455], device=q.device)
+    s = (q[0, hh, rows].float() @ k[0, hh].float().t()) * D ** -0.5
+    assert (torch.logsumexp(s, -1) - lse[0, hh, rows]).abs().max().item() <= 5e-3
+    ref = torch.softmax(s, -1) @ v[0, hh].float()
+    assert (out[0, hh, rows].float() - ref).abs().max().item() <= 2e-2
+    # replay map for one head, three query blocks, all key blocks
+    scale = D ** -0.5
+    log_thr = float(torch.log(torch.tensor(1e-4)))
+    qh, kh = q[:, hh:hh + 1].contiguous(), k[:, hh:hh + 1].contiguous()
+    lse_h = lse[:, hh:hh + 1].contiguous()
+    got = ops.replay_map(qh, kh, lse_h, softmax_scale=scale, log_threshold=log_thr, q_video_offset=0, k_video_offset=0,
+                         video_blocks=NV, block_size=BS)[0, 0]
+    assert ops.replay_status(q.device) == (0, 0, 0, 0)
+    qs = (qh[0, 0].float() * scale).to(q.dtype).float()
+    for i in (0, 450, 899):
+        sc = qs[i * BS:(i + 1) * BS] @ kh[0, 0, :VIDEO].float().t()
+        below = sc < (lse_h[0, 0, i * BS:(i + 1) * BS] + log_thr).unsqueeze(1)
+        cnt = below.view(BS, NV, BS).sum(dim=(0, 2)).float()
+        assert ((got[i].float() * BS * BS) - (cnt / (BS * BS)).half().float() * BS * BS).abs().max().item() <= 16.0
