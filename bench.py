@@ -161,25 +161,43 @@ def run_ours(args):
     state = make_state(cfg, he - hb)
 
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
-    resharder = mdist.PeerResharder(H, N, D, q_in.dtype, dev) if world > 1 else None
+    resharder, value_group = None, None
+    reshard = "none"
+    if world > 1:
+        try:
+            resharder = mdist.PeerResharder(H, N, D, q_in.dtype, dev)
+            reshard = "peer-memory copies + fused output scatter"
+        except Exception as exc:   # symmetric memory unavailable on this box: NCCL all-to-all does the same exchange
+            print(f"[bench] peer-memory re-shard unavailable ({exc!r}); using NCCL all-to-all", file=sys.stderr)
+            value_group = dist.new_group(backend="nccl")
+            reshard = "NCCL all-to-all"
 
     def layer(qs, ks, vs, step):
-        ready = None
+        ready, scatter = None, None
         if world > 1:
             main = torch.cuda.current_stream(dev)
             comm_stream.wait_stream(main)
             with torch.cuda.stream(comm_stream):
                 # value is not needed until the attention kernel: it travels while the mask is predicted
-                vs = resharder.seq_to_head(vs, 2, channel=1)
+                vs_h = (resharder.seq_to_head(vs, 2, channel=1) if resharder is not None
+                        else mdist.seq_to_head(vs, group=value_group))
                 ready = torch.cuda.Event()
                 ready.record(comm_stream)
-            qs, ks = resharder.seq_to_head_many([qs, ks], [0, 1], channel=0)
-        scatter = resharder.begin_output(channel=0) if world > 1 else None
+            if resharder is not None:
+                qs, ks = resharder.seq_to_head_many([qs, ks], [0, 1], channel=0)
+                scatter = resharder.begin_output(channel=0)
+            else:
+                qs, ks = mdist.seq_to_head(qs), mdist.seq_to_head(ks)
+            vs = vs_h
+            vs.record_stream(main)
         out, _ = SparseAttentionWithMap(qs, ks, vs, state, logger, current_step=step, value_ready=ready,
                                         output_scatter=scatter)
         if world > 1:
-            # sparse steps wrote their rows straight into the peers' buffers; dense (priming) steps did not
-            out = resharder.finish_output(channel=0) if out is None else resharder.head_to_seq(out, channel=0)
+            if resharder is None:
+                out = mdist.head_to_seq(out)
+            else:
+                # sparse steps wrote their rows straight into the peers' buffers; dense (priming) steps did not
+                out = resharder.finish_output(channel=0) if out is None else resharder.head_to_seq(out, channel=0)
         return out
 
     def barrier():
@@ -309,7 +327,7 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{args.workload}: B=1 H={H} D={D} N={N} block={bs} top_k={cfg['top_k']} "
                                    f"pooled mask prediction every step",
-                       "sparsity": round(sparsity_sum / world, 4), "parallelism": f"head-sharded x{world}",
+                       "sparsity": round(sparsity_sum / world, 4), "parallelism": f"head-sharded x{world}", "reshard": reshard,
                        "l2": "inputs larger than L2", "gain": args.gain, "seed": 1},
             "mask_pred_ms": round(pred_ms, 3), "mask_pred_pct": round(100.0 * pred_ms / max(pred_ms + attn_ms, 1e-9), 2),
             "attn_ms": round(attn_ms, 3), "reshard_copy_ms": round(comm_ms, 3),
