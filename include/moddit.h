@@ -175,7 +175,8 @@ int moddit_select_mass(const void* map_f16, int H, int n, float tau, uint8_t* ke
  * (2*row_half + col_half) marks a kept 64x64 quarter (block_size 128: 0 or 0xF).
  *   mask    : (Hm, nbq, nbk) bool bytes, blocks of `block_size` tokens on the grid that starts at token 0
  *   counts  : (Hm, npairs) int32      entries : (Hm, npairs, ntiles) int32,
- *   order   : NULL or (Hm, npairs) int32: the pairs of each head sorted by list length, longest first
+ *   order   : NULL or Hm*npairs int32: start order of the (head, pair) work items, order[pos] = head*npairs+pair:
+ *             the two longest pairs of every head first, then head after head with the longer lists first
  *             (ties by index); the sparse forward starts its blocks in this order
  *   npairs = ceil(ceil(N/128)/2), ntiles = ceil(N/128); key blocks >= kv_block_limit are dropped.
  * Re-encodes the mask that MoD/mod/attn_mask.py:297-317 hands to the third-party sparse kernel.
@@ -188,7 +189,7 @@ int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, int block_s
  * masks) and, with all-true lists and `lse` non-null, the dense pass of
  * MoD/mod/triton_flash_sparsity.py:314-324.
  *   q,k,v,out : (BH, N, D); head bh uses lists of mask head bh % Hm
- *   order     : NULL (pairs in index order) or the (Hm, npairs) order from moddit_tile_lists
+ *   order     : NULL (work items in index order) or the Hm*npairs start order from moddit_tile_lists
  *   rows < q_split attend keys < kv_len_lo, other rows keys < kv_len_hi
  *   lse       : NULL or (BH, N) float32 natural-log row log-sum-exp
  *   status    : device int32[4], zeroed by the caller; non-zero afterwards means a bounded wait

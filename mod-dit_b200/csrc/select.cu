@@ -228,16 +228,21 @@ __global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t*
   if (threadIdx.x == 0) counts[static_cast<int64_t>(h) * npairs + p] = base_s;
 }
 
-// Longest-first order of the query-tile pairs of one mask head (rank by counting; ties by index, so the
-// result is deterministic).  A pair with a long list (text rows keep every key tile) started last would
-// leave the other SMs idle at the end of the launch.
+// Start order of the (head, query-tile pair) work items of the sparse forward: order[pos] = head * npairs + pair.
+// Pairs are ranked by list length inside their head (rank by counting; ties by index, so the result is
+// deterministic).  The kLongFirst longest pairs of EVERY head come first (a pair of text rows keeps every key
+// tile and runs several times longer than the average pair: started late it would be the tail of the launch),
+// then head after head, longest first, so that one head's K and V stay in L2 while its pairs run.
+constexpr int kLongFirst = 2;
 __global__ void __launch_bounds__(256) order_pairs_kernel(const int32_t* __restrict__ counts, int npairs,
                                                           int32_t* __restrict__ order) {
   extern __shared__ int32_t cnt_s[];
   const int h = blockIdx.x;
+  const int Hm = gridDim.x;
   const int32_t* c = counts + static_cast<int64_t>(h) * npairs;
   for (int i = threadIdx.x; i < npairs; i += blockDim.x) cnt_s[i] = c[i];
   __syncthreads();
+  const int r0 = min(kLongFirst, npairs);
   for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
     const int ci = cnt_s[i];
     int rank = 0;
@@ -245,7 +250,9 @@ __global__ void __launch_bounds__(256) order_pairs_kernel(const int32_t* __restr
       const int cj = cnt_s[j];
       rank += (cj > ci) || (cj == ci && j < i);
     }
-    order[static_cast<int64_t>(h) * npairs + rank] = i;
+    const int64_t pos = (rank < r0) ? static_cast<int64_t>(rank) * Hm + h
+                                    : static_cast<int64_t>(r0) * Hm + static_cast<int64_t>(h) * (npairs - r0) + (rank - r0);
+    order[pos] = h * npairs + i;
   }
 }
 

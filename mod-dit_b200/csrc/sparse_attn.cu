@@ -122,11 +122,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
-  const int bh = blockIdx.y;
-  const int npairs = gridDim.x;
-  const int mh = bh % Hm;
-  // blocks start in increasing blockIdx.x: `order` puts the longest lists of the head first
-  const int pair = order ? order[static_cast<int64_t>(mh) * npairs + blockIdx.x] : static_cast<int>(blockIdx.x);
+  // grid: x = work item (mask head, query-tile pair), y = batch.  Blocks start in increasing blockIdx.x;
+  // `order` (from the work-list builder) puts long lists first, otherwise items run head by head.
+  const int npairs = static_cast<int>(gridDim.x) / Hm;
+  const int item = order ? order[blockIdx.x] : static_cast<int>(blockIdx.x);
+  const int mh = item / npairs;
+  const int pair = item - mh * npairs;
+  const int bh = blockIdx.y * Hm + mh;
   const int ntq = (N + kTile - 1) / kTile;
   const bool has_b = (2 * pair + 1) < ntq;
   const int cnt = counts[static_cast<int64_t>(mh) * npairs + pair];
@@ -503,7 +505,7 @@ int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N
   const size_t smem = smem_bytes<D>();
   MODDIT_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   const float scale_log2 = softmax_scale * 1.4426950408889634f;
-  kernel<<<dim3(npairs, BH), kThreads, smem, st>>>(tq, tk, tv, counts, entries, order, Hm, ntq, N, scale_log2, q_split,
+  kernel<<<dim3(npairs * Hm, BH / Hm), kThreads, smem, st>>>(tq, tk, tv, counts, entries, order, Hm, ntq, N, scale_log2, q_split,
                                                    kvl_lo, kvl_hi, out, lse, status, scatter);
   MODDIT_CHECK_LAUNCH("sparse_attn_fwd_kernel");
   return MODDIT_OK;

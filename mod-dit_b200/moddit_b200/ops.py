@@ -344,8 +344,8 @@ class TileLists(tuple):
 
 def tile_lists(mask: torch.Tensor, block_size: int, n_tokens: int, kv_block_limit: Optional[int] = None
                ) -> TileLists:
-    """Work lists of the sparse forward for a bool (H, nbq, nbk) block mask, plus the longest-first order of
-    the query-tile pairs of every head."""
+    """Work lists of the sparse forward for a bool (H, nbq, nbk) block mask, plus the start order of the
+    (head, query-tile pair) work items (long lists first)."""
     dev = _need_cuda(mask)
     if mask.dtype != torch.bool or mask.dim() != 3:
         raise ValueError("mask must be a bool (H, nbq, nbk) tensor")

@@ -120,11 +120,19 @@ def test_two_calls_are_bitwise_identical(ops):
     b = ops.sparse_attn_fwd(q, k, v, counts, entries)
     c = ops.sparse_attn_fwd(q, k, v, counts, entries, order=lists.order)
     assert torch.equal(a, b) and torch.equal(a, c)
+    # the start order is a permutation of all (head, pair) items: the two longest pairs of every head first,
+    # then head after head with non-increasing list lengths
     cnt = counts.cpu()
-    for h in range(cnt.shape[0]):
-        o = lists.order[h].cpu().long()
-        assert sorted(o.tolist()) == list(range(cnt.shape[1]))
-        assert (cnt[h][o][:-1] >= cnt[h][o][1:]).all()
+    Hm, npairs = cnt.shape
+    o = lists.order.cpu().long().flatten()
+    assert sorted(o.tolist()) == list(range(Hm * npairs))
+    flat = cnt.flatten()
+    for h in range(Hm):
+        top2 = sorted(cnt[h].tolist(), reverse=True)[:2]
+        assert [int(flat[o[r * Hm + h]]) for r in range(2)] == top2 and all(int(o[r * Hm + h]) // npairs == h for r in range(2))
+        rest = o[2 * Hm + h * (npairs - 2): 2 * Hm + (h + 1) * (npairs - 2)]
+        assert (rest // npairs == h).all()
+        assert (flat[rest][:-1] >= flat[rest][1:]).all()
 
 
 def test_medium_shape_against_chunked_oracle(ops):
