@@ -118,11 +118,12 @@ def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_
     One kernel launch covers both; the result is (B,H,S,D).
     """
     seq_len = query.shape[2]
-    query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
+    query, key = query.contiguous(), key.contiguous()
     lists = _lists if _lists is not None else _engine_lists(mask, block_size, seq_len)
     counts, entries, order = lists.counts, lists.entries, lists.order
     if _value_ready is not None:       # value produced on another stream (e.g. still arriving from peers)
         torch.cuda.current_stream(query.device).wait_event(_value_ready)
+    value = value.contiguous()
     if pre_defined_mask is None:
         return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, check_status=False,
                                     scatter=_scatter)
