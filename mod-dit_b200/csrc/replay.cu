@@ -3,10 +3,12 @@
 //
 // One CTA owns 128 consecutive video query rows of one head and sweeps all video key tiles.
 //   warp 0      TMA producer: Q tile once, K tiles through a 4-stage ring
-//   warp 1      MMA issuer: S[b] = Q K_j^T into one of four 128-column accumulators
+//   warp 1      MMA issuer: two key tiles per instruction (N = 256: the instruction-issue cost of the one
+//               issuing thread, not the tensor pipe, limits this kernel), into one of two 256-column
+//               accumulators
 //   warp 2      tensor-memory allocation / release
-//   warps 4-7   count group 0 (key tiles 0,2,4,...); thread r owns row r
-//   warps 8-11  count group 1 (key tiles 1,3,5,...)
+//   warps 4-7   count group 0 (even key tiles = first 128 columns of an accumulator); thread r owns row r
+//   warps 8-11  count group 1 (odd key tiles = second 128 columns)
 // The Q tile is scaled and rounded to the input dtype in shared memory before the first MMA (the
 // reference rounds the scaled query the same way).  Counts of the four 64x64 quarters of every
 // 128x128 tile are accumulated in shared memory and the finished map rows are written once, coalesced.
@@ -31,9 +33,9 @@ enum BarrierIndex {
   kQReady,
   kKFull0,                      // kStages
   kKEmpty0 = kKFull0 + kStages, // kStages
-  kSFull0 = kKEmpty0 + kStages, // 4
-  kSFree0 = kSFull0 + 4,        // 4
-  kNumBarriers = kSFree0 + 4
+  kSFull0 = kKEmpty0 + kStages, // 2: accumulator b holds the scores of key tiles 2*pj, 2*pj+1
+  kSFree0 = kSFull0 + 2,        // 2
+  kNumBarriers = kSFree0 + 2
 };
 
 struct __align__(8) Control {
@@ -63,7 +65,11 @@ __global__ void __launch_bounds__(kThreads, 1) replay_map_kernel(
   constexpr int kTileBytes = kTile * D * 2;
   constexpr int kChunks = D / 64;
   constexpr int kChunkBytes = kTile * 128;
-  constexpr uint32_t kIdesc = ptx::idesc_f16(128, 128, kBF16, false);
+  constexpr uint32_t kIdesc256 = ptx::idesc_f16(128, 256, kBF16, false);
+  constexpr uint32_t kIdesc128 = ptx::idesc_f16(128, 128, kBF16, false);
+  // K ring, chunk-major: [64-column chunk][stage][128 rows x 128 B], so the rows of two consecutive stages are
+  // contiguous inside a chunk and one N = 256 operand covers both tiles
+  constexpr int kRingChunkBytes = kStages * kChunkBytes;
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -87,7 +93,7 @@ __global__ void __launch_bounds__(kThreads, 1) replay_map_kernel(
     for (int i = 0; i < kNumBarriers; ++i) {
       uint32_t c = 1;
       if (i == kQReady) c = 256;
-      if (i >= kSFree0) c = 128;
+      if (i >= kSFree0) c = 256;
       ptx::mbar_init(bar(i), c);
     }
     ctl->abort_flag = 0;
@@ -117,7 +123,7 @@ __global__ void __launch_bounds__(kThreads, 1) replay_map_kernel(
         if (!ok) { report(status, 1, 0, j); break; }
         ptx::mbar_expect_tx(bar(kKFull0 + s), kTileBytes);
         for (int c = 0; c < kChunks; ++c)
-          ptx::tma_load_3d(sK + s * kTileBytes + c * kChunkBytes, &tm_k, bar(kKFull0 + s), c * 64, k_off + j * kTile,
+          ptx::tma_load_3d(sK + c * kRingChunkBytes + s * kChunkBytes, &tm_k, bar(kKFull0 + s), c * 64, k_off + j * kTile,
                            bh);
         issued = j + 1;
       }
@@ -130,22 +136,25 @@ __global__ void __launch_bounds__(kThreads, 1) replay_map_kernel(
     if (lane == 0) {
       bool ok = ptx::mbar_wait(bar(kQReady), 0, abort_flag);
       if (!ok) report(status, 2, 1, -1);
-      for (int j = 0; j < ntk && ok; ++j) {
-        const int s = j % kStages;
-        const int b = j % 4;
+      for (int j = 0; j < ntk && ok; j += 2) {
+        const int s = j % kStages;                  // even: 0 or 2, so stage s+1 follows it in the ring
+        const int pj = j / 2;
+        const int b = pj & 1;
+        const bool two = (j + 1) < ntk;
         ok = ptx::mbar_wait(bar(kKFull0 + s), (j / kStages) & 1, abort_flag);
-        if (ok) ok = ptx::mbar_wait(bar(kSFree0 + b), ((j / 4) & 1) ^ 1, abort_flag);
+        if (ok && two) ok = ptx::mbar_wait(bar(kKFull0 + s + 1), (j / kStages) & 1, abort_flag);
+        if (ok) ok = ptx::mbar_wait(bar(kSFree0 + b), ((pj >> 1) & 1) ^ 1, abort_flag);
         if (!ok) { report(status, 2, 1, j); break; }
         ptx::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kChunkBytes + (kk % 4) * 32;
-          const uint64_t a = ptx::smem_desc_sw128(sQ + off, 16, 1024);
-          const uint64_t bd = ptx::smem_desc_sw128(sK + s * kTileBytes + off, 16, 1024);
-          ptx::mma_ss(tmem + b * 128, a, bd, kIdesc, kk > 0 ? 1u : 0u);
+          const uint64_t a = ptx::smem_desc_sw128(sQ + (kk / 4) * kChunkBytes + (kk % 4) * 32, 16, 1024);
+          const uint64_t bd = ptx::smem_desc_sw128(sK + (kk / 4) * kRingChunkBytes + s * kChunkBytes + (kk % 4) * 32, 16, 1024);
+          ptx::mma_ss(tmem + b * 256, a, bd, two ? kIdesc256 : kIdesc128, kk > 0 ? 1u : 0u);
         }
         ptx::tc_commit(bar(kSFull0 + b));
         ptx::tc_commit(bar(kKEmpty0 + s));
+        if (two) ptx::tc_commit(bar(kKEmpty0 + s + 1));
       }
     }
   } else if (warp >= 4) {
@@ -190,14 +199,15 @@ __global__ void __launch_bounds__(kThreads, 1) replay_map_kernel(
     const float line = row_ok ? (lse[static_cast<int64_t>(bh) * N + grow] + log_thr) : -INFINITY;
     const int rh = r >> 6;
     for (int j = g; j < ntk && ok; j += 2) {
-      const int b = j % 4;
-      ok = ptx::mbar_wait(bar(kSFull0 + b), (j / 4) & 1, abort_flag);
+      const int pj = j / 2;
+      const int b = pj & 1;
+      ok = ptx::mbar_wait(bar(kSFull0 + b), (pj >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report(status, 5, 2 + g, j); break; }
       ptx::tc_fence_after();
       float v[kTile];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) ptx::tmem_ld32(tmem + lane_base + b * 128 + c * 32, reinterpret_cast<uint32_t*>(v) + c * 32);
+      for (int c = 0; c < 4; ++c) ptx::tmem_ld32(tmem + lane_base + b * 256 + g * 128 + c * 32, reinterpret_cast<uint32_t*>(v) + c * 32);
       ptx::tmem_ld_wait();
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(kSFree0 + b));
