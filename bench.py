@@ -161,19 +161,21 @@ def run_ours(args):
     state = make_state(cfg, he - hb)
 
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    qk_stream = torch.cuda.Stream(device=dev) if world > 1 else None
     resharder, value_group = None, None
     reshard = "none"
     if world > 1:
         try:
             resharder = mdist.PeerResharder(H, N, D, q_in.dtype, dev)
-            reshard = "peer-memory copies + fused output scatter"
+            resharder.enable_pooling(bs)
+            reshard = "peer-memory copies + fused output scatter; query/key pooled on the sequence shards"
         except Exception as exc:   # symmetric memory unavailable on this box: NCCL all-to-all does the same exchange
             print(f"[bench] peer-memory re-shard unavailable ({exc!r}); using NCCL all-to-all", file=sys.stderr)
             value_group = dist.new_group(backend="nccl")
             reshard = "NCCL all-to-all"
 
     def layer(qs, ks, vs, step):
-        ready, scatter = None, None
+        ready, scatter, qk_ready, pooled = None, None, None, None
         if world > 1:
             main = torch.cuda.current_stream(dev)
             comm_stream.wait_stream(main)
@@ -184,14 +186,22 @@ def run_ours(args):
                 ready = torch.cuda.Event()
                 ready.record(comm_stream)
             if resharder is not None:
-                qs, ks = resharder.seq_to_head_many([qs, ks], [0, 1], channel=0)
+                # the mask needs only block means of query and key: they are pooled on the sequence shards and
+                # sent to the head owners, so the prediction runs while the rows themselves still travel
+                qk_stream.wait_stream(main)
+                with torch.cuda.stream(qk_stream):
+                    qh, kh = resharder.seq_to_head_many([qs, ks], [0, 1], channel=0)
+                    qk_ready = torch.cuda.Event()
+                    qk_ready.record(qk_stream)
+                pooled = resharder.pool_to_head(qs, ks, channel=0)
+                qs, ks = qh, kh
                 scatter = resharder.begin_output(channel=0)
             else:
                 qs, ks = mdist.seq_to_head(qs), mdist.seq_to_head(ks)
             vs = vs_h
             vs.record_stream(main)
         out, _ = SparseAttentionWithMap(qs, ks, vs, state, logger, current_step=step, value_ready=ready,
-                                        output_scatter=scatter)
+                                        output_scatter=scatter, qk_ready=qk_ready, pooled_qk=pooled)
         if world > 1:
             if resharder is None:
                 out = mdist.head_to_seq(out)

@@ -58,6 +58,19 @@ const char* moddit_last_error_string(void);
 int moddit_pool_blocks(const void* x, int dtype, int BH, int N, int D, int block_size,
                        float* out, void* stream);
 
+/* The same pooling for a sequence-parallel caller, before the sequence->head exchange (no reference
+ * counterpart; the reference pools nothing and re-shards through its host framework).  A rank holds
+ * `rows_local` consecutive rows of every head; the first block may start in the previous rank's rows, which
+ * arrive in `halo` ((heads, halo_capacity, D), `halo_rows` of them valid, < block_size).  Block i of the
+ * rows halo ++ x is block `block_base + i` of the sequence; its mean is stored to the rank owning the head:
+ * peer_out[h / heads_per_peer] is that rank's (heads_per_peer, total_blocks, D) float32 buffer (peer-mapped
+ * memory is fine: plain stores).  Results equal moddit_pool_blocks on the gathered head bit for bit.
+ */
+int moddit_pool_blocks_shard(const void* x, const void* halo, int dtype, int heads, int rows_local,
+                             int halo_rows, int halo_capacity, int D, int block_size, int n_blocks,
+                             float* const* peer_out, int n_peers, int heads_per_peer, int total_blocks,
+                             int block_base, void* stream);
+
 /* Pooled stand-in for the sparsity map: with l_ij = qbar[h,qo+i,:].kbar[h,ko+j,:]*scale over the n video
  * blocks, map[h,i,j] = 1 - exp(l_ij - max_j l_ij), written as float16 (no reference function; consumed
  * exactly like the reference map of MoD/mod/triton_flash_sparsity.py:275-341: 1 = nothing there).

@@ -71,13 +71,17 @@ def compute_block_sparse_map_triton(query, key, value, warmup_state):
 compute_block_sparse_map = compute_block_sparse_map_triton
 
 
-def compute_pooled_map(query, key, warmup_state) -> torch.Tensor:
-    """Mean-pooled stand-in for the sparsity map: (B,H,n,n) float16, same polarity as the exact map."""
+def compute_pooled_map(query, key, warmup_state, pooled_qk=None) -> torch.Tensor:
+    """Mean-pooled stand-in for the sparsity map: (B,H,n,n) float16, same polarity as the exact map.
+    `pooled_qk`: block means of query and key computed elsewhere (then query and key are not read)."""
     bs = warmup_state['block_size']
     n = _video_blocks(warmup_state, query.shape[2])
     off = warmup_state['text_token_num'] // bs if warmup_state['model_type'] == 'cogvideox' else 0
-    qbar = _ops.pool_blocks(query, bs)
-    kbar = _ops.pool_blocks(key, bs)
+    if pooled_qk is not None:
+        qbar, kbar = pooled_qk
+    else:
+        qbar = _ops.pool_blocks(query, bs)
+        kbar = _ops.pool_blocks(key, bs)
     return _ops.pooled_map(qbar, kbar, q_block_offset=off, k_block_offset=off, video_blocks=n,
                            scale=query.shape[3] ** -0.5)
 
@@ -109,6 +113,12 @@ def _engine_lists(mask: torch.Tensor, block_size: int, seq_len: int):
     return _ops.tile_lists(mask, block_size, seq_len)
 
 
+def _events(ready):
+    if ready is None:
+        return ()
+    return tuple(ev for ev in ready if ev is not None) if isinstance(ready, (tuple, list)) else (ready,)
+
+
 def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_token_num=0, block_size=128,
                           _lists=None, _value_ready=None, _scatter=None):
     """Block-sparse attention of (B,H,S,D) tensors under a bool block mask (:266-331).
@@ -121,8 +131,8 @@ def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_
     query, key = query.contiguous(), key.contiguous()
     lists = _lists if _lists is not None else _engine_lists(mask, block_size, seq_len)
     counts, entries, order = lists.counts, lists.entries, lists.order
-    if _value_ready is not None:       # value produced on another stream (e.g. still arriving from peers)
-        torch.cuda.current_stream(query.device).wait_event(_value_ready)
+    for ev in _events(_value_ready):   # inputs produced on another stream (e.g. still arriving from peers)
+        torch.cuda.current_stream(query.device).wait_event(ev)
     value = value.contiguous()
     if pre_defined_mask is None:
         return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, check_status=False,
@@ -267,6 +277,10 @@ def SparseAttentionWithMap(
     Optional keyword `value_ready` (a torch.cuda.Event): `value` is produced on another stream and only
     becomes valid once the event has fired; mask prediction, which needs query and key only, starts at
     once and the wait happens right before the attention kernel.
+    Optional keywords `pooled_qk` and `qk_ready` (pooled producer only): block means of query and key that
+    the caller already holds ((1,H,nb,D) float32 each) and the event after which `query` and `key`
+    themselves are valid - a sequence-parallel caller pools its shards before the exchange
+    (`moddit_b200.dist.PeerResharder.pool_to_head`), so the mask is predicted while the rows still travel.
     Optional keyword `output_scatter` (from `moddit_b200.dist.PeerResharder.begin_output`): on sparse steps
     the attention kernel stores its rows straight into the peers' sequence-shard buffers and the returned
     output is None; steps that run dense attention ignore it and return the output tensor as usual.
@@ -296,7 +310,10 @@ def SparseAttentionWithMap(
 
     if pooled:
         return _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx,
-                            value_ready, kwargs.get('output_scatter'))
+                            value_ready, kwargs.get('output_scatter'), kwargs.get('pooled_qk'),
+                            kwargs.get('qk_ready'))
+    if kwargs.get('pooled_qk') is not None or kwargs.get('qk_ready') is not None:
+        raise ValueError("pooled_qk / qk_ready need warmup_state['score_producer'] == 'pooled'")
     if value_ready is not None:
         torch.cuda.current_stream(query.device).wait_event(value_ready)
     value = value.contiguous()
@@ -347,7 +364,7 @@ def SparseAttentionWithMap(
 
 
 def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx,
-                 value_ready=None, output_scatter=None):
+                 value_ready=None, output_scatter=None, pooled_qk=None, qk_ready=None):
     """Variant with the mean-pooled map producer: the mask is re-predicted on every step from the pooled map
     of that step, so no dense pass is needed after the first feature-collection step."""
     seq_len, num_heads = query.size(2), query.size(1)
@@ -355,14 +372,16 @@ def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, curr
     bs = warmup_state['block_size']
 
     def wait_value():
-        if value_ready is not None:
-            torch.cuda.current_stream(query.device).wait_event(value_ready)
+        for ev in _events((value_ready, qk_ready)):
+            torch.cuda.current_stream(query.device).wait_event(ev)
 
     if current_step < warmup_steps - 2:
         wait_value()
         output, _ = dense_attention_with_lse(query, key, value, kv_len=_valid_kv(pre_defined_mask, seq_len))
         return output, {'mode': 'warmup', 'mask': None}
-    dark = compute_pooled_map(query, key, warmup_state).squeeze(0)
+    if pooled_qk is None and qk_ready is not None:      # query and key are read by the pooling itself
+        torch.cuda.current_stream(query.device).wait_event(qk_ready)
+    dark = compute_pooled_map(query, key, warmup_state, pooled_qk).squeeze(0)
     n = dark.shape[-1]
     mts, _ = _ops.mts(dark, warmup_state['blocks_per_frame'])
     X = _ops.solve(mts, n, warmup_state['blocks_per_frame'], 1.0)
@@ -386,6 +405,6 @@ def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, curr
     _store_mask(warmup_state, mask, seq_len)
     output = AttentionSparseEngine(query, key, value, mask, pre_defined_mask=pre_defined_mask,
                                    video_token_num=warmup_state.get('video_token_num', 0), block_size=bs,
-                                   _lists=warmup_state['_tile_lists'][1], _value_ready=value_ready,
+                                   _lists=warmup_state['_tile_lists'][1], _value_ready=(value_ready, qk_ready),
                                    _scatter=output_scatter)
     return output, {'mask': mask}

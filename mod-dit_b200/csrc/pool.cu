@@ -43,10 +43,27 @@ __device__ __forceinline__ void unpack8<__half>(const uint4& v, float (&f)[8]) {
 
 constexpr int kPoolThreads = 256;
 
+// Sequence-shard form of the pooling (kShard): the rows of a head are `halo_rows` rows of a halo buffer (the
+// part of the first block that the previous rank holds) followed by this rank's `N` rows, and the mean of
+// block `blk` goes to the rank that owns the head, at block `block_base + blk` of its (heads_per_peer,
+// nb_total, D) buffer - plain peer stores.  Row order and reduction order are those of the plain form, so a
+// block pooled from a shard equals the block pooled from the whole sequence bit for bit.
+constexpr int kMaxPoolPeers = 8;
+struct PoolShard {
+  const void* halo;          // (heads, halo_cap, D) rows received from the previous rank
+  int halo_rows;
+  int halo_cap;
+  float* peer[kMaxPoolPeers];
+  int heads_per_peer;
+  int nb_total;
+  int block_base;
+};
+
 // D is 64 or 128: D/8 threads cover one row with one 16-byte load each.
-template <typename T, int D>
+template <typename T, int D, bool kShard>
 __global__ void __launch_bounds__(kPoolThreads) pool_blocks_kernel(const T* __restrict__ x, int N, int bs,
-                                                                   float* __restrict__ out) {
+                                                                   float* __restrict__ out,
+                                                                   const __grid_constant__ PoolShard shard) {
   constexpr int kTpr = D / 8;                   // threads per row
   constexpr int kRpp = kPoolThreads / kTpr;     // rows per pass
   __shared__ float red[kRpp][D];
@@ -55,10 +72,16 @@ __global__ void __launch_bounds__(kPoolThreads) pool_blocks_kernel(const T* __re
   const int bh = blockIdx.y;
   const int nb = gridDim.x;
   const int row0 = blk * bs;
-  const int rows = min(bs, N - row0);
+  const int halo_rows = kShard ? shard.halo_rows : 0;
+  const int rows = min(bs, halo_rows + N - row0);
   const int cg = threadIdx.x % kTpr;
   const int rg = threadIdx.x / kTpr;
-  const uint4* base = reinterpret_cast<const uint4*>(x + (static_cast<int64_t>(bh) * N + row0) * D) + cg;
+  // row r of the block: in the halo while row0 + r < halo_rows, in x afterwards
+  const uint4* base = reinterpret_cast<const uint4*>(x + (static_cast<int64_t>(bh) * N + (row0 - halo_rows)) * D) + cg;
+  const uint4* hbase = nullptr;
+  if constexpr (kShard)
+    hbase = reinterpret_cast<const uint4*>(static_cast<const T*>(shard.halo) +
+                                           (static_cast<int64_t>(bh) * shard.halo_cap + row0) * D) + cg;
 
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   // rows/kRpp is at most 8 (bs=128, D=128): issue the loads of up to eight rows before using any.
@@ -67,7 +90,13 @@ __global__ void __launch_bounds__(kPoolThreads) pool_blocks_kernel(const T* __re
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int r = r0 + u * kRpp;
-      v[u] = (r < rows) ? __ldg(base + static_cast<int64_t>(r) * kTpr) : make_uint4(0, 0, 0, 0);
+      if (r >= rows) {
+        v[u] = make_uint4(0, 0, 0, 0);
+      } else if (kShard && row0 + r < halo_rows) {
+        v[u] = __ldg(hbase + static_cast<int64_t>(r) * kTpr);
+      } else {
+        v[u] = __ldg(base + static_cast<int64_t>(r) * kTpr);
+      }
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -84,7 +113,35 @@ __global__ void __launch_bounds__(kPoolThreads) pool_blocks_kernel(const T* __re
     float s = 0.f;
 #pragma unroll 8
     for (int g = 0; g < kRpp; ++g) s += red[g][threadIdx.x];
-    out[(static_cast<int64_t>(bh) * nb + blk) * D + threadIdx.x] = s / static_cast<float>(rows);
+    float* dst;
+    if constexpr (kShard) {
+      const int owner = bh / shard.heads_per_peer;
+      dst = shard.peer[owner] + (static_cast<int64_t>(bh - owner * shard.heads_per_peer) * shard.nb_total +
+                                 shard.block_base + blk) * D;
+    } else {
+      dst = out + (static_cast<int64_t>(bh) * nb + blk) * D;
+    }
+    dst[threadIdx.x] = s / static_cast<float>(rows);
+  }
+}
+
+template <bool kShard>
+void launch_pool(const void* x, int dtype, int D, int N, int bs, float* out, const PoolShard& shard, dim3 grid,
+                 cudaStream_t st) {
+  if (dtype == MODDIT_BF16) {
+    if (D == 64)
+      pool_blocks_kernel<__nv_bfloat16, 64, kShard><<<grid, kPoolThreads, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(x), N, bs, out, shard);
+    else
+      pool_blocks_kernel<__nv_bfloat16, 128, kShard><<<grid, kPoolThreads, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(x), N, bs, out, shard);
+  } else {
+    if (D == 64)
+      pool_blocks_kernel<__half, 64, kShard><<<grid, kPoolThreads, 0, st>>>(static_cast<const __half*>(x), N, bs, out,
+                                                                           shard);
+    else
+      pool_blocks_kernel<__half, 128, kShard><<<grid, kPoolThreads, 0, st>>>(static_cast<const __half*>(x), N, bs, out,
+                                                                            shard);
   }
 }
 
@@ -197,22 +254,50 @@ extern "C" int moddit_pool_blocks(const void* x, int dtype, int BH, int N, int D
   if (BH > 65535) return fail(MODDIT_E_UNSUPPORTED, "pool_blocks: BH=%d exceeds 65535", BH);
   if (int rc = require_sm100()) return rc;
   const dim3 grid(ceil_div(N, block_size), BH);
-  cudaStream_t st = as_stream(stream);
-  if (dtype == MODDIT_BF16) {
-    if (D == 64)
-      pool_blocks_kernel<__nv_bfloat16, 64><<<grid, kPoolThreads, 0, st>>>(
-          static_cast<const __nv_bfloat16*>(x), N, block_size, out);
-    else
-      pool_blocks_kernel<__nv_bfloat16, 128><<<grid, kPoolThreads, 0, st>>>(
-          static_cast<const __nv_bfloat16*>(x), N, block_size, out);
-  } else {
-    if (D == 64)
-      pool_blocks_kernel<__half, 64><<<grid, kPoolThreads, 0, st>>>(static_cast<const __half*>(x), N, block_size, out);
-    else
-      pool_blocks_kernel<__half, 128><<<grid, kPoolThreads, 0, st>>>(static_cast<const __half*>(x), N, block_size,
-                                                                       out);
-  }
+  const PoolShard none = {};
+  launch_pool<false>(x, dtype, D, N, block_size, out, none, grid, as_stream(stream));
   MODDIT_CHECK_LAUNCH("pool_blocks_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_pool_blocks_shard(const void* x, const void* halo, int dtype, int heads, int rows_local,
+                                        int halo_rows, int halo_capacity, int D, int block_size, int n_blocks,
+                                        float* const* peer_out, int n_peers, int heads_per_peer, int total_blocks,
+                                        int block_base, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(x && peer_out, "pool_blocks_shard: null pointer");
+  MODDIT_CHECK_ARG(heads > 0 && heads <= 65535 && rows_local > 0 && n_blocks > 0,
+                   "pool_blocks_shard: heads=%d rows=%d blocks=%d out of range", heads, rows_local, n_blocks);
+  if (D != 64 && D != 128) return fail(MODDIT_E_UNSUPPORTED, "pool_blocks_shard: head_dim must be 64 or 128, got %d", D);
+  if (block_size != 64 && block_size != 128)
+    return fail(MODDIT_E_UNSUPPORTED, "pool_blocks_shard: block_size must be 64 or 128, got %d", block_size);
+  if (dtype != MODDIT_BF16 && dtype != MODDIT_FP16)
+    return fail(MODDIT_E_ARG, "pool_blocks_shard: unknown dtype %d", dtype);
+  MODDIT_CHECK_ARG(n_peers >= 1 && n_peers <= kMaxPoolPeers && heads_per_peer > 0 && heads == n_peers * heads_per_peer,
+                   "pool_blocks_shard: %d heads do not split into %d peers x %d heads", heads, n_peers, heads_per_peer);
+  MODDIT_CHECK_ARG(halo_rows >= 0 && halo_rows < block_size && halo_rows <= halo_capacity,
+                   "pool_blocks_shard: halo_rows=%d outside [0, min(block_size, capacity=%d))", halo_rows, halo_capacity);
+  MODDIT_CHECK_ARG(halo_rows == 0 || halo, "pool_blocks_shard: halo rows without a halo buffer");
+  MODDIT_CHECK_ARG(static_cast<long long>(n_blocks - 1) * block_size < static_cast<long long>(halo_rows) + rows_local,
+                   "pool_blocks_shard: %d blocks exceed the %d + %d rows at hand", n_blocks, halo_rows, rows_local);
+  MODDIT_CHECK_ARG(block_base >= 0 && block_base + n_blocks <= total_blocks,
+                   "pool_blocks_shard: blocks [%d, %d) outside [0, %d)", block_base, block_base + n_blocks, total_blocks);
+  if (!aligned16(x) || (halo && !aligned16(halo)))
+    return fail(MODDIT_E_ALIGN, "pool_blocks_shard: inputs must be 16-byte aligned");
+  if (int rc = require_sm100()) return rc;
+  PoolShard shard = {};
+  shard.halo = halo;
+  shard.halo_rows = halo_rows;
+  shard.halo_cap = halo_capacity;
+  for (int i = 0; i < n_peers; ++i) {
+    MODDIT_CHECK_ARG(peer_out[i] && aligned16(peer_out[i]), "pool_blocks_shard: peer buffer %d null or unaligned", i);
+    shard.peer[i] = peer_out[i];
+  }
+  shard.heads_per_peer = heads_per_peer;
+  shard.nb_total = total_blocks;
+  shard.block_base = block_base;
+  launch_pool<true>(x, dtype, D, rows_local, block_size, nullptr, shard, dim3(n_blocks, heads), as_stream(stream));
+  MODDIT_CHECK_LAUNCH("pool_blocks_kernel (shard)");
   return MODDIT_OK;
 }
 

@@ -25,6 +25,8 @@ SIGNATURES = {
     "moddit_abi_version": (c_int, []),
     "moddit_last_error_string": (c_char_p, []),
     "moddit_pool_blocks": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "moddit_pool_blocks_shard": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                         c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "moddit_pooled_map": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_void_p, c_void_p]),
     "moddit_replay_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,

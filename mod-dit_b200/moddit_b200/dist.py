@@ -23,6 +23,25 @@ def shard_bounds(total: int, world: int, rank: int):
     return rank * per, (rank + 1) * per
 
 
+def pool_partition(seq_len: int, block_size: int, world: int, rank: int):
+    """Which pooled blocks a sequence shard produces: (first block, end block, halo rows, tail rows).
+
+    A block belongs to the rank that holds its last row.  `halo rows` is how many rows of the rank's first
+    block lie in the previous rank's shard; `tail rows` is how many of its own last rows belong to a block
+    that the next rank finishes (they are that rank's halo)."""
+    if seq_len % world:
+        raise ValueError(f"{seq_len} rows do not divide evenly over {world} ranks")
+    ns = seq_len // world
+    if ns < block_size:
+        raise ValueError("a sequence shard must hold at least one block")
+    nb = (seq_len + block_size - 1) // block_size
+    first = (rank * ns) // block_size
+    end = nb if rank == world - 1 else ((rank + 1) * ns) // block_size
+    halo = rank * ns - first * block_size
+    tail = 0 if rank == world - 1 else (rank + 1) * ns - end * block_size
+    return first, end, halo, tail
+
+
 def _exchange(world: int, rank: int, send_view, recv_view, local_copy, group):
     """One grouped exchange: `send_view(peer)` / `recv_view(peer)` give lists of contiguous tensors."""
     ops = []
@@ -191,6 +210,48 @@ class PeerResharder:
         self._ops.copy_rows_multi(src, dst, self.N * self.D * self.esize, row, row, self.hp, self.device)
         hdl.barrier(channel=channel, timeout_ms=self.timeout_ms)
         return self.output
+
+    # ---- block means of query and key, pooled on the sequence shards ----------------------------------------
+    def enable_pooling(self, block_size: int) -> None:
+        """Allocates the halo and pooled-mean buffers for `pool_to_head` (collective: every rank calls it)."""
+        import torch.distributed._symmetric_memory as symm_mem
+        self.pool_bs = block_size
+        self.pool_nb = (self.N + block_size - 1) // block_size
+        self.pool_part = pool_partition(self.N, block_size, self.world, self.rank)
+        self.halo = symm_mem.empty((2, self.H, block_size, self.D), dtype=self.dtype, device=self.device)
+        self.halo_handle = symm_mem.rendezvous(self.halo, self.group)
+        self.pooled = symm_mem.empty((2, 1, self.hp, self.pool_nb, self.D), dtype=torch.float32, device=self.device)
+        self.pooled_handle = symm_mem.rendezvous(self.pooled, self.group)
+
+    def pool_to_head(self, q: torch.Tensor, k: torch.Tensor, channel: int = 0):
+        """Block means of this rank's (1, H, N/P, D) query and key shards, delivered to the head owners.
+
+        Returns this rank's (1, H/P, nb, D) float32 means of query and key - equal, bit for bit, to pooling
+        the gathered heads - without waiting for the bulk sequence->head exchange of query and key: only
+        the rows of a block cut by a shard boundary (fewer than block_size per head) and the means
+        themselves cross the links."""
+        for x in (q, k):
+            if tuple(x.shape) != (1, self.H, self.ns, self.D) or x.dtype != self.dtype or not x.is_contiguous():
+                raise ValueError("inputs must be contiguous (1, H, N/P, D) tensors of the configured dtype")
+        first, end, halo_rows, tail_rows = self.pool_part
+        bs = self.pool_bs
+        row = self.D * self.esize
+        self.halo_handle.barrier(channel=channel, timeout_ms=self.timeout_ms)   # last call's readers are done
+        if tail_rows:
+            nxt = self.rank + 1
+            base = int(self.halo_handle.buffer_ptrs[nxt])
+            src = [x.data_ptr() + (self.ns - tail_rows) * row for x in (q, k)]
+            dst = [base + t * self.H * bs * row for t in range(2)]
+            self._ops.copy_rows_multi(src, dst, self.ns * row, bs * row, tail_rows * row, self.H, self.device)
+        self.halo_handle.barrier(channel=channel, timeout_ms=self.timeout_ms)   # halos have landed
+        plane = self.hp * self.pool_nb * self.D * 4
+        for t, x in enumerate((q, k)):
+            peers = [int(p) + t * plane for p in self.pooled_handle.buffer_ptrs]
+            halo_ptr = self.halo.data_ptr() + t * self.H * bs * row
+            self._ops.pool_blocks_shard(x, halo_ptr, halo_rows, bs, bs, end - first, peers, self.hp, self.pool_nb,
+                                        first)
+        self.pooled_handle.barrier(channel=channel, timeout_ms=self.timeout_ms)  # every rank's means have landed
+        return self.pooled[0], self.pooled[1]
 
     # ---- output re-shard fused into the attention kernel's epilogue ------------------------------------
     def begin_output(self, channel: int = 0):

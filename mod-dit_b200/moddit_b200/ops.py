@@ -114,6 +114,25 @@ def pool_blocks(x: torch.Tensor, block_size: int) -> torch.Tensor:
     return out
 
 
+def pool_blocks_shard(x: torch.Tensor, halo_ptr: int, halo_rows: int, halo_capacity: int, block_size: int,
+                      n_blocks: int, peer_ptrs, heads_per_peer: int, total_blocks: int, block_base: int) -> None:
+    """Pools the blocks of a (1,H,rows,D) sequence shard (preceded by `halo_rows` rows of the halo buffer at
+    `halo_ptr`) and stores block i as block `block_base + i` of the head owner's (heads_per_peer,
+    total_blocks, D) float32 buffer (`peer_ptrs[h // heads_per_peer]`, device pointers, may be peer memory)."""
+    dev = _need_cuda(x)
+    _need_contig(x=x)
+    B, H, rows, D = x.shape
+    if B != 1:
+        raise ValueError("pool_blocks_shard: batch must be 1")
+    n = len(peer_ptrs)
+    table = (ctypes.c_void_p * n)(*peer_ptrs)
+    with torch.cuda.device(dev), _timed("moddit_pool_blocks", dev):
+        check(lib.moddit_pool_blocks_shard(_ptr(x), ctypes.c_void_p(halo_ptr) if halo_ptr else None, _qkv_dtype(x), H,
+                                           rows, halo_rows, halo_capacity, D, block_size, n_blocks, table, n,
+                                           heads_per_peer, total_blocks, block_base, _stream(dev)),
+              "moddit_pool_blocks_shard")
+
+
 def pooled_map(qbar: torch.Tensor, kbar: torch.Tensor, *, q_block_offset: int, k_block_offset: int,
                video_blocks: int, scale: float) -> torch.Tensor:
     """(B,H,nb,D) float32 block means -> (B,H,n,n) float16 darkness map, 1 - exp(logit - row maximum)."""

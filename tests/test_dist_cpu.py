@@ -42,3 +42,41 @@ def test_reshard_round_trip_two_ranks():
         p.join(120)
         assert p.exitcode == 0
     assert ret[0] and ret[1]
+
+
+def _load_dist_module():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("moddit_dist_plain",
+                                                  os.path.join(ROOT, "mod-dit_b200", "moddit_b200", "dist.py"))
+    md = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(md)
+    return md
+
+
+def test_pool_partition_covers_every_block_once():
+    """Shard-side pooling: every block has exactly one producer, halos and tails of neighbours agree, and
+    block means taken from (halo ++ own rows) equal the means of the whole sequence."""
+    md = _load_dist_module()
+    for N, bs, world in ((115456, 128, 8), (115456, 128, 4), (115456, 128, 2), (1344, 128, 2), (75600, 64, 8),
+                         (1472, 64, 2), (1024, 128, 8)):
+        parts = [md.pool_partition(N, bs, world, r) for r in range(world)]
+        nb = (N + bs - 1) // bs
+        assert parts[0][0] == 0 and parts[0][2] == 0 and parts[-1][1] == nb and parts[-1][3] == 0
+        for a, b in zip(parts, parts[1:]):
+            assert a[1] == b[0] and a[3] == b[2] and 0 <= a[3] < bs
+        if N > 20000:
+            continue
+        ns = N // world
+        x = torch.arange(N, dtype=torch.float64) ** 2
+        want = torch.stack([x[i * bs:(i + 1) * bs].mean() for i in range(nb)])
+        got = torch.empty(nb, dtype=torch.float64)
+        for r, (first, end, halo, tail) in enumerate(parts):
+            rows = torch.cat([x[r * ns - halo:r * ns], x[r * ns:(r + 1) * ns]])
+            for i in range(end - first):
+                got[first + i] = rows[i * bs:(i + 1) * bs].mean()
+        assert torch.equal(got, want)
+    import pytest
+    with pytest.raises(ValueError):
+        md.pool_partition(1000, 128, 8, 0)      # a shard shorter than a block
+    with pytest.raises(ValueError):
+        md.pool_partition(1001, 128, 2, 0)

@@ -46,14 +46,88 @@ dist.barrier(); dist.destroy_process_group()
 print("CHILD_OK", rank)
 '''
 
+# Pooling on the sequence shards (halo rows + means sent to the head owners) against pooling the gathered
+# heads: bit-exact, with a shard boundary inside a block and a short last block; then one full step of the
+# state machine fed with those means while query and key arrive on a side stream.
+CHILD_POOL = r'''
+import os, sys, logging, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "mod-dit_b200"))
+from moddit_b200 import dist as md, ops
+from MoD.mod.attn_mask import SparseAttentionWithMap
+from MoD.mod.state import create_adaptive_mask_state
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank); dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+for (H, N, D, bs, dt) in ((4, 1344, 128, 128, torch.bfloat16), (2, 1472, 64, 64, torch.float16)):
+    g = torch.Generator().manual_seed(11)
+    q, k = (torch.randn(1, H, N, D, generator=g).to(dt) for _ in range(2))
+    b, e = md.shard_bounds(N, world, rank)
+    hb, he = md.shard_bounds(H, world, rank)
+    pr = md.PeerResharder(H, N, D, dt, dev, n_inputs=2)
+    pr.enable_pooling(bs)
+    assert pr.pool_part[2] + pr.pool_part[3] > 0          # a boundary really cuts a block
+    qs, ks = q[:, :, b:e].contiguous().to(dev), k[:, :, b:e].contiguous().to(dev)
+    for _ in range(2):                                    # buffers are reused across calls
+        qbar, kbar = pr.pool_to_head(qs, ks)
+        assert torch.equal(qbar, ops.pool_blocks(q[:, hb:he].contiguous().to(dev), bs))
+        assert torch.equal(kbar, ops.pool_blocks(k[:, hb:he].contiguous().to(dev), bs))
+    del pr
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_peer_reshard_and_fused_scatter_two_gpus(tmp_path):
+# state machine: the step fed with shard-pooled means equals the step that pools the gathered heads
+H, T, F, D, bs = 4, 5, 256, 128, 128
+N = T * F + 64                                            # 1344: 640 rows per rank, boundary inside block 5
+g = torch.Generator().manual_seed(3)
+q, k, v = (torch.randn(1, H, N, D, generator=g).bfloat16() for _ in range(3))
+b, e = md.shard_bounds(N, world, rank)
+hb, he = md.shard_bounds(H, world, rank)
+pr = md.PeerResharder(H, N, D, torch.bfloat16, dev)
+pr.enable_pooling(bs)
+log = logging.getLogger("t")
+def state():
+    st = create_adaptive_mask_state("hunyuan", he - hb, T * F, 64, F, T, warmup_steps=2, top_k=6, predict_T=5, block_size=bs)
+    st["score_producer"] = "pooled"
+    return st
+st_a, st_b = state(), state()
+side = torch.cuda.Stream(device=dev)
+for step in range(3):
+    qh, kh, vh = (t[:, hb:he].contiguous().to(dev) for t in (q, k, v))
+    out_a, _ = SparseAttentionWithMap(qh, kh, vh, st_a, log, current_step=step)
+    shard = [t[:, :, b:e].contiguous().to(dev) for t in (q, k, v)]
+    main = torch.cuda.current_stream(dev)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        qs, ks = pr.seq_to_head_many(shard[:2], [0, 1], channel=0)
+        vs = pr.seq_to_head(shard[2], 2, channel=0)
+        ready = torch.cuda.Event(); ready.record(side)
+    pooled = pr.pool_to_head(shard[0], shard[1], channel=1)
+    out_b, _ = SparseAttentionWithMap(qs, ks, vs, st_b, log, current_step=step, value_ready=ready, qk_ready=ready,
+                                      pooled_qk=pooled)
+    assert torch.equal(out_a, out_b), step
+    if step == 2:
+        assert torch.equal(st_a["mask"], st_b["mask"])
+    torch.cuda.synchronize(); dist.barrier()
+ops.raise_on_status(dev)
+dist.barrier(); dist.destroy_process_group()
+print("CHILD_OK", rank)
+'''
+
+
+def _run_two_ranks(tmp_path, text):
     script = tmp_path / "child.py"
-    script.write_text(CHILD)
+    script.write_text(text)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", str(29600 + os.getpid() % 300), str(script), ROOT]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert res.stdout.count("CHILD_OK") == 2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_shard_pooling_matches_gathered_pooling_two_gpus(tmp_path):
+    _run_two_ranks(tmp_path, CHILD_POOL)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_reshard_and_fused_scatter_two_gpus(tmp_path):
+    _run_two_ranks(tmp_path, CHILD)
