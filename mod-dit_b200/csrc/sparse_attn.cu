@@ -4,7 +4,8 @@
 //
 // One CTA owns a PAIR of adjacent 128-row query tiles (A, B) of one head and walks the union of
 // their key-tile lists, so a K/V tile needed by both is fetched once.  Roles (12 warps):
-//   warp 0      TMA producer: Q tiles once, then K and V tiles through two 2-stage rings
+//   warp 0      TMA producer: Q tiles once, then K and V tiles through two 2-stage rings (V of entry e and K
+//               of entry e + 1 share their barriers: they are consumed together)
 //   warp 1      MMA issuer: S_X = Q_X K^T (SS form), O_X += P_X V (P read from tensor memory)
 //   warp 2      tensor-memory allocation / release
 //   warps 4-7   softmax of tile A: thread r owns row r (tensor-memory lane r)
@@ -36,8 +37,9 @@ constexpr float kRescaleThreshold = 8.0f;   // log2 domain: rescale O only when 
 
 enum BarrierIndex {
   kQFull = 0,
-  kKFull0, kKFull1, kKEmpty0, kKEmpty1,
-  kVFull0, kVFull1, kVEmpty0, kVEmpty1,
+  kKFirst,                      // K tile of entry 0
+  kFull0, kFull1,               // entry e (index e & 1): V tile of e and K tile of e + 1 have landed
+  kEmpty0, kEmpty1,             // entry e: its V stage and the K stage of e + 1 may be overwritten
   kSFullA, kSFullB,
   kPLoA, kPHiA, kPLoB, kPHiB,   // first / second half row of P stored, per query tile
   kOFinal,
@@ -164,36 +166,38 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
         for (int c = 0; c < kChunks; ++c)
           ptx::tma_load_3d(sQ + x * kTileBytes + c * kChunkBytes, &tm_q, bar(kQFull), c * 64, (2 * pair + x) * kTile,
                            bh);
+      // Entry e consumes V(e) and K(e+1) together (P V of e, then Q K^T of e + 1), so the two tiles share one
+      // pair of barriers: the MMA-issuing thread pays one wait and one commit per entry for its operands.
       bool ok = true;
       int issued = 0;
+      if (cnt > 0) {
+        ptx::mbar_expect_tx(bar(kKFirst), kTileBytes);
+        for (int c = 0; c < kChunks; ++c)
+          ptx::tma_load_3d(sK + c * kChunkBytes, &tm_k, bar(kKFirst), c * 64, (ent[0] >> 8) * kTile, bh);
+      }
       for (int e = 0; e < cnt && ok; ++e) {
         const int s = e & 1;
-        const uint32_t par = ((e >> 1) & 1) ^ 1;
-        const int row0 = (ent[e] >> 8) * kTile;
-        ok = ptx::mbar_wait(bar(kKEmpty0 + s), par, abort_flag);
+        // kEmpty1 also completes once before the loop (the first K tile's stage), hence the shifted parity
+        const uint32_t par = ((e >> 1) & 1) ^ (s ? 0u : 1u);
+        const bool next = (e + 1) < cnt;
+        ok = ptx::mbar_wait(bar(kEmpty0 + s), par, abort_flag);
         if (!ok) { report(status, 1, 0, e); break; }
-        ptx::mbar_expect_tx(bar(kKFull0 + s), kTileBytes);
+        ptx::mbar_expect_tx(bar(kFull0 + s), (next ? 2u : 1u) * kTileBytes);
+        const int row0 = (ent[e] >> 8) * kTile;
         for (int c = 0; c < kChunks; ++c)
-          ptx::tma_load_3d(sK + s * kTileBytes + c * kChunkBytes, &tm_k, bar(kKFull0 + s), c * 64, row0, bh);
-        ok = ptx::mbar_wait(bar(kVEmpty0 + s), par, abort_flag);
-        if (!ok) {
-          // the K copy just issued must land before the CTA may exit
-          report(status, 1, 0, e);
-          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(kKFull0 + s), (e >> 1) & 1); ++i) {}
-          break;
+          ptx::tma_load_3d(sV + s * kTileBytes + c * kChunkBytes, &tm_v, bar(kFull0 + s), c * 64, row0, bh);
+        if (next) {
+          const int row1 = (ent[e + 1] >> 8) * kTile;
+          for (int c = 0; c < kChunks; ++c)
+            ptx::tma_load_3d(sK + (s ^ 1) * kTileBytes + c * kChunkBytes, &tm_k, bar(kFull0 + s), c * 64, row1, bh);
         }
-        ptx::mbar_expect_tx(bar(kVFull0 + s), kTileBytes);
-        for (int c = 0; c < kChunks; ++c)
-          ptx::tma_load_3d(sV + s * kTileBytes + c * kChunkBytes, &tm_v, bar(kVFull0 + s), c * 64, row0, bh);
         issued = e + 1;
       }
       if (!ok) {
         // give copies in flight a bounded time to land (their barriers may never be consumed)
-        for (int e = max(0, issued - 2); e < issued; ++e) {
-          const int s = e & 1;
-          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(kKFull0 + s), (e >> 1) & 1); ++i) {}
-          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(kVFull0 + s), (e >> 1) & 1); ++i) {}
-        }
+        for (int i = 0; i < 4096 && cnt > 0 && !ptx::mbar_try_wait(bar(kKFirst), 0); ++i) {}
+        for (int e = max(0, issued - 2); e < issued; ++e)
+          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(kFull0 + (e & 1)), (e >> 1) & 1); ++i) {}
       }
     }
   } else if (warp == 1) {
@@ -248,26 +252,27 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
       uint32_t par_p[2] = {0, 0};
       uint32_t acc[2] = {0, 0};
       if (ok && cnt > 0) {
-        ok = ptx::mbar_wait(bar(kKFull0), 0, abort_flag);
+        ok = ptx::mbar_wait(bar(kKFirst), 0, abort_flag);
         if (!ok) report(status, 2, 1, 0);
         if (ok) {
           ptx::tc_fence_after();
           const int fl = ent[0] & 0xff;
           if (fl & 0x0f) issue_qk(0, 0);
           if (fl & 0xf0) issue_qk(1, 0);
-          ptx::tc_commit(bar(kKEmpty0));
+          ptx::tc_commit(bar(kEmpty1));     // K stage 0 is free for the K tile of entry 2 (loaded with V of entry 1)
         }
       }
       long long pt_kv = 0, pt_p = 0, pt_qk = 0, pt_pv = 0;
       const long long pt_begin = PROF_T();
+      int fl_carry = (cnt > 0) ? (ent[0] & 0xff) : 0;
       for (int e = 0; e < cnt && ok; ++e) {
         const int s = e & 1;
-        const int fl = ent[e] & 0xff;
+        const int fl = fl_carry;
         const bool next = (e + 1) < cnt;
-        const int fln = next ? (ent[e + 1] & 0xff) : 0;
+        const int fln = next ? (ent[e + 1] & 0xff) : 0;   // issued here, first used after the P V of tile A
+        fl_carry = fln;
         long long pt0 = PROF_T();
-        if (next) ok = ptx::mbar_wait(bar(kKFull0 + (s ^ 1)), ((e + 1) >> 1) & 1, abort_flag);
-        if (ok) ok = ptx::mbar_wait(bar(kVFull0 + s), (e >> 1) & 1, abort_flag);
+        ok = ptx::mbar_wait(bar(kFull0 + s), (e >> 1) & 1, abort_flag);
         pt_kv += PROF_T() - pt0;
         if (!ok) { report(status, 2, 1, e); break; }
         if (fl & 0x0f) {
@@ -293,11 +298,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
           par_p[1] ^= 1;
           acc[1] = 1;
         }
-        ptx::tc_commit(bar(kVEmpty0 + s));
         pt0 = PROF_T();
         if (fln & 0xf0) issue_qk(1, s ^ 1);
         pt_qk += PROF_T() - pt0;
-        if (next) ptx::tc_commit(bar(kKEmpty0 + (s ^ 1)));
+        ptx::tc_commit(bar(kEmpty0 + s));
       }
       ptx::tc_commit(bar(kOFinal));
       PROF_ADD(0, PROF_T() - pt_begin);   // MMA loop total
