@@ -27,13 +27,14 @@ namespace {
 constexpr int kThreads = 384;
 constexpr int kTile = 128;
 constexpr int kStages = 4;
+constexpr int kPairStages = kStages / 2;
 
 enum BarrierIndex {
   kQFull = 0,
   kQReady,
-  kKFull0,                      // kStages
-  kKEmpty0 = kKFull0 + kStages, // kStages
-  kSFull0 = kKEmpty0 + kStages, // 2: accumulator b holds the scores of key tiles 2*pj, 2*pj+1
+  kKFull0,                          // kPairStages: both key tiles of a pair have landed
+  kKEmpty0 = kKFull0 + kPairStages, // kPairStages
+  kSFull0 = kKEmpty0 + kPairStages, // 2: accumulator b holds the scores of key tiles 2*pj, 2*pj+1
   kSFree0 = kSFull0 + 2,        // 2
   kNumBarriers = kSFree0 + 2
 };
@@ -115,46 +116,55 @@ __global__ void __launch_bounds__(kThreads, 1) replay_map_kernel(
     if (lane == 0) {
       ptx::mbar_expect_tx(bar(kQFull), kTileBytes);
       for (int c = 0; c < kChunks; ++c) ptx::tma_load_3d(sQ + c * kChunkBytes, &tm_q, bar(kQFull), c * 64, qrow0, bh);
+      // two key tiles (one N = 256 operand) share a barrier pair: the issuing thread pays one wait and one
+      // commit per MMA group for its operands
       bool ok = true;
       int issued = 0;
-      for (int j = 0; j < ntk; ++j) {
-        const int s = j % kStages;
-        ok = ptx::mbar_wait(bar(kKEmpty0 + s), ((j / kStages) & 1) ^ 1, abort_flag);
+      for (int j = 0; j < ntk; j += 2) {
+        const int pj = j / 2;
+        const int ps = pj % kPairStages;
+        const bool two = (j + 1) < ntk;
+        ok = ptx::mbar_wait(bar(kKEmpty0 + ps), ((pj / kPairStages) & 1) ^ 1, abort_flag);
         if (!ok) { report(status, 1, 0, j); break; }
-        ptx::mbar_expect_tx(bar(kKFull0 + s), kTileBytes);
-        for (int c = 0; c < kChunks; ++c)
-          ptx::tma_load_3d(sK + c * kRingChunkBytes + s * kChunkBytes, &tm_k, bar(kKFull0 + s), c * 64, k_off + j * kTile,
-                           bh);
-        issued = j + 1;
+        ptx::mbar_expect_tx(bar(kKFull0 + ps), (two ? 2u : 1u) * kTileBytes);
+        for (int t = 0; t < (two ? 2 : 1); ++t)
+          for (int c = 0; c < kChunks; ++c)
+            ptx::tma_load_3d(sK + c * kRingChunkBytes + (2 * ps + t) * kChunkBytes, &tm_k, bar(kKFull0 + ps), c * 64,
+                             k_off + (j + t) * kTile, bh);
+        issued = pj + 1;
       }
       if (!ok) {
-        for (int j = max(0, issued - kStages); j < issued; ++j)
-          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(kKFull0 + j % kStages), (j / kStages) & 1); ++i) {}
+        for (int pj = max(0, issued - kPairStages); pj < issued; ++pj)
+          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(kKFull0 + pj % kPairStages), (pj / kPairStages) & 1); ++i) {}
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = ptx::mbar_wait(bar(kQReady), 0, abort_flag);
       if (!ok) report(status, 2, 1, -1);
+      const uint64_t dq0 = ptx::smem_desc_sw128(sQ, 16, 1024);
+      const uint64_t dk0 = ptx::smem_desc_sw128(sK, 16, 1024);
+      auto advance = [](uint64_t desc, uint32_t bytes) -> uint64_t {
+        // the start-address field (units of 16 bytes) never carries out for shared-memory addresses
+        return (desc & 0xffffffff00000000ull) | static_cast<uint32_t>(static_cast<uint32_t>(desc) + (bytes >> 4));
+      };
       for (int j = 0; j < ntk && ok; j += 2) {
-        const int s = j % kStages;                  // even: 0 or 2, so stage s+1 follows it in the ring
         const int pj = j / 2;
+        const int ps = pj % kPairStages;
         const int b = pj & 1;
         const bool two = (j + 1) < ntk;
-        ok = ptx::mbar_wait(bar(kKFull0 + s), (j / kStages) & 1, abort_flag);
-        if (ok && two) ok = ptx::mbar_wait(bar(kKFull0 + s + 1), (j / kStages) & 1, abort_flag);
+        ok = ptx::mbar_wait(bar(kKFull0 + ps), (pj / kPairStages) & 1, abort_flag);
         if (ok) ok = ptx::mbar_wait(bar(kSFree0 + b), ((pj >> 1) & 1) ^ 1, abort_flag);
         if (!ok) { report(status, 2, 1, j); break; }
         ptx::tc_fence_after();
+        const uint64_t dk = advance(dk0, static_cast<uint32_t>(2 * ps) * kChunkBytes);
+        const uint32_t idesc = two ? kIdesc256 : kIdesc128;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t a = ptx::smem_desc_sw128(sQ + (kk / 4) * kChunkBytes + (kk % 4) * 32, 16, 1024);
-          const uint64_t bd = ptx::smem_desc_sw128(sK + (kk / 4) * kRingChunkBytes + s * kChunkBytes + (kk % 4) * 32, 16, 1024);
-          ptx::mma_ss(tmem + b * 256, a, bd, two ? kIdesc256 : kIdesc128, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          ptx::mma_ss(tmem + b * 256, advance(dq0, (kk / 4) * kChunkBytes + (kk % 4) * 32),
+                      advance(dk, (kk / 4) * kRingChunkBytes + (kk % 4) * 32), idesc, kk > 0 ? 1u : 0u);
         ptx::tc_commit(bar(kSFull0 + b));
-        ptx::tc_commit(bar(kKEmpty0 + s));
-        if (two) ptx::tc_commit(bar(kKEmpty0 + s + 1));
+        ptx::tc_commit(bar(kKEmpty0 + ps));
       }
     }
   } else if (warp >= 4) {
