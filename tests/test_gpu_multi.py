@@ -75,7 +75,7 @@ for (H, N, D, bs, dt) in ((4, 1344, 128, 128, torch.bfloat16), (2, 1472, 64, 64,
 
 # state machine: the step fed with shard-pooled means equals the step that pools the gathered heads
 H, T, F, D, bs = 4, 5, 256, 128, 128
-N = T * F + 64                                            # 1344: 640 rows per rank, boundary inside block 5
+N = T * F + 128                                           # 1408: 704 rows per rank, boundary inside block 5
 g = torch.Generator().manual_seed(3)
 q, k, v = (torch.randn(1, H, N, D, generator=g).bfloat16() for _ in range(3))
 b, e = md.shard_bounds(N, world, rank)
@@ -84,7 +84,7 @@ pr = md.PeerResharder(H, N, D, torch.bfloat16, dev)
 pr.enable_pooling(bs)
 log = logging.getLogger("t")
 def state():
-    st = create_adaptive_mask_state("hunyuan", he - hb, T * F, 64, F, T, warmup_steps=2, top_k=6, predict_T=5, block_size=bs)
+    st = create_adaptive_mask_state("hunyuan", he - hb, T * F, 128, F, T, warmup_steps=2, top_k=6, predict_T=5, block_size=bs)
     st["score_producer"] = "pooled"
     return st
 st_a, st_b = state(), state()
@@ -119,7 +119,8 @@ def _run_two_ranks(tmp_path, text):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", str(29600 + os.getpid() % 300), str(script), ROOT]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    first = res.stderr.find("Traceback")            # the child's own traceback comes before the launcher's summary
+    assert res.returncode == 0, res.stdout[-1000:] + res.stderr[max(first, 0):][:3000]
     assert res.stdout.count("CHILD_OK") == 2
 
 
