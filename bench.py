@@ -248,9 +248,10 @@ def run_ours(args):
     for name, ms in records:
         stage_ms[name] = stage_ms.get(name, 0.0) + ms
     attn_ms = stage_ms.get("moddit_sparse_attn_fwd", 0.0) / args.steps
-    comm_ms = stage_ms.get("moddit_copy_rows", 0.0) / args.steps       # re-shard copies (N > 1 only)
+    copies = ("moddit_copy_rows", "moddit_copy_rows_dma")               # re-shard copies (N > 1 only)
+    comm_ms = sum(stage_ms.get(name, 0.0) for name in copies) / args.steps
     pred_ms = sum(ms for name, ms in stage_ms.items()
-                  if name not in ("moddit_sparse_attn_fwd", "moddit_copy_rows")) / args.steps
+                  if name not in ("moddit_sparse_attn_fwd",) + copies) / args.steps
 
     # ---- e2e: inputs in pinned host memory, output copied back ----------------------------------
     e2e_steps = max(1, min(args.steps, args.e2e_steps))

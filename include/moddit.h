@@ -227,6 +227,11 @@ int moddit_copy_rows(const void* src, void* dst, int64_t src_pitch, int64_t dst_
 int moddit_copy_rows_multi(const void* const* src, void* const* dst, int n_jobs, int64_t src_pitch,
                            int64_t dst_pitch, int64_t width_bytes, int rows, void* stream);
 
+/* The same copy on the GPU's copy engines (one asynchronous 2-D copy, no kernel): for the bulk pieces of the
+ * re-shard, which then neither occupy SMs nor compete with the step's kernels; no alignment requirement. */
+int moddit_copy_rows_dma(const void* src, void* dst, int64_t src_pitch, int64_t dst_pitch, int64_t width_bytes,
+                         int rows, void* stream);
+
 /* moddit_sparse_attn_fwd with the output re-shard fused into the epilogue: rows of sequence shard r
  * ([r*N/n_peers, (r+1)*N/n_peers)) of local head bh are stored into peer_out[r], a (total_heads, N/n_peers, D)
  * buffer of rank r mapped into this process, at head `head_base + bh` (plain peer stores).  `peer_out` is a

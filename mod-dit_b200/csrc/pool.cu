@@ -402,6 +402,22 @@ extern "C" int moddit_copy_rows_multi(const void* const* src, void* const* dst, 
   return MODDIT_OK;
 }
 
+// The same strided copy on the copy engines (no SM is used): one 2-D asynchronous copy.  On an NVLink node a
+// peer destination gets the full link bandwidth and the SMs stay free for the kernels of the step.
+extern "C" int moddit_copy_rows_dma(const void* src, void* dst, int64_t src_pitch, int64_t dst_pitch,
+                                    int64_t width_bytes, int rows, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(src && dst, "copy_rows_dma: null pointer");
+  MODDIT_CHECK_ARG(rows > 0 && width_bytes > 0 && src_pitch >= width_bytes && dst_pitch >= width_bytes,
+                   "copy_rows_dma: rows=%d width=%lld pitches %lld/%lld out of range", rows,
+                   static_cast<long long>(width_bytes), static_cast<long long>(src_pitch),
+                   static_cast<long long>(dst_pitch));
+  MODDIT_CHECK_CUDA(cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_pitch), src, static_cast<size_t>(src_pitch),
+                                      static_cast<size_t>(width_bytes), static_cast<size_t>(rows), cudaMemcpyDefault,
+                                      as_stream(stream)));
+  return MODDIT_OK;
+}
+
 extern "C" int moddit_copy_rows(const void* src, void* dst, int64_t src_pitch, int64_t dst_pitch, int64_t width_bytes,
                                 int rows, void* stream) {
   clear_error();

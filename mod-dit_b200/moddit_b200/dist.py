@@ -148,7 +148,8 @@ class PeerResharder:
     """
 
     def __init__(self, heads: int, seq_len: int, head_dim: int, dtype: torch.dtype, device: torch.device,
-                 group: Optional[dist.ProcessGroup] = None, n_inputs: int = 3, timeout_ms: int = 20000):
+                 group: Optional[dist.ProcessGroup] = None, n_inputs: int = 3, timeout_ms: int = 20000,
+                 bulk_copy: str = "dma"):
         import torch.distributed._symmetric_memory as symm_mem
         from . import ops
         self._ops = ops
@@ -162,6 +163,9 @@ class PeerResharder:
         self.dtype, self.device = dtype, device
         self.esize = torch.empty((), dtype=dtype).element_size()
         self.timeout_ms = timeout_ms
+        if bulk_copy not in ("dma", "kernel"):
+            raise ValueError("bulk_copy must be 'dma' (copy engines) or 'kernel' (this library's copy kernel)")
+        self.bulk_copy = bulk_copy
         self.inputs, self.in_handles = [], []
         for _ in range(n_inputs):
             t = symm_mem.empty((1, self.hp, self.N, self.D), dtype=dtype, device=device)
@@ -189,9 +193,7 @@ class PeerResharder:
             for x, slot in zip(xs, slots):
                 src.append(x.data_ptr() + peer * self.hp * row)
                 dst.append(int(self.in_handles[slot].buffer_ptrs[peer]) + self.rank * row)
-        for i in range(0, len(src), 24):                               # one launch per 24 (peer, tensor) pairs
-            self._ops.copy_rows_multi(src[i:i + 24], dst[i:i + 24], row, self.N * self.D * self.esize, row, self.hp,
-                                      self.device)
+        self._bulk(src, dst, row, self.N * self.D * self.esize, row, self.hp)
         sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # every rank's stores have landed
         return [self.inputs[slot] for slot in slots]
 
@@ -207,9 +209,20 @@ class PeerResharder:
             peer = (self.rank + step) % self.world
             src.append(x.data_ptr() + peer * row)
             dst.append(int(hdl.buffer_ptrs[peer]) + self.rank * self.hp * row)
-        self._ops.copy_rows_multi(src, dst, self.N * self.D * self.esize, row, row, self.hp, self.device)
+        self._bulk(src, dst, self.N * self.D * self.esize, row, row, self.hp)
         hdl.barrier(channel=channel, timeout_ms=self.timeout_ms)
         return self.output
+
+    def _bulk(self, src, dst, src_pitch: int, dst_pitch: int, width: int, rows: int) -> None:
+        """The (peer, tensor) pieces of one exchange: asynchronous 2-D copies on the copy engines (the SMs stay
+        with the kernels of the step, a peer gets the whole link), or this library's copy kernel, one launch
+        per 24 pieces."""
+        if self.bulk_copy == "dma":
+            for s_, d_ in zip(src, dst):
+                self._ops.copy_rows_dma(s_, d_, src_pitch, dst_pitch, width, rows, self.device)
+            return
+        for i in range(0, len(src), 24):
+            self._ops.copy_rows_multi(src[i:i + 24], dst[i:i + 24], src_pitch, dst_pitch, width, rows, self.device)
 
     # ---- block means of query and key, pooled on the sequence shards ----------------------------------------
     def enable_pooling(self, block_size: int) -> None:

@@ -26,7 +26,7 @@ KERNELS_PER_CALL = {"moddit_pool_blocks": 1, "moddit_pooled_map": 1, "moddit_rep
                     "moddit_mtm": 1, "moddit_solve": 3, "moddit_select_lines": 1, "moddit_head_modes": 1,
                     "moddit_mask_from_lines": 1, "moddit_select_mass": 1, "moddit_tile_lists": 2,
                     "moddit_sparse_attn_fwd": 1, "moddit_replay_status": 0,
-                    "moddit_mts_noalloc": 2}
+                    "moddit_mts_noalloc": 2, "moddit_copy_rows_dma": 0}
 
 
 def stage_timing(enable: bool) -> None:
@@ -388,6 +388,14 @@ def copy_rows(src_ptr: int, dst_ptr: int, src_pitch: int, dst_pitch: int, width_
     with torch.cuda.device(device), _timed("moddit_copy_rows", device):
         check(lib.moddit_copy_rows(ctypes.c_void_p(src_ptr), ctypes.c_void_p(dst_ptr), src_pitch, dst_pitch,
                                    width_bytes, rows, _stream(device)), "moddit_copy_rows")
+
+
+def copy_rows_dma(src_ptr: int, dst_ptr: int, src_pitch: int, dst_pitch: int, width_bytes: int, rows: int,
+                  device: torch.device) -> None:
+    """`copy_rows` on the copy engines (no kernel launch, hence not counted as one)."""
+    with torch.cuda.device(device), _timed("moddit_copy_rows_dma", device):
+        check(lib.moddit_copy_rows_dma(ctypes.c_void_p(src_ptr), ctypes.c_void_p(dst_ptr), src_pitch, dst_pitch,
+                                       width_bytes, rows, _stream(device)), "moddit_copy_rows_dma")
 
 
 def copy_rows_multi(src_ptrs, dst_ptrs, src_pitch: int, dst_pitch: int, width_bytes: int, rows: int,
