@@ -20,7 +20,7 @@ _DTYPE = {torch.bfloat16: _lib.MODDIT_BF16, torch.float16: _lib.MODDIT_FP16}
 # ---------------------------------------------------------------------------------------------
 # optional per-entry-point timing (CUDA events on the launching stream); off by default
 # ---------------------------------------------------------------------------------------------
-_TIMING = {"on": False, "records": [], "launches": 0}
+_TIMING = {"on": False, "only": None, "records": [], "launches": 0}
 # kernels launched by one call of each entry point (for launch accounting in benchmarks)
 KERNELS_PER_CALL = {"moddit_pool_blocks": 1, "moddit_pooled_map": 1, "moddit_replay_map": 1, "moddit_mts": 2,
                     "moddit_mtm": 1, "moddit_solve": 3, "moddit_select_lines": 1, "moddit_head_modes": 1,
@@ -29,9 +29,11 @@ KERNELS_PER_CALL = {"moddit_pool_blocks": 1, "moddit_pooled_map": 1, "moddit_rep
                     "moddit_mts_noalloc": 2, "moddit_copy_rows_dma": 0}
 
 
-def stage_timing(enable: bool) -> None:
-    """Turn event timing of every entry-point call on or off and clear the records."""
+def stage_timing(enable: bool, only=None) -> None:
+    """Turn launch counting and event timing of the entry-point calls on or off and clear the records.
+    `only`: names of the entry points to time (all when None); the others are still counted."""
     _TIMING["on"] = bool(enable)
+    _TIMING["only"] = None if only is None else frozenset(only)
     _TIMING["records"] = []
     _TIMING["launches"] = 0
 
@@ -53,16 +55,18 @@ class _timed:
         self.name, self.dev = name, dev
 
     def __enter__(self):
-        if _TIMING["on"]:
+        self.start = None
+        if _TIMING["on"] and (_TIMING["only"] is None or self.name in _TIMING["only"]):
             self.start = torch.cuda.Event(enable_timing=True)
             self.start.record(torch.cuda.current_stream(self.dev))
         return self
 
     def __exit__(self, *exc):
         if _TIMING["on"]:
-            end = torch.cuda.Event(enable_timing=True)
-            end.record(torch.cuda.current_stream(self.dev))
-            _TIMING["records"].append((self.name, self.start, end))
+            if self.start is not None:
+                end = torch.cuda.Event(enable_timing=True)
+                end.record(torch.cuda.current_stream(self.dev))
+                _TIMING["records"].append((self.name, self.start, end))
             _TIMING["launches"] += KERNELS_PER_CALL.get(self.name, 1)
         return False
 
