@@ -179,6 +179,14 @@ int moddit_mask_from_lines(const int64_t* selected, int k, const int32_t* modes,
                            int blocks_per_frame, int layout, int text_blocks, int nbt, uint8_t* mask,
                            void* stream);
 
+/* Static block mask of the radial comparison mode (`--sparse_type radial`).  Replaces `get_radial_mask`
+ * (MoD/mod/get_radial_mask.py:157-164; construction :84-130, :47-82, :18-31) for one head - the reference
+ * repeats the same mask for every head.  layout: MODDIT_LAYOUT_HUNYUAN or MODDIT_LAYOUT_WAN (the reference
+ * raises for anything else).  mask: (seq_len/block_size)^2 bool bytes, text rows and columns all true.
+ * The reference always calls it with block_size 128 and decay_factor 0.2. */
+int moddit_radial_mask(int layout, int video_tokens, int num_frames, int seq_len, int block_size,
+                       float decay_factor, uint8_t* mask, void* stream);
+
 /* Cumulative-mass selection on a darkness map (no reference function).  keep: (H,n,n) bool bytes. */
 int moddit_select_mass(const void* map_f16, int H, int n, float tau, uint8_t* keep, void* stream);
 

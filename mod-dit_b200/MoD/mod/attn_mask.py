@@ -12,7 +12,8 @@ Differences that are deliberate:
     third-party sparse kernel coarsens it to 128-row x 64-column tiles);
   * two optional state keys, `score_producer='pooled'` and `selector='cumulative_mass'`, enable the
     mean-pooled map producer and the cumulative-mass selector; their defaults keep reference behaviour;
-  * 'radial' and 'spargeattn' baselines are not part of this build and raise NotImplementedError.
+  * `sparse_type='radial'` runs its static mask (MoD/mod/get_radial_mask.py) through the same sparse
+    forward; the 'spargeattn' and 'svg' baselines are not part of this build and raise NotImplementedError.
 """
 import logging
 from typing import Dict, List, Optional, Tuple
@@ -20,6 +21,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from MoD.mod.cuda_lstsq import features_from_solution, solve_lstsq
+from MoD.mod.get_radial_mask import get_radial_mask
 from MoD.mod.state import is_warmup_complete
 from MoD.mod.triton_flash_sparsity import dense_attention_with_lse, flash_attn_with_sparsity_map
 from moddit_b200 import _lib
@@ -300,8 +302,10 @@ def SparseAttentionWithMap(
         output, _ = dense_attention_with_lse(query, key, value, kv_len=valid)
         return output, {'mode': 'warmup', 'mask': None}
     sparse_type = warmup_state['sparse_type']
-    if sparse_type in ('spargeattn', 'radial', 'svg'):
+    if sparse_type in ('spargeattn', 'svg'):
         raise NotImplementedError(f"sparse_type '{sparse_type}' is a third-party baseline that this build does not include")
+    if sparse_type == 'radial':
+        return _radial_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx)
 
     pooled = warmup_state.get('score_producer', 'replay') == 'pooled'
     warmup_steps = warmup_state['warmup_steps']
@@ -360,6 +364,34 @@ def SparseAttentionWithMap(
                                        video_token_num=video_token_num, block_size=block_size,
                                        _lists=_lists_for(warmup_state, seq_len),
                                        _scatter=kwargs.get('output_scatter'))
+    return output, {'mask': warmup_state['mask']}
+
+
+def _radial_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx):
+    """`sparse_type='radial'` (:624-630, :713-722): a static mask shared by all heads, built on first use;
+    dense attention over all keys during the warm-up steps, the block-sparse forward afterwards."""
+    seq_len = query.size(2)
+    bs = warmup_state['block_size']
+    if bs != 128:
+        raise ValueError("the radial mask is built for block_size 128 (the reference never passes another size)")
+    query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
+    if warmup_state.get('mask', None) is None:
+        mask = get_radial_mask(query, warmup_state['video_token_num'], warmup_state['num_frames'],
+                               model_type=warmup_state['model_type'])
+        nb = (seq_len + bs - 1) // bs
+        if mask.shape[-1] != nb:
+            raise ValueError(f"mask of {mask.shape[-1]} blocks does not cover a sequence of {nb} blocks")
+        warmup_state['mask'] = mask
+        # every head shares the mask: one work list serves all heads
+        warmup_state['_tile_lists'] = (mask, _ops.tile_lists(mask[:1].contiguous(), bs, seq_len))
+        warmup_state['_radial_sparsity'] = 1.0 - float(mask[0].float().mean())
+    if current_step < warmup_state['warmup_steps']:
+        logger.info(f"Layer {layer_idx}, Mask Sparsity: {warmup_state['_radial_sparsity']:.3%}")
+        output, _ = dense_attention_with_lse(query, key, value, kv_len=seq_len)
+        return output, {'mode': 'warmup', 'mask': None}
+    output = AttentionSparseEngine(query, key, value, warmup_state['mask'], pre_defined_mask=pre_defined_mask,
+                                   video_token_num=warmup_state.get('video_token_num', 0), block_size=bs,
+                                   _lists=_lists_for(warmup_state, seq_len))
     return output, {'mask': warmup_state['mask']}
 
 

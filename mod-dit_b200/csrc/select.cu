@@ -256,6 +256,63 @@ __global__ void __launch_bounds__(256) order_pairs_kernel(const int32_t* __restr
   }
 }
 
+
+// ---- static radial mask (comparison mode `--sparse_type radial`) -----------------------------------------
+// The reference builds, for every pair of frames, a token-level band |col - row| <= width(frame distance),
+// drops whole frame distances at a distance-dependent stride, places the band in a tile padded to the block
+// grid and keeps a block when more than 60 % of its non-empty columns are more than a third full; the
+// tiles are OR-ed into the mask and text rows/columns are all true.  A column's fill is the overlap of two
+// intervals, so a block is decided in O(block_size) integer operations without any token-level array: one
+// thread per block, looping over the frame pairs whose tile covers it.
+constexpr int kMaxRadialFrames = 128;
+struct RadialTable {
+  int width[kMaxRadialFrames];        // band half-width per frame distance (floor of the float32 bound)
+  uint8_t kept[kMaxRadialFrames];     // whether that frame distance is kept at all
+};
+
+__global__ void __launch_bounds__(256) radial_mask_kernel(const __grid_constant__ RadialTable tab, int tpf, int frames,
+                                                          int bs, int nb, int border, int first_col_all,
+                                                          uint8_t* __restrict__ mask) {
+  const int C = blockIdx.x * blockDim.x + threadIdx.x;
+  const int R = blockIdx.y;
+  if (C >= nb) return;
+  bool keep = (R >= border) || (C >= border);
+  if (!keep) {
+    const int k = (tpf - 1) / bs + 1;                       // blocks per side of a frame-pair tile
+    // frames whose tile covers block row R: (R-k+1)*bs <= i*tpf < (R+1)*bs
+    const long long lo_r = static_cast<long long>(R - k + 1) * bs, hi_r = static_cast<long long>(R + 1) * bs;
+    const long long lo_c = static_cast<long long>(C - k + 1) * bs, hi_c = static_cast<long long>(C + 1) * bs;
+    const int i0 = lo_r <= 0 ? 0 : static_cast<int>((lo_r + tpf - 1) / tpf);
+    const int i1 = min(frames - 1, static_cast<int>((hi_r + tpf - 1) / tpf) - 1);
+    const int j0 = lo_c <= 0 ? 0 : static_cast<int>((lo_c + tpf - 1) / tpf);
+    const int j1 = min(frames - 1, static_cast<int>((hi_c + tpf - 1) / tpf) - 1);
+    for (int i = i0; i <= i1 && !keep; ++i) {
+      const long long ti = static_cast<long long>(i) * tpf;
+      const int lr = R - static_cast<int>(ti / bs), rem_r = static_cast<int>(ti % bs);
+      const int ra = max(0, lr * bs - rem_r), rb = min(tpf, (lr + 1) * bs - rem_r);    // local rows [ra, rb)
+      if (rb <= ra) continue;
+      for (int j = j0; j <= j1 && !keep; ++j) {
+        const long long tj = static_cast<long long>(j) * tpf;
+        const int lc = C - static_cast<int>(tj / bs), rem_c = static_cast<int>(tj % bs);
+        const int ca = max(0, lc * bs - rem_c), cb = min(tpf, (lc + 1) * bs - rem_c);  // local columns [ca, cb)
+        if (cb <= ca) continue;
+        const int dist = abs(i - j);
+        const bool all = first_col_all && j == 0;
+        if (!all && !tab.kept[dist]) continue;
+        const int W = all ? tpf : tab.width[dist];
+        int nonzero = 0, high = 0;
+        for (int c = ca; c < cb; ++c) {
+          const int cnt = min(rb - 1, c + W) - max(ra, c - W) + 1;
+          nonzero += cnt > 0;
+          high += 3 * cnt > bs;
+        }
+        keep = nonzero > 0 && 5 * high > 3 * nonzero;
+      }
+    }
+  }
+  mask[static_cast<int64_t>(R) * nb + C] = keep ? 1 : 0;
+}
+
 }  // namespace
 }  // namespace moddit
 
@@ -348,5 +405,53 @@ extern "C" int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, 
     order_pairs_kernel<<<Hm, 256, sizeof(int32_t) * npairs, as_stream(stream)>>>(counts, npairs, order);
     MODDIT_CHECK_LAUNCH("order_pairs_kernel");
   }
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_radial_mask(int layout, int video_tokens, int num_frames, int seq_len, int block_size,
+                                  float decay_factor, uint8_t* mask, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(mask, "radial_mask: null pointer");
+  MODDIT_CHECK_ARG(video_tokens > 0 && num_frames > 0 && seq_len >= video_tokens && block_size > 0,
+                   "radial_mask: video=%d frames=%d seq=%d block=%d out of range", video_tokens, num_frames, seq_len,
+                   block_size);
+  MODDIT_CHECK_ARG(decay_factor > 0.f, "radial_mask: decay_factor must be positive");
+  if (layout != MODDIT_LAYOUT_HUNYUAN && layout != MODDIT_LAYOUT_WAN)
+    return fail(MODDIT_E_ARG, "radial_mask: Unknown model type: layout %d (hunyuan and wan only)", layout);
+  if (num_frames > kMaxRadialFrames)
+    return fail(MODDIT_E_UNSUPPORTED, "radial_mask: %d frames exceed %d", num_frames, kMaxRadialFrames);
+  const int tpf = video_tokens / num_frames;
+  MODDIT_CHECK_ARG(tpf > 0, "radial_mask: fewer video tokens than frames");
+  const int nb = seq_len / block_size;
+  MODDIT_CHECK_ARG(nb > 0, "radial_mask: sequence shorter than a block");
+  const int k = (tpf - 1) / block_size + 1;
+  MODDIT_CHECK_ARG(static_cast<long long>(num_frames - 1) * tpf / block_size + k <= nb,
+                   "radial_mask: the last frame's tile does not fit %d blocks", nb);
+  if (int rc = require_sm100()) return rc;
+  // band half-width and kept flag per frame distance, in the reference's arithmetic: powers of two and the
+  // decay factor in double precision, the comparison against token distances in float32
+  RadialTable tab = {};
+  int bits = 0;
+  for (int t = tpf; t > 0; t >>= 1) ++bits;                 // tpf.bit_length()
+  const double pow_tpf = ldexp(1.0, bits);
+  for (int dist = 0; dist < num_frames; ++dist) {
+    int group = 0;
+    for (int t = dist; t > 0; t >>= 1) ++group;             // dist.bit_length()
+    double width;
+    if ((layout == MODDIT_LAYOUT_WAN && dist < 1) || (layout == MODDIT_LAYOUT_HUNYUAN && dist <= 1)) {
+      width = tpf;
+    } else if (layout == MODDIT_LAYOUT_WAN && dist == 1) {
+      width = tpf / 2;
+    } else {
+      const double decay = pow_tpf / ldexp(1.0, group) * static_cast<double>(decay_factor);
+      width = decay >= block_size ? decay : block_size;
+    }
+    tab.width[dist] = static_cast<int>(floorf(fminf(static_cast<float>(width), 1.0e9f)));
+    const double plain = pow_tpf / ldexp(1.0, group);
+    tab.kept[dist] = plain >= 128.0 ? 1 : (dist % static_cast<int>(128.0 / plain) == 0);
+  }
+  radial_mask_kernel<<<dim3(ceil_div(nb, 256), nb), 256, 0, as_stream(stream)>>>(
+      tab, tpf, num_frames, block_size, nb, video_tokens / block_size, layout == MODDIT_LAYOUT_WAN ? 1 : 0, mask);
+  MODDIT_CHECK_LAUNCH("radial_mask_kernel");
   return MODDIT_OK;
 }

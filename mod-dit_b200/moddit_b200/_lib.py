@@ -47,6 +47,7 @@ SIGNATURES = {
     "moddit_select_lines": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                                     c_void_p, c_void_p]),
     "moddit_head_modes": (c_int, [c_void_p, c_int, c_float, c_void_p, c_void_p]),
+    "moddit_radial_mask": (c_int, [c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
     "moddit_mask_from_lines": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_void_p, c_void_p]),
     "moddit_select_mass": (c_int, [c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),

@@ -345,6 +345,23 @@ def mask_from_lines(selected: torch.Tensor, modes: torch.Tensor, *, n: int, bloc
     return mask
 
 
+def radial_mask(model_type: str, video_token_num: int, num_frames: int, seq_len: int, device: torch.device,
+                block_size: int = 128, decay_factor: float = 0.2) -> torch.Tensor:
+    """(seq_len//block_size, seq_len//block_size) bool: the static radial block mask (one head)."""
+    if model_type not in ("hunyuan", "wan"):
+        raise ValueError(f"Unknown model type: {model_type}")
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError("moddit_b200 runs on CUDA devices only (no CPU fallback)")
+    nb = seq_len // block_size
+    mask = torch.empty(nb, nb, device=device, dtype=torch.bool)
+    with torch.cuda.device(device), _timed("moddit_radial_mask", device):
+        check(lib.moddit_radial_mask(_lib.LAYOUT[model_type], int(video_token_num), int(num_frames), int(seq_len),
+                                     int(block_size), float(decay_factor), _ptr(mask), _stream(device)),
+              "moddit_radial_mask")
+    return mask
+
+
 def select_mass(dark_map: torch.Tensor, tau: float) -> torch.Tensor:
     dev = _need_cuda(dark_map)
     dark_map = dark_map.to(torch.float16).contiguous()

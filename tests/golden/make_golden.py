@@ -168,7 +168,23 @@ def main():
         out[f"sel{ci}_mask2"] = mask_modes.numpy()
     np.savez_compressed(os.path.join(HERE, "selection.npz"), **out)
 
-    # ---- 4. state keys -----------------------------------------------------------------------------
+    # ---- 4. static radial masks (frames of whole, fractional and sub-block size; both model layouts) ---
+    out = {}
+    radial_cases = [("hunyuan", 1536, 6, 128), ("hunyuan", 1920, 5, 256), ("hunyuan", 1280, 4, 128),
+                    ("wan", 1600, 8, 64), ("wan", 2560, 10, 0), ("hunyuan", 2560, 20, 128), ("wan", 3072, 12, 0),
+                    ("hunyuan", 7680, 30, 256), ("wan", 6240, 13, 32)]
+    for ci, (model_type, video, frames, text) in enumerate(radial_cases):
+        q = torch.zeros(1, 1, video + text, 8)
+        with contextlib.redirect_stdout(io.StringIO()):
+            mask = am.get_radial_mask(q, video, frames, model_type=model_type)
+        out[f"rad{ci}_model"] = np.array(model_type)
+        out[f"rad{ci}_meta"] = np.array([video, frames, text], dtype=np.int64)
+        out[f"rad{ci}_mask"] = np.packbits(mask[0].numpy())
+        out[f"rad{ci}_shape"] = np.array(mask[0].shape, dtype=np.int64)
+    out["count"] = np.array(len(radial_cases))
+    np.savez_compressed(os.path.join(HERE, "radial.npz"), **out)
+
+    # ---- 5. state keys -----------------------------------------------------------------------------
     state = st.create_adaptive_mask_state("hunyuan", 24, 115200, 256, 3840, 30)
     with open(os.path.join(HERE, "state_keys.txt"), "w") as fh:
         for key in state:

@@ -176,3 +176,30 @@ def test_dense_forward_lse_and_replay_at_full_size(env):
         below = sc < (lse_h[0, 0, i * BS:(i + 1) * BS] + log_thr).unsqueeze(1)
         cnt = below.view(BS, NV, BS).sum(dim=(0, 2)).float()
         assert ((got[i].float() * BS * BS) - (cnt / (BS * BS)).half().float() * BS * BS).abs().max().item() <= 16.0
+
+
+def test_radial_mask_at_full_size():
+    """HunyuanVideo geometry (30 frames of 3840 tokens + 256 text tokens): text rows/columns all true, the mask is
+    symmetric, every frame-pair tile depends on the frame distance only, and the tiles of distances 0..7 equal
+    those of the CPU oracle run on 8 frames of the same size (the oracle builds token-level masks, so the full
+    900 frame pairs are left to these properties)."""
+    from moddit_b200 import ops
+    tpf, T, text = 3840, 30, 256
+    video, S = tpf * T, tpf * T + text
+    m = ops.radial_mask("hunyuan", video, T, S, torch.device("cuda")).cpu()
+    n, k = video // 128, tpf // 128
+    assert m.shape == (S // 128, S // 128)
+    assert bool(m[n:].all()) and bool(m[:, n:].all())
+    assert torch.equal(m, m.t())
+    tiles = m[:n, :n].reshape(T, k, T, k).permute(0, 2, 1, 3)           # (frame i, frame j, k, k)
+    for d in range(T):
+        first = tiles[0, d]
+        for i in range(T - d):
+            assert torch.equal(tiles[i, i + d], first), (i, d)
+    small = torch.from_numpy(orc.radial_mask("hunyuan", tpf * 8, 8, tpf * 8 + text))
+    small_tiles = small[:8 * k, :8 * k].reshape(8, k, 8, k).permute(0, 2, 1, 3)
+    for d in range(8):
+        assert torch.equal(tiles[0, d], small_tiles[0, d]), d
+    assert bool(tiles[0, 0].all()) and bool(tiles[0, 1].all())             # neighbouring frames are kept whole
+    sparsity = 1.0 - m.float().mean().item()
+    assert 0.5 < sparsity < 0.95

@@ -221,6 +221,78 @@ def test_use_dense_and_unsupported_types(mod):
     out, info = am.SparseAttentionWithMap(q, q, q, state, LOG, use_dense=True, use_cuda=True)
     ref = orc.masked_attention(q.cpu(), q.cpu(), q.cpu(), torch.ones(1, 8, 8, dtype=torch.bool), 64)
     assert (out.float().cpu() - ref).abs().max().item() <= 2e-2 and info["mask"] is None
-    state["sparse_type"] = "radial"
+    state["sparse_type"] = "spargeattn"
     with pytest.raises(NotImplementedError):
         am.SparseAttentionWithMap(q, q, q, state, LOG, current_step=0)
+    state["sparse_type"] = "radial"            # the reference builds this mask for block_size 128 only
+    with pytest.raises(ValueError, match="block_size 128"):
+        am.SparseAttentionWithMap(q, q, q, state, LOG, current_step=0)
+
+
+@pytest.mark.parametrize("model_type,video,frames,text", [("hunyuan", 2560, 20, 128), ("hunyuan", 1280, 4, 128),
+                                                          ("wan", 2560, 10, 0), ("wan", 1600, 8, 64)])
+def test_radial_mask_kernel_against_oracle_and_reference(mod, golden_dir, model_type, video, frames, text):
+    """`get_radial_mask` (one closed-form kernel) against the oracle and the reference's stored masks."""
+    import numpy as np
+    from MoD.mod.get_radial_mask import get_radial_mask
+    S = video + text
+    q = torch.empty(1, 3, S, 8, device="cuda", dtype=torch.bfloat16)
+    mask = get_radial_mask(q, video, frames, model_type=model_type)
+    assert mask.shape == (3, S // 128, S // 128) and mask.dtype == torch.bool
+    want = orc.radial_mask(model_type, video, frames, S)
+    assert (mask[0].cpu().numpy() == want).all() and torch.equal(mask[0], mask[2])
+    g = np.load(os.path.join(golden_dir, "radial.npz"))
+    hits = 0
+    for ci in range(int(g["count"])):
+        if str(g[f"rad{ci}_model"]) == model_type and tuple(int(x) for x in g[f"rad{ci}_meta"]) == (video, frames, text):
+            shape = tuple(int(x) for x in g[f"rad{ci}_shape"])
+            ref = np.unpackbits(g[f"rad{ci}_mask"])[:shape[0] * shape[1]].reshape(shape).astype(bool)
+            assert (mask[0].cpu().numpy() == ref).all()
+            hits += 1
+    assert hits == 1
+    with pytest.raises(ValueError, match="Unknown model type"):
+        get_radial_mask(q, video, frames, model_type="cogvideox")
+
+
+def test_radial_mask_all_stored_reference_cases(mod, golden_dir):
+    import numpy as np
+    from moddit_b200 import ops
+    g = np.load(os.path.join(golden_dir, "radial.npz"))
+    for ci in range(int(g["count"])):
+        video, frames, text = (int(x) for x in g[f"rad{ci}_meta"])
+        shape = tuple(int(x) for x in g[f"rad{ci}_shape"])
+        ref = np.unpackbits(g[f"rad{ci}_mask"])[:shape[0] * shape[1]].reshape(shape).astype(bool)
+        got = ops.radial_mask(str(g[f"rad{ci}_model"]), video, frames, video + text, torch.device("cuda"))
+        assert (got.cpu().numpy() == ref).all(), ci
+    # other block sizes and decay factors exist in the reference function's signature: against the oracle
+    for bs, decay in ((64, 0.2), (128, 0.5), (128, 1.0)):
+        got = ops.radial_mask("hunyuan", 3840, 12, 3840 + 256, torch.device("cuda"), block_size=bs, decay_factor=decay)
+        assert (got.cpu().numpy() == orc.radial_mask("hunyuan", 3840, 12, 3840 + 256, bs, decay)).all(), (bs, decay)
+
+
+def test_radial_state_machine(mod):
+    """sparse_type='radial': dense output over all keys while warming up, then the sparse forward under the
+    static mask (text padding rules of the hunyuan layout included)."""
+    am, st = mod["am"], mod["st"]
+    H, T, Hh, Ww, D, text = 2, 10, 16, 16, 64, 128
+    video = T * Hh * Ww                                   # 2560 tokens, 256 per frame
+    q, k, v = _locality(7, H, T, Hh, Ww, D, text, False)
+    S = video + text
+    state = st.create_adaptive_mask_state("hunyuan", H, video, text, Hh * Ww, T, warmup_steps=2, block_size=128,
+                                          sparse_type="radial")
+    valid = S - 29
+    pdm = (torch.arange(S) < valid).unsqueeze(0).expand(S, S).contiguous().cuda()
+    want_mask = torch.from_numpy(orc.radial_mask("hunyuan", video, T, S))
+    dense = orc.masked_attention(q, k, v, torch.ones(1, S // 128, S // 128, dtype=torch.bool), 128)
+    for step in range(4):
+        out, info = am.SparseAttentionWithMap(q.cuda(), k.cuda(), v.cuda(), state, LOG, pre_defined_mask=pdm,
+                                              current_step=step)
+        if step < 2:
+            assert info == {"mode": "warmup", "mask": None}
+            assert (out.float().cpu() - dense).abs().max().item() <= 2e-2
+        else:
+            assert torch.equal(info["mask"][0].cpu(), want_mask) and info["mask"].shape[0] == H
+            ref = orc.masked_attention(q, k, v, want_mask[None], 128, q_split=video,
+                                       kv_len_lo=min(S, (valid + 63) // 64 * 64), kv_len_hi=valid)
+            assert (out.float().cpu() - ref).abs().max().item() <= 2e-2
+    assert not bool(want_mask.all())

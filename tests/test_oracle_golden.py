@@ -2,6 +2,7 @@
 import os
 
 import numpy as np
+import pytest
 import torch
 
 from oracle import moddit_oracle as orc
@@ -145,3 +146,18 @@ def test_select_mass_properties():
             assert keep[h, i, i]
             assert b[h, i][keep[h, i]].sum() >= 0.9 * b[h, i].sum() - 1e-3
     assert orc.select_mass(dark, 1.0).float().mean() > keep.float().mean()
+
+
+def test_radial_mask_matches_reference(golden_dir):
+    """The static radial mask of the reference's `get_radial_mask` (block 128, decay 0.2) on nine layouts."""
+    g = np.load(os.path.join(golden_dir, "radial.npz"))
+    for ci in range(int(g["count"])):
+        model_type = str(g[f"rad{ci}_model"])
+        video, frames, text = (int(x) for x in g[f"rad{ci}_meta"])
+        shape = tuple(int(x) for x in g[f"rad{ci}_shape"])
+        want = np.unpackbits(g[f"rad{ci}_mask"])[:shape[0] * shape[1]].reshape(shape).astype(bool)
+        got = orc.radial_mask(model_type, video, frames, video + text)
+        assert got.shape == want.shape
+        assert (got == want).all(), (model_type, video, frames, text)
+    with pytest.raises(ValueError):
+        orc.radial_mask("cogvideox", 1024, 4, 1024)
