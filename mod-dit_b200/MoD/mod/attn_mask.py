@@ -16,6 +16,7 @@ Differences that are deliberate:
     forward; the 'spargeattn' and 'svg' baselines are not part of this build and raise NotImplementedError.
 """
 import logging
+import weakref
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -98,11 +99,25 @@ def _video_blocks(warmup_state, seq_len):
 # sparse engine
 # ------------------------------------------------------------------------------------------------
 
+_VALID_KV: Dict[int, Tuple] = {}      # id(mask tensor) -> (weak reference, tensor version, valid length)
+
+
 def _valid_kv(pre_defined_mask: Optional[torch.Tensor], seq_len: int) -> int:
-    """Number of valid (unpadded) keys; reads one row of the caller's mask (one host sync, as :270,281,310)."""
+    """Number of valid (unpadded) keys; reads one row of the caller's mask (a host sync, as :270,281,310).
+    The result is remembered per mask tensor object (and its in-place version counter), so a caller that
+    passes the same padding mask to every layer and step pays the synchronisation once."""
     if pre_defined_mask is None:
         return seq_len
-    return int(pre_defined_mask[0].sum().item())
+    key = id(pre_defined_mask)
+    hit = _VALID_KV.get(key)
+    if hit is not None and hit[0]() is pre_defined_mask and hit[1] == pre_defined_mask._version:
+        return hit[2]
+    valid = int(pre_defined_mask[0].sum().item())
+    if len(_VALID_KV) >= 64:
+        _VALID_KV.clear()
+    _VALID_KV[key] = (weakref.ref(pre_defined_mask, lambda _ref, key=key: _VALID_KV.pop(key, None)),
+                      pre_defined_mask._version, valid)
+    return valid
 
 
 def _engine_lists(mask: torch.Tensor, block_size: int, seq_len: int):
