@@ -28,6 +28,54 @@ def test_pool_blocks(ops, dtype, D, bs, N):
     assert torch.allclose(got, ref, rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("dtype,D,bs,N,world", [(torch.bfloat16, 128, 128, 1344, 2), (torch.float16, 64, 64, 1472, 2),
+                                                 (torch.bfloat16, 128, 128, 2000, 4), (torch.bfloat16, 64, 128, 1032, 8)])
+def test_pool_blocks_shard_equals_pooling_the_whole_sequence(ops, dtype, D, bs, N, world):
+    """The sequence-shard form of the pooling, with all 'ranks' emulated on one GPU: every rank pools
+    halo ++ own rows and stores into the head owners' buffers; the result equals pool_blocks bit for bit
+    (shard boundaries inside blocks, a short last block, several heads per owner)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "moddit_dist_for_test", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "mod-dit_b200",
+                                             "moddit_b200", "dist.py"))
+    md = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(md)
+    torch.manual_seed(3)
+    H = 2 * world
+    hp, ns, nb = H // world, N // world, (N + bs - 1) // bs
+    x = torch.randn(1, H, N, D).to(dtype).cuda()
+    want = ops.pool_blocks(x, bs)
+    owners = [torch.full((hp, nb, D), float("nan"), device="cuda") for _ in range(world)]
+    cut = False
+    for r in range(world):
+        first, end, halo_rows, tail = md.pool_partition(N, bs, world, r)
+        cut = cut or halo_rows > 0
+        shard = x[:, :, r * ns:(r + 1) * ns].contiguous()
+        halo = torch.zeros(H, bs, D, device="cuda", dtype=dtype)
+        if halo_rows:
+            halo[:, :halo_rows] = x[0, :, r * ns - halo_rows:r * ns]
+        ops.pool_blocks_shard(shard, halo.data_ptr(), halo_rows, bs, bs, end - first, [o.data_ptr() for o in owners],
+                              hp, nb, first)
+    assert cut
+    got = torch.cat(owners, 0)[None]
+    assert torch.equal(got, want)
+    with pytest.raises(ValueError, match="pool_blocks_shard"):
+        ops.pool_blocks_shard(shard, 0, 5, bs, bs, 1, [o.data_ptr() for o in owners], hp, nb, 0)   # halo rows, no buffer
+
+
+def test_copy_rows_dma_and_kernel_agree(ops):
+    """Strided row copies: the copy-engine form and the kernel form place the same bytes."""
+    torch.manual_seed(4)
+    src = torch.randn(6, 1000, device="cuda").to(torch.bfloat16)           # pitch 2000 B
+    for fn in (ops.copy_rows_dma, ops.copy_rows):
+        dst = torch.zeros(6, 1536, device="cuda", dtype=torch.bfloat16)     # pitch 3072 B
+        fn(src.data_ptr() + 32, dst.data_ptr() + 64, 2000, 3072, 1600, 5, torch.device("cuda"))
+        torch.cuda.synchronize()
+        assert torch.equal(dst[:5, 32:832], src[:5, 16:816])
+        assert float(dst[5].abs().sum()) == 0.0 and float(dst[:, :32].abs().sum()) == 0.0
+        assert float(dst[:, 832:].abs().sum()) == 0.0
+
+
 @pytest.mark.parametrize("n,nb,qo,D", [(20, 22, 0, 128), (37, 40, 3, 64), (70, 70, 0, 128)])
 def test_pooled_map(ops, n, nb, qo, D):
     torch.manual_seed(1)
