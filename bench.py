@@ -185,7 +185,14 @@ def run_ours(args):
         try:
             resharder = mdist.PeerResharder(H, N, D, q_in.dtype, dev)
             resharder.enable_pooling(bs)
-            reshard = "peer-memory copies + fused output scatter; query/key pooled on the sequence shards"
+            reshard = "peer-memory copies (copy engines) + fused output scatter; query/key pooled on the sequence shards"
+            try:                   # one exchange up front: a box without peer DMA fails here, on every rank alike
+                resharder.seq_to_head(v_in, 2, channel=1)
+                torch.cuda.synchronize(dev)
+            except RuntimeError as exc:
+                print(f"[bench] copy-engine peer copies unavailable ({exc!r}); using the copy kernel", file=sys.stderr)
+                resharder.bulk_copy = "kernel"
+                reshard = "peer-memory copies (copy kernel) + fused output scatter; query/key pooled on the sequence shards"
         except Exception as exc:   # symmetric memory unavailable on this box: NCCL all-to-all does the same exchange
             print(f"[bench] peer-memory re-shard unavailable ({exc!r}); using NCCL all-to-all", file=sys.stderr)
             value_group = dist.new_group(backend="nccl")
