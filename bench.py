@@ -364,7 +364,7 @@ def run_ours(args):
                 "peak_source": f"of {peaks['_source']} (burst)", "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
                 "frac_of_sustained": round(achieved / float(peaks["bf16_tflops_sustained"]), 4),
                 "frac_of_nominal_2250": round(achieved / 2250.0, 4), "kernel_ms": round(attn_ms, 3),
-                "flops_per_launch": flops_local, "traffic": load_traffic(args.workload)}
+                "flops_per_launch": flops_local, "traffic": load_traffic(args.workload, (he - hb) / H)}
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
@@ -390,12 +390,14 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def load_traffic(workload):
-    """DRAM bytes per launch of the sparse forward from the committed ncu summary, or None."""
+def load_traffic(workload, head_share=1.0):
+    """DRAM bytes per launch of the sparse forward from the committed ncu summary (all heads of the workload;
+    a rank holding `head_share` of the heads moves that share: traffic follows tensor bytes), or None."""
     path = os.path.join(ROOT, "profiles", f"sparse_attn_fwd_{workload}_traffic.json")
     if os.path.exists(path):
         with open(path) as fh:
-            return json.load(fh).get("dram_bytes_per_launch")
+            total = json.load(fh).get("dram_bytes_per_launch")
+        return None if total is None else float(total) * head_share
     return None
 
 
