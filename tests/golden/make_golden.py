@@ -67,8 +67,11 @@ def locality_inputs(seed, H, T, Hh, Ww, D, gain=2.0, text=0, text_first=False):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MODDIT_REFERENCE", ""),
+                    help="path of the reference checkout (or set MODDIT_REFERENCE)")
     args = ap.parse_args()
+    if not args.reference or not os.path.isdir(os.path.join(args.reference, "MoD")):
+        ap.error("--reference must point to a MOD-DiT checkout (the directory that holds MoD/)")
     am, ls, st, tf = import_reference(args.reference)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
 
