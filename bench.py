@@ -342,6 +342,11 @@ def run_ours(args):
         barrier()
         e2e_ms = e0.elapsed_time(e1)
 
+    # ---- the processors' prologue (norm + rotary + head-major layout + block means), timed on its own ------
+    prologue = None
+    if world == 1 and not args.no_e2e:
+        prologue = time_prologue(ops, dev, H, D, N, cfg, bs)
+
     # ---- reduce over ranks ------------------------------------------------------------------------
     vals = torch.tensor([total_ms, e2e_ms, attn_ms, pred_ms, comm_ms], device=dev, dtype=torch.float64)
     sums = torch.tensor([flops_local, sparsity_local, float(launches), float(h2d), float(d2h)], device=dev,
@@ -383,11 +388,51 @@ def run_ours(args):
             "gpu_launches": int(launches_total),
             "roofline": roof,
         }
+        if prologue is not None:
+            peak_gbs = float(peaks["hbm_gbs"])
+            prologue["peak"] = peak_gbs
+            prologue["frac"] = round(prologue["achieved"] / peak_gbs, 4)
+            line["prologue"] = prologue
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.workload, args.gain, blocks=args.cpu_blocks)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def time_prologue(ops, dev, H, D, N, cfg, bs, reps=10):
+    """Times moddit_qkv_prologue at the workload's shape (RMS norm per head, rotary on the video tokens, block
+    means as a by-product) on synthetic token-major projections: not part of the timed step, reported beside
+    it as an HBM-bound kernel (algorithmic bytes = q, k, v read once and written once)."""
+    g = torch.Generator(device=dev).manual_seed(7)
+    fused = torch.randn(1, N, 3 * H * D, device=dev, dtype=torch.bfloat16, generator=g)
+    qi, ki, vi = fused.split(H * D, dim=2)
+    weights = [torch.ones(D, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    text = cfg["text_tokens"]
+    lo, hi = (text, N) if cfg["text_first"] else (0, N - text)
+    ang = torch.rand(hi - lo, D // 2, device=dev, generator=g) * 6.28
+    cos, sin = ang.cos().repeat_interleave(2, 1).contiguous(), ang.sin().repeat_interleave(2, 1).contiguous()
+    pool_bs = bs if lo % bs == 0 else 0
+    out, pools = ops.qkv_prologue(qi, ki, vi, num_heads=H, norm="rms_head", q_weight=weights[0], k_weight=weights[1],
+                                  rope_cos=cos, rope_sin=sin, rope_range=(lo, hi), pool_block_size=pool_bs)
+    def call():
+        ops.qkv_prologue(qi, ki, vi, num_heads=H, norm="rms_head", q_weight=weights[0], k_weight=weights[1],
+                         rope_cos=cos, rope_sin=sin, rope_range=(lo, hi), out=out, pool_block_size=pool_bs, pools=pools)
+    for _ in range(3):
+        call()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    e0.record()
+    for _ in range(reps):
+        call()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / reps
+    nbytes = 2 * 3 * N * H * D * 2
+    return {"kernel": "qkv_prologue_kernel", "bound": "hbm", "ms": round(ms, 4), "bytes_per_launch": nbytes,
+            "achieved": round(nbytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+            "workload": f"norm=rms_head rotary=[{lo},{hi}) block means={'yes' if pool_bs else 'no'}; inputs "
+                        f"{3 * N * H * D * 2 / 1e9:.2f} GB (larger than L2)"}
 
 
 def load_traffic(workload, head_share=1.0):

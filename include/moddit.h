@@ -251,6 +251,44 @@ int moddit_sparse_attn_fwd_scatter(const void* q, const void* k, const void* v, 
                                    void* const* peer_out, int n_peers, int head_base, float* lse,
                                    int32_t* status, void* stream);
 
+/* Attention prologue: the steps of the reference's attention processors between the q/k/v projections and the
+ * attention call, in one pass (MoD/models/hunyuan/attention_processor.py:57-106: unflatten + transpose,
+ * norm_q / norm_k, rotary embedding of the latent tokens, concatenation with the text stream;
+ * MoD/models/wan/attention_processor.py:70-93,123-125; MoD/models/cogvideox/attention_processor.py:113-135).
+ * The normalisation modules and the Hunyuan/CogVideoX rotary function come from the `diffusers` package, which
+ * the reference leaves unpinned and which is not part of its tree; their arithmetic is restated here:
+ *   MODDIT_NORM_RMS_HEAD      y = T(T(x * rsqrt(mean_D(x^2) + eps)) * w)         (RMSNorm over head_dim)
+ *   MODDIT_NORM_RMS_ALL_HEADS the same with the mean over all H*D values of the token, w of H*D values (Wan)
+ *   MODDIT_NORM_LAYER         y = T((x - mean) * rsqrt(var + eps) * w + b)       (LayerNorm over head_dim)
+ * (float32 arithmetic, T(.) = rounding to the tensors' 16-bit type; null weight/bias = 1/0), then for tokens
+ * s in [rope_lo, rope_hi), with c = rope_cos[s - rope_lo], n = rope_sin[s - rope_lo] (float32 rows of D):
+ *   MODDIT_ROPE_ELEMENTWISE        out[2i] = y[2i]*c[2i] - y[2i+1]*n[2i],   out[2i+1] = y[2i]*n[2i+1] + y[2i+1]*c[2i+1]
+ *   MODDIT_ROPE_EVEN_COS_ODD_SIN   out[2i] = y[2i]*c[2i] - y[2i+1]*n[2i+1], out[2i+1] = y[2i]*n[2i+1] + y[2i+1]*c[2i]
+ * (the second is the function defined at MoD/models/wan/attention_processor.py:78-90), products rounded
+ * separately in float32, the sum rounded once to T.  v is only moved.
+ *   q_in,k_in,v_in : (B, S, >= H*D) token-major, `token_stride` elements between tokens (a slice of a fused
+ *                    projection is fine); any of them may be null and is then skipped
+ *   q_out,k_out,v_out : (B, H, N_out, D) head-major; token s is stored at row dst_row0 + s, so a text stream
+ *                    projected separately is appended by a second call
+ *   q_pool,k_pool  : optional (B*H, ceil(N_out/block_size), D) float32 block means of the stored q / k rows
+ *                    (what moddit_pool_blocks returns for the finished tensor, bit for bit); needs dst_row0
+ *                    on a block boundary and S a multiple of block_size unless the call ends the sequence
+ *   workspace      : moddit_qkv_prologue_workspace_bytes(...) bytes, only for MODDIT_NORM_RMS_ALL_HEADS
+ */
+#define MODDIT_NORM_NONE 0
+#define MODDIT_NORM_RMS_HEAD 1
+#define MODDIT_NORM_RMS_ALL_HEADS 2
+#define MODDIT_NORM_LAYER 3
+#define MODDIT_ROPE_ELEMENTWISE 0
+#define MODDIT_ROPE_EVEN_COS_ODD_SIN 1
+size_t moddit_qkv_prologue_workspace_bytes(int B, int S, int norm_kind);
+int moddit_qkv_prologue(const void* q_in, const void* k_in, const void* v_in, int dtype, int B, int S, int H,
+                        int D, int64_t token_stride, int norm_kind, const void* q_weight, const void* q_bias,
+                        const void* k_weight, const void* k_bias, float eps, const float* rope_cos,
+                        const float* rope_sin, int rope_form, int rope_lo, int rope_hi, void* q_out, void* k_out,
+                        void* v_out, int N_out, int dst_row0, float* q_pool, float* k_pool, int block_size,
+                        void* workspace, size_t ws_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -27,6 +27,11 @@ SIGNATURES = {
     "moddit_pool_blocks": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moddit_pool_blocks_shard": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                          c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "moddit_qkv_prologue_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "moddit_qkv_prologue": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                                    c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                    c_int, c_void_p, c_size_t, c_void_p]),
     "moddit_pooled_map": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_void_p, c_void_p]),
     "moddit_replay_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -70,6 +75,8 @@ for _name, (_res, _args) in SIGNATURES.items():
     _fn.argtypes = _args
 
 MODDIT_BF16, MODDIT_FP16 = 0, 1
+NORM_KIND = {None: 0, "none": 0, "rms_head": 1, "rms_all_heads": 2, "layer": 3}
+ROPE_FORM = {"elementwise": 0, "even_cos_odd_sin": 1}
 LAYOUT = {"wan": 0, "hunyuan": 1, "cogvideox": 2}
 MODE_SPARSE, MODE_BLOCK_DIAGONAL, MODE_FULL = 0, 1, 2
 MODE_CODE = {"sparse": MODE_SPARSE, "block_diagonal": MODE_BLOCK_DIAGONAL, "full": MODE_FULL}

@@ -26,7 +26,7 @@ KERNELS_PER_CALL = {"moddit_pool_blocks": 1, "moddit_pooled_map": 1, "moddit_rep
                     "moddit_mtm": 1, "moddit_solve": 3, "moddit_select_lines": 1, "moddit_head_modes": 1,
                     "moddit_mask_from_lines": 1, "moddit_select_mass": 1, "moddit_tile_lists": 2,
                     "moddit_sparse_attn_fwd": 1, "moddit_replay_status": 0,
-                    "moddit_mts_noalloc": 2, "moddit_copy_rows_dma": 0}
+                    "moddit_mts_noalloc": 2, "moddit_copy_rows_dma": 0, "moddit_qkv_prologue": 1}
 
 
 def stage_timing(enable: bool, only=None) -> None:
@@ -135,6 +135,75 @@ def pool_blocks_shard(x: torch.Tensor, halo_ptr: int, halo_rows: int, halo_capac
                                            rows, halo_rows, halo_capacity, D, block_size, n_blocks, table, n,
                                            heads_per_peer, total_blocks, block_base, _stream(dev)),
               "moddit_pool_blocks_shard")
+
+
+def qkv_prologue(q_in: Optional[torch.Tensor], k_in: Optional[torch.Tensor], v_in: Optional[torch.Tensor], *,
+                 num_heads: int, norm: Optional[str] = None, q_weight: Optional[torch.Tensor] = None,
+                 q_bias: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None,
+                 k_bias: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                 rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None,
+                 rope_form: str = "elementwise", rope_range: Optional[Tuple[int, int]] = None,
+                 out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None, dst_row0: int = 0,
+                 total_tokens: Optional[int] = None, pool_block_size: int = 0,
+                 pools: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+    """Normalisation of q and k, rotary embedding and the token-major -> head-major move in one pass
+    (`moddit_qkv_prologue`; the reference does these as separate tensor operations in its processors,
+    MoD/models/hunyuan/attention_processor.py:57-106).
+
+    q_in/k_in/v_in: (B, S, H*D) projections (the last dimension contiguous; a slice of a fused projection is
+    accepted), any may be None.  norm: None | "rms_head" | "rms_all_heads" | "layer".  rope_cos/rope_sin:
+    (rows, D) float32 for the tokens of rope_range (default: all).  `out`: (q, k, v) buffers (B, H, N_out, D)
+    to fill from row `dst_row0` on (allocated with N_out = total_tokens or S when None).  With
+    pool_block_size > 0 the block means of the stored q and k are produced as well (`pools` to fill, else
+    allocated).  Returns ((q, k, v), (q_pool, k_pool) or None).
+    """
+    given = [t for t in (q_in, k_in, v_in) if t is not None]
+    if not given:
+        raise ValueError("qkv_prologue: no input")
+    dev = _need_cuda(*given)
+    ref = given[0]
+    B, S, W = ref.shape
+    if W % num_heads:
+        raise ValueError(f"inner dimension {W} is not divisible by {num_heads} heads")
+    D = W // num_heads
+    stride = ref.stride(1)
+    for t in given:
+        if t.shape != ref.shape or t.dtype != ref.dtype:
+            raise ValueError("q_in, k_in and v_in must have one shape and dtype")
+        if t.stride(2) != 1 or t.stride(1) != stride or t.stride(0) != S * stride:
+            raise ValueError("inputs must be (B, S, H*D) with a contiguous last dimension and one token stride")
+    dt = _qkv_dtype(ref)
+    for name, p in (("q_weight", q_weight), ("q_bias", q_bias), ("k_weight", k_weight), ("k_bias", k_bias)):
+        if p is not None and (p.dtype != ref.dtype or not p.is_contiguous() or p.device != dev):
+            raise ValueError(f"{name} must be a contiguous {ref.dtype} tensor on {dev}")
+    if (rope_cos is None) != (rope_sin is None):
+        raise ValueError("rope_cos and rope_sin go together")
+    lo, hi = (0, S) if rope_range is None else rope_range
+    if rope_cos is not None:
+        for t in (rope_cos, rope_sin):
+            if t.dtype != torch.float32 or not t.is_contiguous() or t.shape != (hi - lo, D) or t.device != dev:
+                raise ValueError(f"rotary tables must be contiguous float32 ({hi - lo}, {D}) tensors on {dev}")
+    N_out = total_tokens if total_tokens is not None else (out[0].shape[2] if out is not None else S)
+    if out is None:
+        out = tuple(torch.empty(B, num_heads, N_out, D, device=dev, dtype=ref.dtype) for _ in range(3))
+    for t in out:
+        if t.shape != (B, num_heads, N_out, D) or not t.is_contiguous() or t.dtype != ref.dtype:
+            raise ValueError("output buffers must be contiguous (B, H, N_out, D) tensors of the input dtype")
+    if pool_block_size > 0 and pools is None:
+        nb = (N_out + pool_block_size - 1) // pool_block_size
+        pools = tuple(torch.empty(B, num_heads, nb, D, device=dev, dtype=torch.float32) for _ in range(2))
+    kind = _lib.NORM_KIND[norm]
+    ws_bytes = lib.moddit_qkv_prologue_workspace_bytes(B, S, kind)
+    ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8) if ws_bytes else None
+    with torch.cuda.device(dev), _timed("moddit_qkv_prologue", dev):
+        check(lib.moddit_qkv_prologue(
+            _ptr(q_in), _ptr(k_in), _ptr(v_in), dt, B, S, num_heads, D, stride, kind, _ptr(q_weight), _ptr(q_bias),
+            _ptr(k_weight), _ptr(k_bias), eps, _ptr(rope_cos), _ptr(rope_sin), _lib.ROPE_FORM[rope_form], lo, hi,
+            _ptr(out[0]), _ptr(out[1]), _ptr(out[2]), N_out, dst_row0,
+            _ptr(pools[0] if pools is not None and q_in is not None else None),
+            _ptr(pools[1] if pools is not None and k_in is not None else None), pool_block_size, _ptr(ws),
+            ws_bytes, _stream(dev)), "moddit_qkv_prologue")
+    return out, pools
 
 
 def pooled_map(qbar: torch.Tensor, kbar: torch.Tensor, *, q_block_offset: int, k_block_offset: int,
