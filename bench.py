@@ -411,13 +411,14 @@ def time_prologue(ops, dev, H, D, N, cfg, bs, reps=10):
     text = cfg["text_tokens"]
     lo, hi = (text, N) if cfg["text_first"] else (0, N - text)
     ang = torch.rand(hi - lo, D // 2, device=dev, generator=g) * 6.28
-    cos, sin = ang.cos().repeat_interleave(2, 1).contiguous(), ang.sin().repeat_interleave(2, 1).contiguous()
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()        # one value per rotated pair
     pool_bs = bs if lo % bs == 0 else 0
-    out, pools = ops.qkv_prologue(qi, ki, vi, num_heads=H, norm="rms_head", q_weight=weights[0], k_weight=weights[1],
-                                  rope_cos=cos, rope_sin=sin, rope_range=(lo, hi), pool_block_size=pool_bs)
+    kw = dict(num_heads=H, norm="rms_head", q_weight=weights[0], k_weight=weights[1], rope_cos=cos, rope_sin=sin,
+              rope_form="pair", rope_range=(lo, hi), pool_block_size=pool_bs)
+    out, pools = ops.qkv_prologue(qi, ki, vi, **kw)
+
     def call():
-        ops.qkv_prologue(qi, ki, vi, num_heads=H, norm="rms_head", q_weight=weights[0], k_weight=weights[1],
-                         rope_cos=cos, rope_sin=sin, rope_range=(lo, hi), out=out, pool_block_size=pool_bs, pools=pools)
+        ops.qkv_prologue(qi, ki, vi, out=out, pools=pools, **kw)
     for _ in range(3):
         call()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -428,7 +429,7 @@ def time_prologue(ops, dev, H, D, N, cfg, bs, reps=10):
     e1.record()
     torch.cuda.synchronize(dev)
     ms = e0.elapsed_time(e1) / reps
-    nbytes = 2 * 3 * N * H * D * 2
+    nbytes = 2 * 3 * N * H * D * 2 + 2 * (hi - lo) * (D // 2) * 4        # q, k, v in and out + the tables once
     return {"kernel": "qkv_prologue_kernel", "bound": "hbm", "ms": round(ms, 4), "bytes_per_launch": nbytes,
             "achieved": round(nbytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s",
             "workload": f"norm=rms_head rotary=[{lo},{hi}) block means={'yes' if pool_bs else 'no'}; inputs "
@@ -557,8 +558,20 @@ def main():
     ap.add_argument("--ref-blocks", type=int, default=32, help="query blocks per step of --impl reference")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--prologue-only", action="store_true",
+                    help="time only the processors' prologue kernel at the workload's shape and print its record")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.prologue_only:
+        from moddit_b200 import ops, synth
+        cfg = synth.WORKLOADS[args.workload]
+        torch.cuda.set_device(0)
+        N = cfg["grid"][0] * cfg["grid"][1] * cfg["grid"][2] + cfg["text_tokens"]
+        rec = time_prologue(ops, torch.device("cuda", 0), cfg["heads"], cfg["head_dim"], N, cfg, cfg["block_size"],
+                            reps=max(args.steps, 1))
+        peak = float(load_peaks()["hbm_gbs"])
+        rec.update(peak=peak, frac=round(rec["achieved"] / peak, 4))
+        print(json.dumps(rec), flush=True)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

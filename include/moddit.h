@@ -264,8 +264,11 @@ int moddit_sparse_attn_fwd_scatter(const void* q, const void* k, const void* v, 
  * s in [rope_lo, rope_hi), with c = rope_cos[s - rope_lo], n = rope_sin[s - rope_lo] (float32 rows of D):
  *   MODDIT_ROPE_ELEMENTWISE        out[2i] = y[2i]*c[2i] - y[2i+1]*n[2i],   out[2i+1] = y[2i]*n[2i+1] + y[2i+1]*c[2i+1]
  *   MODDIT_ROPE_EVEN_COS_ODD_SIN   out[2i] = y[2i]*c[2i] - y[2i+1]*n[2i+1], out[2i+1] = y[2i]*n[2i+1] + y[2i+1]*c[2i]
- * (the second is the function defined at MoD/models/wan/attention_processor.py:78-90), products rounded
- * separately in float32, the sum rounded once to T.  v is only moved.
+ *   MODDIT_ROPE_PAIR               tables of D/2 values per token, one (c[i], n[i]) per pair:
+ *                                  out[2i] = y[2i]*c[i] - y[2i+1]*n[i],     out[2i+1] = y[2i]*n[i] + y[2i+1]*c[i]
+ * (the second is the function defined at MoD/models/wan/attention_processor.py:78-90; the third equals both
+ * others on the tables the models use, whose entries repeat over each pair, at half the table traffic),
+ * products rounded separately in float32, the sum rounded once to T.  v is only moved.
  *   q_in,k_in,v_in : (B, S, >= H*D) token-major, `token_stride` elements between tokens (a slice of a fused
  *                    projection is fine); any of them may be null and is then skipped
  *   q_out,k_out,v_out : (B, H, N_out, D) head-major; token s is stored at row dst_row0 + s, so a text stream
@@ -281,6 +284,7 @@ int moddit_sparse_attn_fwd_scatter(const void* q, const void* k, const void* v, 
 #define MODDIT_NORM_LAYER 3
 #define MODDIT_ROPE_ELEMENTWISE 0
 #define MODDIT_ROPE_EVEN_COS_ODD_SIN 1
+#define MODDIT_ROPE_PAIR 2
 size_t moddit_qkv_prologue_workspace_bytes(int B, int S, int norm_kind);
 int moddit_qkv_prologue(const void* q_in, const void* k_in, const void* v_in, int dtype, int B, int S, int H,
                         int D, int64_t token_stride, int norm_kind, const void* q_weight, const void* q_bias,

@@ -21,17 +21,36 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// Arithmetic on a 32-bit word holding two neighbouring elements of the 16-bit type T.
 template <typename T>
-struct Cvt;
+struct Pair;
 template <>
-struct Cvt<__nv_bfloat16> {
-  static __device__ __forceinline__ float up(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
-  static __device__ __forceinline__ uint16_t down(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
+  static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {   // round to nearest even, a in the low half
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  // product of two T values rounded once to T (what a tensor product of two T tensors gives)
+  static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a),
+                                     *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
 };
 template <>
-struct Cvt<__half> {
-  static __device__ __forceinline__ float up(uint16_t b) { return __half2float(__ushort_as_half(b)); }
-  static __device__ __forceinline__ uint16_t down(float f) { return __half_as_ushort(__float2half_rn(f)); }
+struct Pair<__half> {
+  static __device__ __forceinline__ float lo(uint32_t w) { return __low2float(*reinterpret_cast<const __half2*>(&w)); }
+  static __device__ __forceinline__ float hi(uint32_t w) { return __high2float(*reinterpret_cast<const __half2*>(&w)); }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+    const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
 };
 
 template <typename T>
@@ -39,29 +58,9 @@ __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    f[2 * i] = Cvt<T>::up(static_cast<uint16_t>(w[i] & 0xffffu));
-    f[2 * i + 1] = Cvt<T>::up(static_cast<uint16_t>(w[i] >> 16));
+    f[2 * i] = Pair<T>::lo(w[i]);
+    f[2 * i + 1] = Pair<T>::hi(w[i]);
   }
-}
-
-// Rounds to T and returns the rounded values in f as well.
-template <typename T>
-__device__ __forceinline__ uint4 pack_round(float (&f)[8]) {
-  uint32_t w[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint16_t lo = Cvt<T>::down(f[2 * i]);
-    const uint16_t hi = Cvt<T>::down(f[2 * i + 1]);
-    f[2 * i] = Cvt<T>::up(lo);
-    f[2 * i + 1] = Cvt<T>::up(hi);
-    w[i] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-  }
-  return make_uint4(w[0], w[1], w[2], w[3]);
-}
-
-template <typename T>
-__device__ __forceinline__ float round_to(float f) {
-  return Cvt<T>::up(Cvt<T>::down(f));
 }
 
 // Sum over the kTpr lanes that hold one row (kTpr is 8 or 16: the lanes are an aligned group of a warp).
@@ -83,43 +82,44 @@ struct PrologueArgs {
   const float* sin;
   int64_t token_stride;   // elements between consecutive tokens of an input
   int S, H, N_out, dst_row0, bs, nb_total, blk_base;
-  int norm_kind, rope_form, rope_lo, rope_hi;
+  int rope_form, rope_lo, rope_hi;
   float eps;
 };
 
-template <typename T, int D>
-__global__ void __launch_bounds__(kThreads) qkv_prologue_kernel(const __grid_constant__ PrologueArgs a) {
+// Grid: x = head + H * tensor (q, k, v), y = token block, z = batch - the CTAs of one token block run together,
+// so the rotary table rows of the block are fetched from HBM once and shared through L2.
+template <typename T, int D, int kNorm>
+__global__ void __launch_bounds__(kThreads, 3) qkv_prologue_kernel(const __grid_constant__ PrologueArgs a) {
   constexpr int kTpr = D / 8;               // threads per row
   constexpr int kRpp = kThreads / kTpr;     // rows per pass
+  constexpr float kInvD = 1.0f / D;         // D is a power of two: the product equals the division
   __shared__ float red[kRpp][D];
 
-  const int which = blockIdx.z % 3;
-  const int b = blockIdx.z / 3;
+  const int which = blockIdx.x / a.H;
+  const int h = blockIdx.x - which * a.H;
+  const int b = blockIdx.z;
   const T* __restrict__ in = static_cast<const T*>(a.in[which]);
   if (in == nullptr) return;
   T* __restrict__ out = static_cast<T*>(a.out[which]);
-  const int blk = blockIdx.x;
-  const int h = blockIdx.y;
+  const int blk = blockIdx.y;
   const int row0 = blk * a.bs;
   const int rows = min(a.bs, a.S - row0);
   const int cg = threadIdx.x % kTpr;
   const int rg = threadIdx.x / kTpr;
-  const int norm = which < 2 ? a.norm_kind : MODDIT_NORM_NONE;
+  const bool normed = kNorm != MODDIT_NORM_NONE && which < 2;
   const bool rope_on = which < 2 && a.cos != nullptr;
   float* pool = which < 2 ? a.pool[which] : nullptr;
 
-  // weight and bias of this thread's eight columns, kept as floats
-  float wv[8], bv[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) { wv[i] = 1.f; bv[i] = 0.f; }
-  if (norm != MODDIT_NORM_NONE) {
-    const int wofs = (norm == MODDIT_NORM_RMS_ALL_HEADS ? h * D : 0) + cg * 8;
-    if (a.weight[which] != nullptr)
-      unpack<T>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.weight[which]) + wofs)), wv);
-    if (norm == MODDIT_NORM_LAYER && a.bias[which] != nullptr)
-      unpack<T>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.bias[which]) + wofs)), bv);
+  // weight (and bias) of this thread's eight columns
+  uint4 w2 = make_uint4(0, 0, 0, 0), b2 = make_uint4(0, 0, 0, 0);
+  bool has_w = false;
+  if (normed) {
+    const int wofs = (kNorm == MODDIT_NORM_RMS_ALL_HEADS ? h * D : 0) + cg * 8;
+    has_w = a.weight[which] != nullptr;
+    if (has_w) w2 = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.weight[which]) + wofs));
+    if (kNorm == MODDIT_NORM_LAYER && a.bias[which] != nullptr)
+      b2 = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.bias[which]) + wofs));
   }
-  const bool has_w = norm != MODDIT_NORM_NONE && a.weight[which] != nullptr;
 
   const T* src = in + (static_cast<int64_t>(b) * a.S + row0) * a.token_stride + h * D + cg * 8;
   T* dst = out + ((static_cast<int64_t>(b) * a.H + h) * a.N_out + a.dst_row0 + row0) * D + cg * 8;
@@ -138,64 +138,93 @@ __global__ void __launch_bounds__(kThreads) qkv_prologue_kernel(const __grid_con
       const int r = base + rg + u * kRpp;
       const bool valid = r < rows;
       const int s = row0 + r;               // token index within the input
-      float f[8];
-      unpack<T>(v[u], f);
-      if (norm == MODDIT_NORM_RMS_HEAD || norm == MODDIT_NORM_RMS_ALL_HEADS) {
-        float rs;
-        if (norm == MODDIT_NORM_RMS_HEAD) {
+      uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+      if (normed) {
+        if constexpr (kNorm == MODDIT_NORM_RMS_HEAD || kNorm == MODDIT_NORM_RMS_ALL_HEADS) {
+          float rs;
+          if constexpr (kNorm == MODDIT_NORM_RMS_HEAD) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float x0 = Pair<T>::lo(w[i]), x1 = Pair<T>::hi(w[i]);
+              ss = fmaf(x0, x0, ss);
+              ss = fmaf(x1, x1, ss);
+            }
+            rs = rsqrtf(__fadd_rn(row_sum<kTpr>(ss) * kInvD, a.eps));
+          } else {
+            rs = valid ? __ldg(a.inv_rms[which] + static_cast<int64_t>(b) * a.S + s) : 0.f;
+          }
+          // x * rsqrt in float32 rounded to T, then the product with the weight rounded to T again
+          const uint32_t wt[4] = {w2.x, w2.y, w2.z, w2.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            w[i] = Pair<T>::pack(__fmul_rn(Pair<T>::lo(w[i]), rs), __fmul_rn(Pair<T>::hi(w[i]), rs));
+            if (has_w) w[i] = Pair<T>::mul(w[i], wt[i]);
+          }
+        } else {
+          float f[8], wv[8], bv[8];
+          unpack<T>(v[u], f);
+          unpack<T>(w2, wv);
+          unpack<T>(b2, bv);
+          float sum = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sum += f[i];
+          const float mean = row_sum<kTpr>(sum) * kInvD;
           float ss = 0.f;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
-          ss = row_sum<kTpr>(ss);
-          rs = __frsqrt_rn(__fadd_rn(ss / static_cast<float>(D), a.eps));
-        } else {
-          rs = valid ? __ldg(a.inv_rms[which] + static_cast<int64_t>(b) * a.S + s) : 0.f;
+          for (int i = 0; i < 8; ++i) {
+            f[i] -= mean;
+            ss = fmaf(f[i], f[i], ss);
+          }
+          const float rstd = rsqrtf(__fadd_rn(row_sum<kTpr>(ss) * kInvD, a.eps));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float y0 = fmaf(f[2 * i] * rstd, has_w ? wv[2 * i] : 1.f, bv[2 * i]);
+            const float y1 = fmaf(f[2 * i + 1] * rstd, has_w ? wv[2 * i + 1] : 1.f, bv[2 * i + 1]);
+            w[i] = valid ? Pair<T>::pack(y0, y1) : 0u;
+          }
         }
-        // x * rsqrt in float32, rounded to T, then the product with the weight rounded to T again
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          f[i] = __fmul_rn(f[i], rs);
-          if (has_w) f[i] = __fmul_rn(round_to<T>(f[i]), wv[i]);
-          f[i] = round_to<T>(f[i]);
-        }
-      } else if (norm == MODDIT_NORM_LAYER) {
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sum += f[i];
-        const float mean = row_sum<kTpr>(sum) / static_cast<float>(D);
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float d = f[i] - mean;
-          ss = fmaf(d, d, ss);
-        }
-        const float rstd = __frsqrt_rn(__fadd_rn(row_sum<kTpr>(ss) / static_cast<float>(D), a.eps));
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = round_to<T>(fmaf((f[i] - mean) * rstd, wv[i], bv[i]));
       }
       if (rope_on && valid && s >= a.rope_lo && s < a.rope_hi) {
-        const int64_t t = (static_cast<int64_t>(s - a.rope_lo)) * D + cg * 8;
-        float c[8], sn[8];
-        *reinterpret_cast<float4*>(c) = __ldg(reinterpret_cast<const float4*>(a.cos + t));
-        *reinterpret_cast<float4*>(c + 4) = __ldg(reinterpret_cast<const float4*>(a.cos + t + 4));
-        *reinterpret_cast<float4*>(sn) = __ldg(reinterpret_cast<const float4*>(a.sin + t));
-        *reinterpret_cast<float4*>(sn + 4) = __ldg(reinterpret_cast<const float4*>(a.sin + t + 4));
+        float ce[4], co[4], se[4], so[4];
+        if (a.rope_form == MODDIT_ROPE_PAIR) {
+          const int64_t t = static_cast<int64_t>(s - a.rope_lo) * (D / 2) + cg * 4;
+          const float4 c = __ldg(reinterpret_cast<const float4*>(a.cos + t));
+          const float4 n = __ldg(reinterpret_cast<const float4*>(a.sin + t));
+          ce[0] = co[0] = c.x; ce[1] = co[1] = c.y; ce[2] = co[2] = c.z; ce[3] = co[3] = c.w;
+          se[0] = so[0] = n.x; se[1] = so[1] = n.y; se[2] = so[2] = n.z; se[3] = so[3] = n.w;
+        } else {
+          const int64_t t = static_cast<int64_t>(s - a.rope_lo) * D + cg * 8;
+          const float4 c0 = __ldg(reinterpret_cast<const float4*>(a.cos + t));
+          const float4 c1 = __ldg(reinterpret_cast<const float4*>(a.cos + t + 4));
+          const float4 n0 = __ldg(reinterpret_cast<const float4*>(a.sin + t));
+          const float4 n1 = __ldg(reinterpret_cast<const float4*>(a.sin + t + 4));
+          ce[0] = c0.x; ce[1] = c0.z; ce[2] = c1.x; ce[3] = c1.z;
+          so[0] = n0.y; so[1] = n0.w; so[2] = n1.y; so[3] = n1.w;
+          if (a.rope_form == MODDIT_ROPE_EVEN_COS_ODD_SIN) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { co[i] = ce[i]; se[i] = so[i]; }
+          } else {
+            co[0] = c0.y; co[1] = c0.w; co[2] = c1.y; co[3] = c1.w;
+            se[0] = n0.x; se[1] = n0.z; se[2] = n1.x; se[3] = n1.z;
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float x0 = f[2 * i], x1 = f[2 * i + 1];
+          const float x0 = Pair<T>::lo(w[i]), x1 = Pair<T>::hi(w[i]);
           // products rounded separately, then one add (no fused multiply-add), as a tensor expression does
-          const float ce = c[2 * i];
-          const float co = a.rope_form == MODDIT_ROPE_EVEN_COS_ODD_SIN ? c[2 * i] : c[2 * i + 1];
-          const float se = a.rope_form == MODDIT_ROPE_EVEN_COS_ODD_SIN ? sn[2 * i + 1] : sn[2 * i];
-          const float so = sn[2 * i + 1];
-          f[2 * i] = __fsub_rn(__fmul_rn(x0, ce), __fmul_rn(x1, se));
-          f[2 * i + 1] = __fadd_rn(__fmul_rn(x0, so), __fmul_rn(x1, co));
+          w[i] = Pair<T>::pack(__fsub_rn(__fmul_rn(x0, ce[i]), __fmul_rn(x1, se[i])),
+                               __fadd_rn(__fmul_rn(x0, so[i]), __fmul_rn(x1, co[i])));
         }
       }
-      const uint4 o = pack_round<T>(f);
-      if (valid) *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * D) = o;
+      if (valid) *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * D) = make_uint4(w[0], w[1], w[2], w[3]);
+      if (pool != nullptr) {                 // rows past the end hold zeros here
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += valid ? f[i] : 0.f;
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] += Pair<T>::lo(w[i]);
+          acc[2 * i + 1] += Pair<T>::hi(w[i]);
+        }
+      }
     }
   }
   if (pool == nullptr) return;
@@ -234,24 +263,36 @@ __global__ void __launch_bounds__(kThreads) token_inv_rms_kernel(const T* __rest
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if (lane == 0) out[tok] = __frsqrt_rn(__fadd_rn(ss / static_cast<float>(width), eps));
+  if (lane == 0) out[tok] = rsqrtf(__fadd_rn(ss / static_cast<float>(width), eps));
 }
 
 template <typename T>
-int launch_prologue(const PrologueArgs& a, int B, int D, bool across, int64_t token_stride, float* ws,
+int launch_prologue(const PrologueArgs& a, int B, int D, int norm_kind, int64_t token_stride, float* ws,
                     cudaStream_t st) {
-  if (across) {
+  if (norm_kind == MODDIT_NORM_RMS_ALL_HEADS) {
     const int64_t tokens = static_cast<int64_t>(B) * a.S;
     const dim3 grid(static_cast<unsigned>((tokens + kThreads / 32 - 1) / (kThreads / 32)), 2);
     token_inv_rms_kernel<T><<<grid, kThreads, 0, st>>>(static_cast<const T*>(a.in[0]), static_cast<const T*>(a.in[1]),
                                                        tokens, token_stride, a.H * D, a.eps, ws, ws + tokens);
     MODDIT_CHECK_LAUNCH("token_inv_rms_kernel");
   }
-  const dim3 grid(ceil_div(a.S, a.bs), a.H, 3 * B);
-  if (D == 64)
-    qkv_prologue_kernel<T, 64><<<grid, kThreads, 0, st>>>(a);
-  else
-    qkv_prologue_kernel<T, 128><<<grid, kThreads, 0, st>>>(a);
+  const dim3 grid(3 * a.H, ceil_div(a.S, a.bs), B);
+#define MODDIT_PROLOGUE_CASE(NORM)                                              \
+  case NORM:                                                                    \
+    if (D == 64)                                                                \
+      qkv_prologue_kernel<T, 64, NORM><<<grid, kThreads, 0, st>>>(a);           \
+    else                                                                        \
+      qkv_prologue_kernel<T, 128, NORM><<<grid, kThreads, 0, st>>>(a);          \
+    break;
+  switch (norm_kind) {
+    MODDIT_PROLOGUE_CASE(MODDIT_NORM_NONE)
+    MODDIT_PROLOGUE_CASE(MODDIT_NORM_RMS_HEAD)
+    MODDIT_PROLOGUE_CASE(MODDIT_NORM_RMS_ALL_HEADS)
+    MODDIT_PROLOGUE_CASE(MODDIT_NORM_LAYER)
+    default:
+      return fail(MODDIT_E_ARG, "unknown norm_kind %d", norm_kind);
+  }
+#undef MODDIT_PROLOGUE_CASE
   MODDIT_CHECK_LAUNCH("qkv_prologue_kernel");
   return MODDIT_OK;
 }
@@ -277,7 +318,7 @@ extern "C" int moddit_qkv_prologue(const void* q_in, const void* k_in, const voi
   MODDIT_CHECK_ARG(dtype == MODDIT_BF16 || dtype == MODDIT_FP16, "dtype must be MODDIT_BF16 or MODDIT_FP16");
   MODDIT_CHECK_ARG(D == 64 || D == 128, "head_dim %d not supported (64 or 128)", D);
   MODDIT_CHECK_ARG(B > 0 && S > 0 && H > 0, "B, S and H must be positive (got %d, %d, %d)", B, S, H);
-  MODDIT_CHECK_ARG(H <= 65535 && 3 * static_cast<int64_t>(B) <= 65535, "H and 3*B must fit a grid dimension");
+  MODDIT_CHECK_ARG(B <= 65535, "B must fit a grid dimension");
   MODDIT_CHECK_ARG(token_stride >= static_cast<int64_t>(H) * D && token_stride % 8 == 0,
                    "token_stride %lld must be a multiple of 8 elements and at least H*D",
                    static_cast<long long>(token_stride));
@@ -300,8 +341,8 @@ extern "C" int moddit_qkv_prologue(const void* q_in, const void* k_in, const voi
     MODDIT_CHECK_ARG(aligned16(rope_cos) && aligned16(rope_sin), "rotary tables must be 16-byte aligned");
     MODDIT_CHECK_ARG(0 <= rope_lo && rope_lo <= rope_hi && rope_hi <= S, "rotary range [%d, %d) outside 0..%d",
                      rope_lo, rope_hi, S);
-    MODDIT_CHECK_ARG(rope_form == MODDIT_ROPE_ELEMENTWISE || rope_form == MODDIT_ROPE_EVEN_COS_ODD_SIN,
-                     "unknown rope_form %d", rope_form);
+    MODDIT_CHECK_ARG(rope_form >= MODDIT_ROPE_ELEMENTWISE && rope_form <= MODDIT_ROPE_PAIR, "unknown rope_form %d",
+                     rope_form);
   }
   const bool pooled = q_pool != nullptr || k_pool != nullptr;
   int bs = 128;
@@ -310,6 +351,7 @@ extern "C" int moddit_qkv_prologue(const void* q_in, const void* k_in, const voi
                      "block means need block_size > 0 and dst_row0 (%d) on a block boundary", dst_row0);
     bs = block_size;
   }
+  MODDIT_CHECK_ARG(ceil_div(S, bs) <= 65535, "S / block_size must fit a grid dimension");
   float* ws = nullptr;
   if (norm_kind == MODDIT_NORM_RMS_ALL_HEADS) {
     MODDIT_CHECK_ARG(workspace != nullptr && ws_bytes >= moddit_qkv_prologue_workspace_bytes(B, S, norm_kind),
@@ -329,10 +371,9 @@ extern "C" int moddit_qkv_prologue(const void* q_in, const void* k_in, const voi
   a.token_stride = token_stride;
   a.S = S; a.H = H; a.N_out = N_out; a.dst_row0 = dst_row0; a.bs = bs;
   a.nb_total = ceil_div(N_out, bs); a.blk_base = dst_row0 / bs;
-  a.norm_kind = norm_kind; a.rope_form = rope_form; a.rope_lo = rope_lo; a.rope_hi = rope_hi;
+  a.rope_form = rope_form; a.rope_lo = rope_lo; a.rope_hi = rope_hi;
   a.eps = eps;
-  const bool across = norm_kind == MODDIT_NORM_RMS_ALL_HEADS;
   return dtype == MODDIT_BF16
-             ? launch_prologue<__nv_bfloat16>(a, B, D, across, token_stride, ws, as_stream(stream))
-             : launch_prologue<__half>(a, B, D, across, token_stride, ws, as_stream(stream));
+             ? launch_prologue<__nv_bfloat16>(a, B, D, norm_kind, token_stride, ws, as_stream(stream))
+             : launch_prologue<__half>(a, B, D, norm_kind, token_stride, ws, as_stream(stream));
 }

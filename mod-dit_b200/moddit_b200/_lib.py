@@ -76,7 +76,7 @@ for _name, (_res, _args) in SIGNATURES.items():
 
 MODDIT_BF16, MODDIT_FP16 = 0, 1
 NORM_KIND = {None: 0, "none": 0, "rms_head": 1, "rms_all_heads": 2, "layer": 3}
-ROPE_FORM = {"elementwise": 0, "even_cos_odd_sin": 1}
+ROPE_FORM = {"elementwise": 0, "even_cos_odd_sin": 1, "pair": 2}
 LAYOUT = {"wan": 0, "hunyuan": 1, "cogvideox": 2}
 MODE_SPARSE, MODE_BLOCK_DIAGONAL, MODE_FULL = 0, 1, 2
 MODE_CODE = {"sparse": MODE_SPARSE, "block_diagonal": MODE_BLOCK_DIAGONAL, "full": MODE_FULL}

@@ -152,7 +152,8 @@ def qkv_prologue(q_in: Optional[torch.Tensor], k_in: Optional[torch.Tensor], v_i
 
     q_in/k_in/v_in: (B, S, H*D) projections (the last dimension contiguous; a slice of a fused projection is
     accepted), any may be None.  norm: None | "rms_head" | "rms_all_heads" | "layer".  rope_cos/rope_sin:
-    (rows, D) float32 for the tokens of rope_range (default: all).  `out`: (q, k, v) buffers (B, H, N_out, D)
+    (rows, D) float32 for the tokens of rope_range (default: all); (rows, D/2), one value per pair, with
+    rope_form="pair".  `out`: (q, k, v) buffers (B, H, N_out, D)
     to fill from row `dst_row0` on (allocated with N_out = total_tokens or S when None).  With
     pool_block_size > 0 the block means of the stored q and k are produced as well (`pools` to fill, else
     allocated).  Returns ((q, k, v), (q_pool, k_pool) or None).
@@ -180,9 +181,10 @@ def qkv_prologue(q_in: Optional[torch.Tensor], k_in: Optional[torch.Tensor], v_i
         raise ValueError("rope_cos and rope_sin go together")
     lo, hi = (0, S) if rope_range is None else rope_range
     if rope_cos is not None:
+        width = D // 2 if rope_form == "pair" else D
         for t in (rope_cos, rope_sin):
-            if t.dtype != torch.float32 or not t.is_contiguous() or t.shape != (hi - lo, D) or t.device != dev:
-                raise ValueError(f"rotary tables must be contiguous float32 ({hi - lo}, {D}) tensors on {dev}")
+            if t.dtype != torch.float32 or not t.is_contiguous() or t.shape != (hi - lo, width) or t.device != dev:
+                raise ValueError(f"rotary tables must be contiguous float32 ({hi - lo}, {width}) tensors on {dev}")
     N_out = total_tokens if total_tokens is not None else (out[0].shape[2] if out is not None else S)
     if out is None:
         out = tuple(torch.empty(B, num_heads, N_out, D, device=dev, dtype=ref.dtype) for _ in range(3))

@@ -38,13 +38,15 @@ def _close_after_norm(got, ref, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("form", ["elementwise", "even_cos_odd_sin"])
+@pytest.mark.parametrize("form", ["elementwise", "even_cos_odd_sin", "pair"])
 @pytest.mark.parametrize("H,D,S,lo,hi", [(3, 128, 300, 0, 300), (2, 64, 197, 40, 197), (2, 128, 130, 0, 100)])
 def test_rotary_and_layout_are_bit_exact(ops, dtype, form, H, D, S, lo, hi):
     q, k, v = _proj(2, S, H * D, dtype, 1)
     cos, sin = _tables(hi - lo, D, 2)
     if form == "elementwise":     # tables whose even and odd entries differ tell the two forms apart
         cos, sin = cos * torch.linspace(0.9, 1.1, D), sin * torch.linspace(1.1, 0.9, D)
+    if form == "pair":
+        cos, sin = cos[:, 0::2].contiguous(), sin[:, 0::2].contiguous()
     ref = orc.qkv_prologue(q, k, v, num_heads=H, rope_cos=cos, rope_sin=sin, rope_form=form, rope_range=(lo, hi))
     (gq, gk, gv), pools = ops.qkv_prologue(q.cuda(), k.cuda(), v.cuda(), num_heads=H, rope_cos=cos.cuda(),
                                            rope_sin=sin.cuda(), rope_form=form, rope_range=(lo, hi))
@@ -151,3 +153,31 @@ def test_rejects_bad_arguments(ops):
         ops.qkv_prologue(q, k, v, num_heads=8)
     with pytest.raises(ValueError):
         ops.qkv_prologue(q.cpu(), k.cpu(), v.cpu(), num_heads=2)
+
+
+def test_prologue_feeds_the_state_machine(ops):
+    """Projections -> prologue -> SparseAttentionWithMap with the prologue's block means handed over as
+    `pooled_qk`: mask and output equal the ones of a call that pools the stored tensors itself."""
+    import logging
+
+    import MoD.mod.attn_mask as am
+    from MoD.mod.state import create_adaptive_mask_state
+    from moddit_b200 import synth
+
+    H, grid, D, bs, text = 2, (4, 16, 16), 128, 128, 128
+    q, k, v = synth.make_qkv(heads=H, grid=grid, head_dim=D, text_tokens=text, seed=5, device=torch.device("cuda"))
+    video = grid[0] * grid[1] * grid[2]
+    proj = [t[0].transpose(0, 1).reshape(1, video + text, H * D).contiguous() for t in (q, k, v)]   # token-major
+    (pq, pk, pv), pools = ops.qkv_prologue(*proj, num_heads=H, pool_block_size=bs)
+    assert torch.equal(pq, q) and torch.equal(pk, k) and torch.equal(pv, v)
+    log = logging.getLogger("prologue-test")
+    results = []
+    for pooled in (None, pools):
+        state = create_adaptive_mask_state("hunyuan", H, video, text, grid[1] * grid[2], grid[0], warmup_steps=2,
+                                           top_k=6, predict_T=5, block_size=bs)
+        state["score_producer"] = "pooled"
+        for step in range(3):
+            kw = {} if pooled is None else {"pooled_qk": pooled}
+            out, _ = am.SparseAttentionWithMap(pq, pk, pv, state, log, current_step=step, **kw)
+        results.append((state["mask"].clone(), out.clone()))
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
