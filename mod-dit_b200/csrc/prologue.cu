@@ -82,6 +82,7 @@ struct PrologueArgs {
   const float* sin;
   int64_t token_stride;   // elements between consecutive tokens of an input
   int S, H, N_out, dst_row0, bs, nb_total, blk_base;
+  int group;              // token blocks per CTA (a CTA always has eight rows per thread to load)
   int rope_form, rope_lo, rope_hi;
   float eps;
 };
@@ -101,9 +102,10 @@ __global__ void __launch_bounds__(kThreads, 3) qkv_prologue_kernel(const __grid_
   const T* __restrict__ in = static_cast<const T*>(a.in[which]);
   if (in == nullptr) return;
   T* __restrict__ out = static_cast<T*>(a.out[which]);
-  const int blk = blockIdx.y;
-  const int row0 = blk * a.bs;
-  const int rows = min(a.bs, a.S - row0);
+  const int blk0 = blockIdx.y * a.group;    // first token block of this CTA
+  const int row0 = blk0 * a.bs;
+  const int rows = min(a.group * a.bs, a.S - row0);
+  const int spb = a.group > 1 ? a.bs / kRpp : 0;   // load slots per block when the CTA holds several blocks
   const int cg = threadIdx.x % kTpr;
   const int rg = threadIdx.x / kTpr;
   const bool normed = kNorm != MODDIT_NORM_NONE && which < 2;
@@ -125,6 +127,20 @@ __global__ void __launch_bounds__(kThreads, 3) qkv_prologue_kernel(const __grid_
   T* dst = out + ((static_cast<int64_t>(b) * a.H + h) * a.N_out + a.dst_row0 + row0) * D + cg * 8;
 
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  // Mean of block blk0 + j from the threads' partial sums, in the order pool_blocks_kernel adds them.
+  auto flush = [&](int j, int block_rows) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[rg][cg * 8 + i] = acc[i];
+    __syncthreads();
+    if (threadIdx.x < D) {
+      float t = 0.f;
+#pragma unroll 8
+      for (int g = 0; g < kRpp; ++g) t += red[g][threadIdx.x];
+      pool[((static_cast<int64_t>(b) * a.H + h) * a.nb_total + a.blk_base + blk0 + j) * D + threadIdx.x] =
+          t / static_cast<float>(block_rows);
+    }
+    __syncthreads();
+  };
   for (int base = 0; base < rows; base += 8 * kRpp) {   // uniform trip count: the shuffles below need every lane
     uint4 v[8];
 #pragma unroll
@@ -132,6 +148,20 @@ __global__ void __launch_bounds__(kThreads, 3) qkv_prologue_kernel(const __grid_
       const int r = base + rg + u * kRpp;
       v[u] = r < rows ? __ldg(reinterpret_cast<const uint4*>(src + static_cast<int64_t>(r) * a.token_stride))
                       : make_uint4(0, 0, 0, 0);
+    }
+    if (rope_on) {
+      // the table rows are needed one after the other below: ask for all of them now
+      const int tw = a.rope_form == MODDIT_ROPE_PAIR ? D / 2 : D;
+      const int tc = a.rope_form == MODDIT_ROPE_PAIR ? cg * 4 : cg * 8;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int s = row0 + base + rg + u * kRpp;
+        if (s - row0 < rows && s >= a.rope_lo && s < a.rope_hi) {
+          const int64_t t = static_cast<int64_t>(s - a.rope_lo) * tw + tc;
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(a.cos + t));
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(a.sin + t));
+        }
+      }
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -224,20 +254,16 @@ __global__ void __launch_bounds__(kThreads, 3) qkv_prologue_kernel(const __grid_
           acc[2 * i] += Pair<T>::lo(w[i]);
           acc[2 * i + 1] += Pair<T>::hi(w[i]);
         }
+        if (spb > 0 && (u + 1) % spb == 0) {  // last slot of a block (the same for every thread)
+          const int j = u / spb;
+          if (j * a.bs < rows) flush(j, min(a.bs, rows - j * a.bs));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        }
       }
     }
   }
-  if (pool == nullptr) return;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) red[rg][cg * 8 + i] = acc[i];
-  __syncthreads();
-  if (threadIdx.x < D) {
-    float s = 0.f;
-#pragma unroll 8
-    for (int g = 0; g < kRpp; ++g) s += red[g][threadIdx.x];
-    pool[((static_cast<int64_t>(b) * a.H + h) * a.nb_total + a.blk_base + blk) * D + threadIdx.x] =
-        s / static_cast<float>(rows);
-  }
+  if (pool != nullptr && spb == 0) flush(0, rows);
 }
 
 // One warp per token: 1/sqrt(mean of squares over the whole H*D row + eps) for the normalisation that spans
@@ -276,7 +302,7 @@ int launch_prologue(const PrologueArgs& a, int B, int D, int norm_kind, int64_t 
                                                        tokens, token_stride, a.H * D, a.eps, ws, ws + tokens);
     MODDIT_CHECK_LAUNCH("token_inv_rms_kernel");
   }
-  const dim3 grid(3 * a.H, ceil_div(a.S, a.bs), B);
+  const dim3 grid(3 * a.H, ceil_div(a.S, a.bs * a.group), B);
 #define MODDIT_PROLOGUE_CASE(NORM)                                              \
   case NORM:                                                                    \
     if (D == 64)                                                                \
@@ -371,6 +397,8 @@ extern "C" int moddit_qkv_prologue(const void* q_in, const void* k_in, const voi
   a.token_stride = token_stride;
   a.S = S; a.H = H; a.N_out = N_out; a.dst_row0 = dst_row0; a.bs = bs;
   a.nb_total = ceil_div(N_out, bs); a.blk_base = dst_row0 / bs;
+  const int rows_per_pass = kThreads / (D / 8);      // short blocks: several per CTA, eight rows per thread
+  a.group = (bs % rows_per_pass == 0 && (8 * rows_per_pass) % bs == 0) ? 8 * rows_per_pass / bs : 1;
   a.rope_form = rope_form; a.rope_lo = rope_lo; a.rope_hi = rope_hi;
   a.eps = eps;
   return dtype == MODDIT_BF16
