@@ -190,6 +190,23 @@ int moddit_radial_mask(int layout, int video_tokens, int num_frames, int seq_len
 /* Cumulative-mass selection on a darkness map (no reference function).  keep: (H,n,n) bool bytes. */
 int moddit_select_mass(const void* map_f16, int H, int n, float tau, uint8_t* keep, void* stream);
 
+/* The two stages of the `--sparse_type spargeattn` comparison mode that the reference delegates to the
+ * third-party call `spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=0.5, is_causal=False)`
+ * (MoD/mod/attn_mask.py:611-614; the package is an unpinned git submodule whose sources are not in the
+ * reference tree, so this follows the method's published description: blocks are represented by their mean,
+ * each query block keeps the `topk` share of key blocks with the largest pooled score, and blocks whose rows
+ * are not similar to one another are not trusted to their mean).
+ * moddit_block_similarity: sim[bh, i] = mean cosine similarity over all pairs of rows of block i of x (BH, N, D),
+ *   after subtracting center[bh, :] (float32, may be null) from every row; out (BH, ceil(N/block_size)) float32.
+ * moddit_select_topk_blocks: per (head, query block) the `count` key blocks with the smallest map value
+ *   (map as moddit_pooled_map writes it: 0 = brightest; ties to the lowest index); row_full (H, n) bool bytes
+ *   keeps whole rows, col_keep (H, n) keeps columns in every row (either may be null).  keep: (H, n, n) bool bytes.
+ */
+int moddit_block_similarity(const void* x, int dtype, int BH, int N, int D, int block_size, const float* center,
+                            float* out, void* stream);
+int moddit_select_topk_blocks(const void* map_f16, int H, int n, int count, const uint8_t* row_full,
+                              const uint8_t* col_keep, uint8_t* keep, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Work lists for the sparse forward: for each (mask head, pair of 128-row query tiles) the key tiles
  * that either tile needs, ascending, each as (key_tile << 8) | (flagsB << 4) | flagsA where flag bit

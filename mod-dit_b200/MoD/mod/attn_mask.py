@@ -13,9 +13,12 @@ Differences that are deliberate:
   * two optional state keys, `score_producer='pooled'` and `selector='cumulative_mass'`, enable the
     mean-pooled map producer and the cumulative-mass selector; their defaults keep reference behaviour;
   * `sparse_type='radial'` runs its static mask (MoD/mod/get_radial_mask.py) through the same sparse
-    forward; the 'spargeattn' and 'svg' baselines are not part of this build and raise NotImplementedError.
+    forward; `sparse_type='spargeattn'` runs the published mean-pooling / top-k method on this library's
+    kernels (the third-party package the reference calls is not part of its tree); the 'svg' baseline is not
+    part of this build and raises NotImplementedError.
 """
 import logging
+import math
 import weakref
 from typing import Dict, List, Optional, Tuple
 
@@ -317,8 +320,10 @@ def SparseAttentionWithMap(
         output, _ = dense_attention_with_lse(query, key, value, kv_len=valid)
         return output, {'mode': 'warmup', 'mask': None}
     sparse_type = warmup_state['sparse_type']
-    if sparse_type in ('spargeattn', 'svg'):
+    if sparse_type == 'svg':
         raise NotImplementedError(f"sparse_type '{sparse_type}' is a third-party baseline that this build does not include")
+    if sparse_type == 'spargeattn':
+        return _spargeattn_step(query, key, value, warmup_state)
     if sparse_type == 'radial':
         return _radial_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx)
 
@@ -408,6 +413,42 @@ def _radial_step(query, key, value, warmup_state, logger, pre_defined_mask, curr
                                    video_token_num=warmup_state.get('video_token_num', 0), block_size=bs,
                                    _lists=_lists_for(warmup_state, seq_len))
     return output, {'mask': warmup_state['mask']}
+
+
+def _spargeattn_step(query, key, value, warmup_state):
+    """`sparse_type='spargeattn'` (:611-614): the reference hands the whole call to the third-party
+    `spas_sage2_attn_meansim_topk_cuda(query, key, value, topk=0.5, is_causal=False)`.  That package is not part
+    of the reference tree (an unpinned submodule), so this follows the published method with this library's
+    kernels, on every step, over the whole sequence: blocks of query and key are represented by their means,
+    every query block keeps the `topk` share (state key `spargeattn_topk`, default 0.5) of key blocks with
+    the largest pooled score, and the block-sparse forward runs under that mask.  Blocks whose rows are not
+    similar to one another (mean pairwise cosine similarity below state key `spargeattn_sim_threshold`; key
+    rows relative to the mean key of the head) are not trusted to their mean: such a query block keeps every
+    key block, such a key block is kept by every query block.  The default threshold 0 switches that test off.
+    Not taken over: the package's 8-bit quantisation of the products, its 128 x 64 block shape (the mask has
+    the state's square block_size) and its skipping of small value products inside the kernel."""
+    bs = warmup_state['block_size']
+    seq_len = query.size(2)
+    query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
+    nb = (seq_len + bs - 1) // bs
+    qbar, kbar = _ops.pool_blocks(query, bs), _ops.pool_blocks(key, bs)
+    dark = _ops.pooled_map(qbar, kbar, q_block_offset=0, k_block_offset=0, video_blocks=nb,
+                           scale=float(query.shape[-1]) ** -0.5).squeeze(0)
+    threshold = float(warmup_state.get('spargeattn_sim_threshold', 0.0))
+    row_full = col_keep = None
+    if threshold > 0.0:
+        rows = torch.full((nb,), float(bs), device=query.device)
+        rows[-1] = float(seq_len - (nb - 1) * bs)
+        centre = ((kbar * rows[None, None, :, None]).sum(dim=2) / float(seq_len)).contiguous()   # mean key per head
+        row_full = (_ops.block_similarity(query, bs) < threshold).squeeze(0)
+        col_keep = (_ops.block_similarity(key, bs, centre) < threshold).squeeze(0)
+    count = max(1, min(nb, int(math.ceil(float(warmup_state.get('spargeattn_topk', 0.5)) * nb))))
+    mask = _ops.select_topk_blocks(dark, count, row_full, col_keep)
+    warmup_state['mask'] = mask
+    lists = _ops.tile_lists(mask, bs, seq_len)
+    output = _ops.sparse_attn_fwd(query, key, value, lists.counts, lists.entries, order=lists.order,
+                                  check_status=False)
+    return output, {'mode': 'warmup', 'mask': None}
 
 
 def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx,

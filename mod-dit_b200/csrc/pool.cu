@@ -125,6 +125,80 @@ __global__ void __launch_bounds__(kPoolThreads) pool_blocks_kernel(const T* __re
   }
 }
 
+// Self-similarity of a block of rows: the mean cosine similarity over all pairs of its rows (a row paired with
+// itself included), which equals |sum of the rows scaled to unit length|^2 / rows^2.  `center` (one vector of D
+// floats per head, may be null) is subtracted from every row first.  One CTA per (block, head), rows laid over
+// the threads as in pool_blocks_kernel; sums in a fixed order.  A block of nearly parallel rows gives ~1, rows
+// pointing anywhere give ~1/rows.  Traffic: N*D*2 bytes read per head.
+template <typename T, int D>
+__global__ void __launch_bounds__(kPoolThreads) block_similarity_kernel(const T* __restrict__ x, int N, int bs,
+                                                                        const float* __restrict__ center,
+                                                                        float* __restrict__ out) {
+  constexpr int kTpr = D / 8;
+  constexpr int kRpp = kPoolThreads / kTpr;
+  __shared__ float red[kRpp][D];
+  __shared__ float part[D / 32];
+
+  const int blk = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int row0 = blk * bs;
+  const int rows = min(bs, N - row0);
+  const int cg = threadIdx.x % kTpr;
+  const int rg = threadIdx.x / kTpr;
+  const uint4* base = reinterpret_cast<const uint4*>(x + (static_cast<int64_t>(bh) * N + row0) * D) + cg;
+  float c[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (center != nullptr) {
+    const float4* cp = reinterpret_cast<const float4*>(center + static_cast<int64_t>(bh) * D + cg * 8);
+    const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1);
+    c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+  }
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int b0 = 0; b0 < rows; b0 += 8 * kRpp) {       // uniform trip count: the shuffles need every lane
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int r = b0 + rg + u * kRpp;
+      v[u] = r < rows ? __ldg(base + static_cast<int64_t>(r) * kTpr) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const bool valid = b0 + rg + u * kRpp < rows;
+      float f[8];
+      unpack8<T>(v[u], f);
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        f[i] -= c[i];
+        ss = fmaf(f[i], f[i], ss);
+      }
+#pragma unroll
+      for (int o = kTpr / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float inv = (valid && ss > 0.f) ? rsqrtf(ss) : 0.f;     // a zero row contributes nothing
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaf(f[i], inv, acc[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[rg][cg * 8 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int g = 0; g < kRpp; ++g) s += red[g][threadIdx.x];
+    s *= s;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (threadIdx.x % 32 == 0) part[threadIdx.x / 32] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < D / 32; ++w) s += part[w];
+    out[static_cast<int64_t>(bh) * gridDim.x + blk] = s / (static_cast<float>(rows) * static_cast<float>(rows));
+  }
+}
+
 template <bool kShard>
 void launch_pool(const void* x, int dtype, int D, int N, int bs, float* out, const PoolShard& shard, dim3 grid,
                  cudaStream_t st) {
@@ -257,6 +331,40 @@ extern "C" int moddit_pool_blocks(const void* x, int dtype, int BH, int N, int D
   const PoolShard none = {};
   launch_pool<false>(x, dtype, D, N, block_size, out, none, grid, as_stream(stream));
   MODDIT_CHECK_LAUNCH("pool_blocks_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_block_similarity(const void* x, int dtype, int BH, int N, int D, int block_size,
+                                       const float* center, float* out, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(x && out, "block_similarity: null pointer");
+  MODDIT_CHECK_ARG(BH > 0 && N > 0, "block_similarity: BH=%d N=%d must be positive", BH, N);
+  if (D != 64 && D != 128) return fail(MODDIT_E_UNSUPPORTED, "block_similarity: head_dim must be 64 or 128, got %d", D);
+  if (block_size != 64 && block_size != 128)
+    return fail(MODDIT_E_UNSUPPORTED, "block_similarity: block_size must be 64 or 128, got %d", block_size);
+  if (dtype != MODDIT_BF16 && dtype != MODDIT_FP16) return fail(MODDIT_E_ARG, "block_similarity: unknown dtype %d", dtype);
+  if (!aligned16(x) || !aligned16(center))
+    return fail(MODDIT_E_ALIGN, "block_similarity: input and center must be 16-byte aligned");
+  if (BH > 65535) return fail(MODDIT_E_UNSUPPORTED, "block_similarity: BH=%d exceeds 65535", BH);
+  if (int rc = require_sm100()) return rc;
+  const dim3 grid(ceil_div(N, block_size), BH);
+  cudaStream_t st = as_stream(stream);
+  if (dtype == MODDIT_BF16) {
+    if (D == 64)
+      block_similarity_kernel<__nv_bfloat16, 64><<<grid, kPoolThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), N,
+                                                                              block_size, center, out);
+    else
+      block_similarity_kernel<__nv_bfloat16, 128><<<grid, kPoolThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), N,
+                                                                               block_size, center, out);
+  } else {
+    if (D == 64)
+      block_similarity_kernel<__half, 64><<<grid, kPoolThreads, 0, st>>>(static_cast<const __half*>(x), N, block_size,
+                                                                       center, out);
+    else
+      block_similarity_kernel<__half, 128><<<grid, kPoolThreads, 0, st>>>(static_cast<const __half*>(x), N, block_size,
+                                                                        center, out);
+  }
+  MODDIT_CHECK_LAUNCH("block_similarity_kernel");
   return MODDIT_OK;
 }
 

@@ -106,8 +106,13 @@ constexpr int kMassThreads = 512;
 
 // One CTA per (query block, head).  Keys ((2^24 - w) << 32 | j) are bitonic-sorted ascending, i.e.
 // by brightness descending then index ascending; integer prefix sums decide the kept prefix.
+// With topk_count > 0 the kept prefix is the first topk_count blocks of that order instead (no forced diagonal);
+// row_full[h,i] != 0 keeps the whole row i, col_keep[h,j] != 0 keeps column j in every row (either may be null).
 __global__ void __launch_bounds__(kMassThreads) select_mass_kernel(const __half* __restrict__ map, int n, int P,
-                                                                   uint32_t tau_fixed, uint8_t* __restrict__ keep) {
+                                                                   uint32_t tau_fixed, int topk_count,
+                                                                   const uint8_t* __restrict__ row_full,
+                                                                   const uint8_t* __restrict__ col_keep,
+                                                                   uint8_t* __restrict__ keep) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned long long* key = reinterpret_cast<unsigned long long*>(smem_raw);   // [P]
   unsigned long long* pre = key + P;                                           // [P] inclusive prefix of w
@@ -174,7 +179,10 @@ __global__ void __launch_bounds__(kMassThreads) select_mass_kernel(const __half*
     if (kk == ~0ull) continue;
     const int j = static_cast<int>(static_cast<uint32_t>(kk));
     const unsigned long long excl = (e == 0) ? 0ull : pre[e - 1];
-    dst[j] = (excl < target || j == i) ? 1 : 0;
+    bool k = topk_count > 0 ? e < topk_count : (excl < target || j == i);
+    if (row_full != nullptr && row_full[static_cast<int64_t>(h) * n + i] != 0) k = true;
+    if (col_keep != nullptr && col_keep[static_cast<int64_t>(h) * n + j] != 0) k = true;
+    dst[j] = k ? 1 : 0;
   }
 }
 
@@ -381,7 +389,23 @@ extern "C" int moddit_select_mass(const void* map_f16, int H, int n, float tau, 
   while (P < n) P <<= 1;
   const uint32_t tau_fixed = static_cast<uint32_t>(floorf(tau * 16777216.0f));
   select_mass_kernel<<<dim3(n, H), kMassThreads, 2 * sizeof(unsigned long long) * P, as_stream(stream)>>>(
-      static_cast<const __half*>(map_f16), n, P, tau_fixed, keep);
+      static_cast<const __half*>(map_f16), n, P, tau_fixed, 0, nullptr, nullptr, keep);
+  MODDIT_CHECK_LAUNCH("select_mass_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_select_topk_blocks(const void* map_f16, int H, int n, int count, const uint8_t* row_full,
+                                         const uint8_t* col_keep, uint8_t* keep, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(map_f16 && keep, "select_topk_blocks: null pointer");
+  MODDIT_CHECK_ARG(H > 0 && H <= 65535 && n > 0, "select_topk_blocks: bad sizes");
+  MODDIT_CHECK_ARG(count > 0 && count <= n, "select_topk_blocks: count=%d outside 1..%d", count, n);
+  if (n > 2048) return fail(MODDIT_E_UNSUPPORTED, "select_topk_blocks: n=%d exceeds 2048", n);
+  if (int rc = require_sm100()) return rc;
+  int P = 2;
+  while (P < n) P <<= 1;
+  select_mass_kernel<<<dim3(n, H), kMassThreads, 2 * sizeof(unsigned long long) * P, as_stream(stream)>>>(
+      static_cast<const __half*>(map_f16), n, P, 0u, count, row_full, col_keep, keep);
   MODDIT_CHECK_LAUNCH("select_mass_kernel");
   return MODDIT_OK;
 }

@@ -56,6 +56,8 @@ SIGNATURES = {
     "moddit_mask_from_lines": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_void_p, c_void_p]),
     "moddit_select_mass": (c_int, [c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),
+    "moddit_block_similarity": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "moddit_select_topk_blocks": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "moddit_tile_lists": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                   c_void_p, c_void_p]),
     "moddit_copy_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),

@@ -444,6 +444,43 @@ def select_mass(dark_map: torch.Tensor, tau: float) -> torch.Tensor:
     return keep
 
 
+def block_similarity(x: torch.Tensor, block_size: int, center: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(B,H,N,D) bf16/fp16 -> (B,H,ceil(N/bs)) float32: mean pairwise cosine similarity of the rows of every
+    block, after subtracting `center` ((B,H,D) float32) from the rows when given."""
+    dev = _need_cuda(x)
+    _need_contig(x=x)
+    B, H, N, D = x.shape
+    if center is not None:
+        if center.shape != (B, H, D) or center.dtype != torch.float32 or not center.is_contiguous():
+            raise ValueError("center must be a contiguous (B, H, D) float32 tensor")
+    out = torch.empty(B, H, (N + block_size - 1) // block_size, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev), _timed("moddit_block_similarity", dev):
+        check(lib.moddit_block_similarity(_ptr(x), _qkv_dtype(x), B * H, N, D, block_size, _ptr(center), _ptr(out),
+                                          _stream(dev)), "moddit_block_similarity")
+    return out
+
+
+def select_topk_blocks(dark_map: torch.Tensor, count: int, row_full: Optional[torch.Tensor] = None,
+                       col_keep: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(H,n,n) float16 map (0 = brightest) -> (H,n,n) bool: per row the `count` brightest blocks, plus whole
+    rows where row_full (H,n) and whole columns where col_keep (H,n) are set."""
+    dev = _need_cuda(dark_map)
+    dark_map = dark_map.to(torch.float16).contiguous()
+    H, n, _ = dark_map.shape
+    flags = []
+    for f in (row_full, col_keep):
+        if f is not None:
+            if f.shape != (H, n) or f.device != dev:
+                raise ValueError("row_full / col_keep must be (H, n) tensors on the map's device")
+            f = f.to(torch.bool).contiguous()
+        flags.append(f)
+    keep = torch.empty(H, n, n, device=dev, dtype=torch.bool)
+    with torch.cuda.device(dev), _timed("moddit_select_topk_blocks", dev):
+        check(lib.moddit_select_topk_blocks(_ptr(dark_map), H, n, int(count), _ptr(flags[0]), _ptr(flags[1]), _ptr(keep),
+                                            _stream(dev)), "moddit_select_topk_blocks")
+    return keep
+
+
 class TileLists(tuple):
     """(counts, entries, order) produced by `tile_lists`; unpacks like the 2-tuple (counts, entries)."""
 
