@@ -7,6 +7,7 @@ there is no alternative implementation: CPU tensors are rejected.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Dict, Optional, Tuple
 
@@ -20,7 +21,8 @@ _DTYPE = {torch.bfloat16: _lib.MODDIT_BF16, torch.float16: _lib.MODDIT_FP16}
 # ---------------------------------------------------------------------------------------------
 # optional per-entry-point timing (CUDA events on the launching stream); off by default
 # ---------------------------------------------------------------------------------------------
-_TIMING = {"on": False, "only": None, "records": [], "launches": 0}
+_TIMING = {"on": False, "only": None, "records": [], "launches": 0,
+           "nvtx": os.environ.get("MODDIT_NVTX", "0") not in ("", "0")}
 # kernels launched by one call of each entry point (for launch accounting in benchmarks)
 KERNELS_PER_CALL = {"moddit_pool_blocks": 1, "moddit_pooled_map": 1, "moddit_replay_map": 1, "moddit_mts": 2,
                     "moddit_mtm": 1, "moddit_solve": 3, "moddit_select_lines": 1, "moddit_head_modes": 1,
@@ -36,6 +38,12 @@ def stage_timing(enable: bool, only=None) -> None:
     _TIMING["only"] = None if only is None else frozenset(only)
     _TIMING["records"] = []
     _TIMING["launches"] = 0
+
+
+def nvtx_ranges(enable: bool) -> None:
+    """Wrap every entry-point call in an NVTX range named after it (also switched on by MODDIT_NVTX=1), so a
+    timeline shows which launches belong to which stage."""
+    _TIMING["nvtx"] = bool(enable)
 
 
 def stage_records():
@@ -56,12 +64,16 @@ class _timed:
 
     def __enter__(self):
         self.start = None
+        if _TIMING["nvtx"]:
+            torch.cuda.nvtx.range_push(self.name)
         if _TIMING["on"] and (_TIMING["only"] is None or self.name in _TIMING["only"]):
             self.start = torch.cuda.Event(enable_timing=True)
             self.start.record(torch.cuda.current_stream(self.dev))
         return self
 
     def __exit__(self, *exc):
+        if _TIMING["nvtx"]:
+            torch.cuda.nvtx.range_pop()
         if _TIMING["on"]:
             if self.start is not None:
                 end = torch.cuda.Event(enable_timing=True)
@@ -488,6 +500,9 @@ class TileLists(tuple):
         obj = super().__new__(cls, (counts, entries))
         obj.counts, obj.entries, obj.order = counts, entries, order
         return obj
+
+    def __getnewargs__(self):          # lets a state dict that holds work lists be pickled / torch.save'd
+        return self.counts, self.entries, self.order
 
 
 def tile_lists(mask: torch.Tensor, block_size: int, n_tokens: int, kv_block_limit: Optional[int] = None

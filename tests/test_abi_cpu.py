@@ -50,3 +50,23 @@ def test_ops_reject_cpu_tensors():
         ops.pool_blocks(x, 64)
     with pytest.raises(ValueError, match="CUDA"):
         ops.sparse_attn_fwd(x, x, x, torch.zeros(1, 1, dtype=torch.int32), torch.zeros(1, 1, 1, dtype=torch.int32))
+
+
+def test_work_lists_survive_pickling_with_the_state_dict():
+    """A state dict holds its mask and the work lists built from it; saving and loading it keeps the pairing
+    (the cached lists are recognised by the identity of the mask tensor)."""
+    import io
+
+    from moddit_b200.ops import TileLists
+    mask = torch.ones(2, 3, 3, dtype=torch.bool)
+    lists = TileLists(torch.zeros(2, 1, dtype=torch.int32), torch.ones(2, 1, 3, dtype=torch.int32),
+                      torch.arange(2, dtype=torch.int32).view(2, 1))
+    state = {"mask": mask, "_tile_lists": (mask, lists), "mode": ["sparse", "full"], "features_history": []}
+    buf = io.BytesIO()
+    torch.save(state, buf)
+    buf.seek(0)
+    back = torch.load(buf, weights_only=False)
+    assert isinstance(back["_tile_lists"][1], TileLists) and back["_tile_lists"][0] is back["mask"]
+    counts, entries = back["_tile_lists"][1]
+    assert torch.equal(counts, lists.counts) and torch.equal(entries, lists.entries)
+    assert torch.equal(back["_tile_lists"][1].order, lists.order)
