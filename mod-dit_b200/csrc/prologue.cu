@@ -14,6 +14,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace moddit {
@@ -89,11 +91,14 @@ struct PrologueArgs {
 
 // Grid: x = head + H * tensor (q, k, v), y = token block, z = batch - the CTAs of one token block run together,
 // so the rotary table rows of the block are fetched from HBM once and shared through L2.
-template <typename T, int D, int kNorm>
+// kRope is the table form (MODDIT_ROPE_*); whether anything is rotated is decided at run time.
+template <typename T, int D, int kNorm, int kRope>
 __global__ void __launch_bounds__(kThreads, 3) qkv_prologue_kernel(const __grid_constant__ PrologueArgs a) {
   constexpr int kTpr = D / 8;               // threads per row
   constexpr int kRpp = kThreads / kTpr;     // rows per pass
   constexpr float kInvD = 1.0f / D;         // D is a power of two: the product equals the division
+  constexpr int kTabW = kRope == MODDIT_ROPE_PAIR ? D / 2 : D;      // table values per token
+  constexpr int kTabC = kRope == MODDIT_ROPE_PAIR ? 4 : 8;          // table values per thread and row
   __shared__ float red[kRpp][D];
 
   const int which = blockIdx.x / a.H;
@@ -125,6 +130,8 @@ __global__ void __launch_bounds__(kThreads, 3) qkv_prologue_kernel(const __grid_
 
   const T* src = in + (static_cast<int64_t>(b) * a.S + row0) * a.token_stride + h * D + cg * 8;
   T* dst = out + ((static_cast<int64_t>(b) * a.H + h) * a.N_out + a.dst_row0 + row0) * D + cg * 8;
+  // table entries of row r of this CTA start at tab + r * kTabW (32-bit offsets: the host checks the size)
+  const int tab = (row0 - a.rope_lo) * kTabW + cg * kTabC;
 
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   // Mean of block blk0 + j from the threads' partial sums, in the order pool_blocks_kernel adds them.
@@ -141,128 +148,128 @@ __global__ void __launch_bounds__(kThreads, 3) qkv_prologue_kernel(const __grid_
     }
     __syncthreads();
   };
-  for (int base = 0; base < rows; base += 8 * kRpp) {   // uniform trip count: the shuffles below need every lane
-    uint4 v[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int r = base + rg + u * kRpp;
-      v[u] = r < rows ? __ldg(reinterpret_cast<const uint4*>(src + static_cast<int64_t>(r) * a.token_stride))
-                      : make_uint4(0, 0, 0, 0);
-    }
-    if (rope_on) {
-      // the table rows are needed one after the other below: ask for all of them now
-      const int tw = a.rope_form == MODDIT_ROPE_PAIR ? D / 2 : D;
-      const int tc = a.rope_form == MODDIT_ROPE_PAIR ? cg * 4 : cg * 8;
+
+  // kWhole: the CTA has all of its 8 * kRpp rows and they are rotated all or none - no test per row.
+  auto run = [&](auto whole_tag) {
+    constexpr bool kWhole = decltype(whole_tag)::value;
+    const bool rope_all = rope_on && row0 >= a.rope_lo && row0 < a.rope_hi;      // only read when kWhole
+    for (int base = 0; base < rows; base += 8 * kRpp) {     // uniform trip count: the shuffles need every lane
+      uint4 v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        const int s = row0 + base + rg + u * kRpp;
-        if (s - row0 < rows && s >= a.rope_lo && s < a.rope_hi) {
-          const int64_t t = static_cast<int64_t>(s - a.rope_lo) * tw + tc;
-          asm volatile("prefetch.global.L1 [%0];" ::"l"(a.cos + t));
-          asm volatile("prefetch.global.L1 [%0];" ::"l"(a.sin + t));
+        const int r = base + rg + u * kRpp;
+        v[u] = (kWhole || r < rows) ? __ldg(reinterpret_cast<const uint4*>(src + static_cast<int64_t>(r) * a.token_stride))
+                                    : make_uint4(0, 0, 0, 0);
+      }
+      if (rope_on) {
+        // the table rows are needed one after the other below: ask for all of them now
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int r = base + rg + u * kRpp;
+          const int s = row0 + r;
+          if (kWhole ? rope_all : (r < rows && s >= a.rope_lo && s < a.rope_hi)) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(a.cos + tab + r * kTabW));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(a.sin + tab + r * kTabW));
+          }
         }
       }
-    }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int r = base + rg + u * kRpp;
-      const bool valid = r < rows;
-      const int s = row0 + r;               // token index within the input
-      uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-      if (normed) {
-        if constexpr (kNorm == MODDIT_NORM_RMS_HEAD || kNorm == MODDIT_NORM_RMS_ALL_HEADS) {
-          float rs;
-          if constexpr (kNorm == MODDIT_NORM_RMS_HEAD) {
-            float ss = 0.f;
+      for (int u = 0; u < 8; ++u) {
+        const int r = base + rg + u * kRpp;
+        const bool valid = kWhole || r < rows;
+        const int s = row0 + r;               // token index within the input
+        uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+        if (normed) {
+          if constexpr (kNorm == MODDIT_NORM_RMS_HEAD || kNorm == MODDIT_NORM_RMS_ALL_HEADS) {
+            float rs;
+            if constexpr (kNorm == MODDIT_NORM_RMS_HEAD) {
+              float ss = 0.f;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float x0 = Pair<T>::lo(w[i]), x1 = Pair<T>::hi(w[i]);
+                ss = fmaf(x0, x0, ss);
+                ss = fmaf(x1, x1, ss);
+              }
+              rs = rsqrtf(__fadd_rn(row_sum<kTpr>(ss) * kInvD, a.eps));
+            } else {
+              rs = valid ? __ldg(a.inv_rms[which] + static_cast<int64_t>(b) * a.S + s) : 0.f;
+            }
+            // x * rsqrt in float32 rounded to T, then the product with the weight rounded to T again
+            const uint32_t wt[4] = {w2.x, w2.y, w2.z, w2.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const float x0 = Pair<T>::lo(w[i]), x1 = Pair<T>::hi(w[i]);
-              ss = fmaf(x0, x0, ss);
-              ss = fmaf(x1, x1, ss);
+              w[i] = Pair<T>::pack(__fmul_rn(Pair<T>::lo(w[i]), rs), __fmul_rn(Pair<T>::hi(w[i]), rs));
+              if (has_w) w[i] = Pair<T>::mul(w[i], wt[i]);
             }
-            rs = rsqrtf(__fadd_rn(row_sum<kTpr>(ss) * kInvD, a.eps));
-          } else {
-            rs = valid ? __ldg(a.inv_rms[which] + static_cast<int64_t>(b) * a.S + s) : 0.f;
+          } else if constexpr (kNorm == MODDIT_NORM_LAYER) {
+            float f[8], wv[8], bv[8];
+            unpack<T>(v[u], f);
+            unpack<T>(w2, wv);
+            unpack<T>(b2, bv);
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum += f[i];
+            const float mean = row_sum<kTpr>(sum) * kInvD;
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              f[i] -= mean;
+              ss = fmaf(f[i], f[i], ss);
+            }
+            const float rstd = rsqrtf(__fadd_rn(row_sum<kTpr>(ss) * kInvD, a.eps));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float y0 = fmaf(f[2 * i] * rstd, has_w ? wv[2 * i] : 1.f, bv[2 * i]);
+              const float y1 = fmaf(f[2 * i + 1] * rstd, has_w ? wv[2 * i + 1] : 1.f, bv[2 * i + 1]);
+              w[i] = valid ? Pair<T>::pack(y0, y1) : 0u;
+            }
           }
-          // x * rsqrt in float32 rounded to T, then the product with the weight rounded to T again
-          const uint32_t wt[4] = {w2.x, w2.y, w2.z, w2.w};
+        }
+        if (kWhole ? rope_all : (rope_on && valid && s >= a.rope_lo && s < a.rope_hi)) {
+          float c[kTabC], n[kTabC];
+          const float* cp = a.cos + tab + r * kTabW;
+          const float* np = a.sin + tab + r * kTabW;
+#pragma unroll
+          for (int i = 0; i < kTabC; i += 4) {
+            *reinterpret_cast<float4*>(c + i) = __ldg(reinterpret_cast<const float4*>(cp + i));
+            *reinterpret_cast<float4*>(n + i) = __ldg(reinterpret_cast<const float4*>(np + i));
+          }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            w[i] = Pair<T>::pack(__fmul_rn(Pair<T>::lo(w[i]), rs), __fmul_rn(Pair<T>::hi(w[i]), rs));
-            if (has_w) w[i] = Pair<T>::mul(w[i], wt[i]);
+            // multipliers of (x0, x1) for the even element (ce, se) and for the odd element (so, co)
+            const float ce = kRope == MODDIT_ROPE_PAIR ? c[i] : c[2 * i];
+            const float co = kRope == MODDIT_ROPE_PAIR ? c[i] : (kRope == MODDIT_ROPE_ELEMENTWISE ? c[2 * i + 1] : c[2 * i]);
+            const float se = kRope == MODDIT_ROPE_PAIR ? n[i] : (kRope == MODDIT_ROPE_ELEMENTWISE ? n[2 * i] : n[2 * i + 1]);
+            const float so = kRope == MODDIT_ROPE_PAIR ? n[i] : n[2 * i + 1];
+            const float x0 = Pair<T>::lo(w[i]), x1 = Pair<T>::hi(w[i]);
+            // products rounded separately, then one add (no fused multiply-add), as a tensor expression does
+            w[i] = Pair<T>::pack(__fsub_rn(__fmul_rn(x0, ce), __fmul_rn(x1, se)),
+                                 __fadd_rn(__fmul_rn(x0, so), __fmul_rn(x1, co)));
           }
-        } else {
-          float f[8], wv[8], bv[8];
-          unpack<T>(v[u], f);
-          unpack<T>(w2, wv);
-          unpack<T>(b2, bv);
-          float sum = 0.f;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) sum += f[i];
-          const float mean = row_sum<kTpr>(sum) * kInvD;
-          float ss = 0.f;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            f[i] -= mean;
-            ss = fmaf(f[i], f[i], ss);
-          }
-          const float rstd = rsqrtf(__fadd_rn(row_sum<kTpr>(ss) * kInvD, a.eps));
+        }
+        if (valid) *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * D) = make_uint4(w[0], w[1], w[2], w[3]);
+        if (pool != nullptr) {                 // rows past the end hold zeros here
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const float y0 = fmaf(f[2 * i] * rstd, has_w ? wv[2 * i] : 1.f, bv[2 * i]);
-            const float y1 = fmaf(f[2 * i + 1] * rstd, has_w ? wv[2 * i + 1] : 1.f, bv[2 * i + 1]);
-            w[i] = valid ? Pair<T>::pack(y0, y1) : 0u;
+            acc[2 * i] += Pair<T>::lo(w[i]);
+            acc[2 * i + 1] += Pair<T>::hi(w[i]);
           }
-        }
-      }
-      if (rope_on && valid && s >= a.rope_lo && s < a.rope_hi) {
-        float ce[4], co[4], se[4], so[4];
-        if (a.rope_form == MODDIT_ROPE_PAIR) {
-          const int64_t t = static_cast<int64_t>(s - a.rope_lo) * (D / 2) + cg * 4;
-          const float4 c = __ldg(reinterpret_cast<const float4*>(a.cos + t));
-          const float4 n = __ldg(reinterpret_cast<const float4*>(a.sin + t));
-          ce[0] = co[0] = c.x; ce[1] = co[1] = c.y; ce[2] = co[2] = c.z; ce[3] = co[3] = c.w;
-          se[0] = so[0] = n.x; se[1] = so[1] = n.y; se[2] = so[2] = n.z; se[3] = so[3] = n.w;
-        } else {
-          const int64_t t = static_cast<int64_t>(s - a.rope_lo) * D + cg * 8;
-          const float4 c0 = __ldg(reinterpret_cast<const float4*>(a.cos + t));
-          const float4 c1 = __ldg(reinterpret_cast<const float4*>(a.cos + t + 4));
-          const float4 n0 = __ldg(reinterpret_cast<const float4*>(a.sin + t));
-          const float4 n1 = __ldg(reinterpret_cast<const float4*>(a.sin + t + 4));
-          ce[0] = c0.x; ce[1] = c0.z; ce[2] = c1.x; ce[3] = c1.z;
-          so[0] = n0.y; so[1] = n0.w; so[2] = n1.y; so[3] = n1.w;
-          if (a.rope_form == MODDIT_ROPE_EVEN_COS_ODD_SIN) {
+          if (spb > 0 && (u + 1) % spb == 0) {  // last slot of a block (the same for every thread)
+            const int j = u / spb;
+            if (j * a.bs < rows) flush(j, min(a.bs, rows - j * a.bs));
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { co[i] = ce[i]; se[i] = so[i]; }
-          } else {
-            co[0] = c0.y; co[1] = c0.w; co[2] = c1.y; co[3] = c1.w;
-            se[0] = n0.x; se[1] = n0.z; se[2] = n1.x; se[3] = n1.z;
+            for (int i = 0; i < 8; ++i) acc[i] = 0.f;
           }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float x0 = Pair<T>::lo(w[i]), x1 = Pair<T>::hi(w[i]);
-          // products rounded separately, then one add (no fused multiply-add), as a tensor expression does
-          w[i] = Pair<T>::pack(__fsub_rn(__fmul_rn(x0, ce[i]), __fmul_rn(x1, se[i])),
-                               __fadd_rn(__fmul_rn(x0, so[i]), __fmul_rn(x1, co[i])));
-        }
-      }
-      if (valid) *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * D) = make_uint4(w[0], w[1], w[2], w[3]);
-      if (pool != nullptr) {                 // rows past the end hold zeros here
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          acc[2 * i] += Pair<T>::lo(w[i]);
-          acc[2 * i + 1] += Pair<T>::hi(w[i]);
-        }
-        if (spb > 0 && (u + 1) % spb == 0) {  // last slot of a block (the same for every thread)
-          const int j = u / spb;
-          if (j * a.bs < rows) flush(j, min(a.bs, rows - j * a.bs));
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] = 0.f;
         }
       }
     }
-  }
+  };
+  const bool rope_mixed = rope_on && !((row0 >= a.rope_lo && row0 + rows <= a.rope_hi) ||
+                                       row0 + rows <= a.rope_lo || row0 >= a.rope_hi);
+  if (rows == 8 * kRpp && !rope_mixed)
+    run(std::true_type{});
+  else
+    run(std::false_type{});
   if (pool != nullptr && spb == 0) flush(0, rows);
 }
 
@@ -303,13 +310,23 @@ int launch_prologue(const PrologueArgs& a, int B, int D, int norm_kind, int64_t 
     MODDIT_CHECK_LAUNCH("token_inv_rms_kernel");
   }
   const dim3 grid(3 * a.H, ceil_div(a.S, a.bs * a.group), B);
+#define MODDIT_PROLOGUE_ROPE(NORM, ROPE)                                        \
+  case ROPE:                                                                    \
+    if (D == 64)                                                                \
+      qkv_prologue_kernel<T, 64, NORM, ROPE><<<grid, kThreads, 0, st>>>(a);     \
+    else                                                                        \
+      qkv_prologue_kernel<T, 128, NORM, ROPE><<<grid, kThreads, 0, st>>>(a);    \
+    break;
 #define MODDIT_PROLOGUE_CASE(NORM)                                              \
   case NORM:                                                                    \
-    if (D == 64)                                                                \
-      qkv_prologue_kernel<T, 64, NORM><<<grid, kThreads, 0, st>>>(a);           \
-    else                                                                        \
-      qkv_prologue_kernel<T, 128, NORM><<<grid, kThreads, 0, st>>>(a);          \
+    switch (rope) {                                                             \
+      MODDIT_PROLOGUE_ROPE(NORM, MODDIT_ROPE_ELEMENTWISE)                       \
+      MODDIT_PROLOGUE_ROPE(NORM, MODDIT_ROPE_EVEN_COS_ODD_SIN)                  \
+      default:                                                                  \
+        MODDIT_PROLOGUE_ROPE(NORM, MODDIT_ROPE_PAIR)                            \
+    }                                                                           \
     break;
+  const int rope = a.cos != nullptr ? a.rope_form : MODDIT_ROPE_PAIR;
   switch (norm_kind) {
     MODDIT_PROLOGUE_CASE(MODDIT_NORM_NONE)
     MODDIT_PROLOGUE_CASE(MODDIT_NORM_RMS_HEAD)
@@ -318,6 +335,7 @@ int launch_prologue(const PrologueArgs& a, int B, int D, int norm_kind, int64_t 
     default:
       return fail(MODDIT_E_ARG, "unknown norm_kind %d", norm_kind);
   }
+#undef MODDIT_PROLOGUE_ROPE
 #undef MODDIT_PROLOGUE_CASE
   MODDIT_CHECK_LAUNCH("qkv_prologue_kernel");
   return MODDIT_OK;
@@ -369,6 +387,7 @@ extern "C" int moddit_qkv_prologue(const void* q_in, const void* k_in, const voi
                      rope_lo, rope_hi, S);
     MODDIT_CHECK_ARG(rope_form >= MODDIT_ROPE_ELEMENTWISE && rope_form <= MODDIT_ROPE_PAIR, "unknown rope_form %d",
                      rope_form);
+    MODDIT_CHECK_ARG(static_cast<int64_t>(S) * D < (1ll << 31), "rotary tables of %d x %d values are too large", S, D);
   }
   const bool pooled = q_pool != nullptr || k_pool != nullptr;
   int bs = 128;
