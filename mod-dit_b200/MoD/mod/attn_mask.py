@@ -77,6 +77,38 @@ def compute_block_sparse_map_triton(query, key, value, warmup_state):
 compute_block_sparse_map = compute_block_sparse_map_triton
 
 
+def _compute_block_sparse_map(query, key, value, *, block_size: int, video_token_num: int, text_token_num: int,
+                              threshold: float, model_type: str, q_chunk_blocks: int = 8):
+    """Keyword form of the same computation (:152-222, the reference's chunked tensor-expression path; the
+    chunk size only bounds its temporaries and is accepted and ignored here: the device path needs none)."""
+    del q_chunk_blocks
+    return flash_attn_with_sparsity_map(query, key, value, block_size=block_size, video_token_num=video_token_num,
+                                        text_token_num=text_token_num, threshold=threshold, model_type=model_type)
+
+
+def reset_peak_gpu_stats(device: Optional[torch.device] = None):
+    """Restart the allocator's peak-memory counters (:41-46)."""
+    if torch.cuda.is_available():
+        torch.cuda.reset_peak_memory_stats(None if device is None else device.index)
+
+
+def get_cuda_arch_versions() -> List[str]:
+    """Compute capability of every visible device as 'sm<major><minor>' (:48-54)."""
+    return ["sm%d%d" % torch.cuda.get_device_capability(i) for i in range(torch.cuda.device_count())]
+
+
+def print_peak_gpu_stats(prefix: str = "", device: Optional[torch.device] = None):
+    """Print the peak allocated / reserved device memory in GiB after a synchronize (:56-70)."""
+    if not torch.cuda.is_available():
+        print(prefix + " GPU not available")
+        return
+    torch.cuda.synchronize()
+    index = None if device is None else device.index
+    gib = float(1 << 30)
+    print(f"{prefix} peak_alloc={torch.cuda.max_memory_allocated(index) / gib:.3f} GiB, "
+          f"peak_reserved={torch.cuda.max_memory_reserved(index) / gib:.3f} GiB")
+
+
 def compute_pooled_map(query, key, warmup_state, pooled_qk=None) -> torch.Tensor:
     """Mean-pooled stand-in for the sparsity map: (B,H,n,n) float16, same polarity as the exact map.
     `pooled_qk`: block means of query and key computed elsewhere (then query and key are not read)."""

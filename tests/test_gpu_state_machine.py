@@ -296,3 +296,23 @@ def test_radial_state_machine(mod):
                                        kv_len_lo=min(S, (valid + 63) // 64 * 64), kv_len_hi=valid)
             assert (out.float().cpu() - ref).abs().max().item() <= 2e-2
     assert not bool(want_mask.all())
+
+
+def test_reference_named_map_functions_and_helpers(mod, capsys):
+    """`_compute_block_sparse_map` / `compute_block_sparse_map` / `compute_block_sparse_map_triton` are three
+    names of one computation in the reference (:152-263); the memory helpers keep their names too."""
+    am = mod["am"]
+    torch.manual_seed(5)
+    q = torch.randn(1, 2, 384, 64, device="cuda", dtype=torch.bfloat16)
+    k, v = torch.randn_like(q), torch.randn_like(q)
+    state = dict(block_size=64, video_token_num=256, text_token_num=128, threshold=1e-3, model_type="hunyuan")
+    a_out, a_map = am.compute_block_sparse_map(q, k, v, state)
+    b_out, b_map = am._compute_block_sparse_map(q, k, v, q_chunk_blocks=2, **state)
+    c_out, c_map = am.compute_block_sparse_map_triton(q, k, v, state)
+    assert torch.equal(a_out, b_out) and torch.equal(a_map, b_map) and torch.equal(a_out, c_out)
+    assert a_map.shape == (1, 2, 4, 4) and a_map.dtype == torch.float16
+    am.reset_peak_gpu_stats()
+    am.reset_peak_gpu_stats(q.device)
+    am.print_peak_gpu_stats("after map:", q.device)
+    assert "peak_alloc=" in capsys.readouterr().out
+    assert am.get_cuda_arch_versions()[0] == "sm100"
