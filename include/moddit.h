@@ -137,6 +137,13 @@ int moddit_mts_noalloc(const void* map_f16, int H, int n, int blocks_per_frame, 
  * MoD/mod/cuda_lstsq_kernel.cu:319-418 and `compute_mtm_pytorch` (MoD/mod/cuda_lstsq.py:42-89). */
 int moddit_mtm(int n, int blocks_per_frame, float regularization, float* mtm, void* stream);
 
+/* The map described by fitted line intensities: out[h,i,j] = d[h, j-i+n-1] + 2*c[h,j] + b_d[h] where rows i and
+ * columns j lie in the same frame (blocks of blocks_per_frame, whole frames only).  Replaces
+ * `reconstruct_attention_map` (MoD/mod/cuda_lstsq.py:271-360, Python loops over every element there); c is the
+ * halved vertical intensity that `solve_lstsq` returns.  d (H, 2n-1), c (H, n), b_d (H) float32; out (H, n, n) float32. */
+int moddit_reconstruct_map(const float* d, const float* c, const float* b_d, int H, int n, int blocks_per_frame,
+                           float* out, void* stream);
+
 /* One-time set-up of the solve for a geometry (n, blocks_per_frame, regularization): eliminates the
  * 2n-1 diagonal unknowns analytically and inverts the remaining (n+1)x(n+1) system in float64.
  * Replaces the cached `torch.linalg.cholesky(MTM)` of MoD/mod/cuda_lstsq.py:153-186.

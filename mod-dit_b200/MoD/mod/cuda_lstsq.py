@@ -25,6 +25,22 @@ def _load_cuda_extension():
     return _Kernels
 
 
+def compute_mts_pytorch(S_T: torch.Tensor, blocks_per_frame: int) -> torch.Tensor:
+    """M^T S (H, 3n) (name of the reference's tensor-expression twin, :91-139; here the fused device pass,
+    which gives the same float32 sums bit for bit on maps of counts / block_size^2)."""
+    return _Kernels.compute_mts(S_T, blocks_per_frame)
+
+
+def compute_mtm_pytorch(S_T: torch.Tensor, blocks_per_frame: int, regularization: float) -> torch.Tensor:
+    """M^T M + regularization * I (3n, 3n) (:42-89); only the shape and device of S_T are used."""
+    return _Kernels.compute_mtm(S_T, blocks_per_frame, regularization)
+
+
+def reconstruct_attention_map(features, n, blocks_per_frame=4):
+    """The (H, n, n) map that a feature dictionary {'d', 'c', 'b_d'} describes (:271-360)."""
+    return _ops.reconstruct_map(features['d'], features['c'], features['b_d'], int(blocks_per_frame))
+
+
 def features_from_solution(X: torch.Tensor, n: int):
     """Split the raw solution (H, 3n) as MoD/mod/cuda_lstsq.py:257-261 does ('c' is halved)."""
     nd = 2 * n - 1

@@ -504,6 +504,38 @@ extern "C" int moddit_mts_noalloc(const void* map_f16, int H, int n, int blocks_
   return MODDIT_OK;
 }
 
+namespace moddit {
+namespace {
+// The map that fitted line intensities describe: one thread per element, rows of the output contiguous over
+// the threads.  Sum in the order diagonal, vertical, block term (float32), as the reference accumulates them.
+__global__ void __launch_bounds__(256) reconstruct_map_kernel(const float* __restrict__ d, const float* __restrict__ c,
+                                                              const float* __restrict__ b_d, int n, int bpf,
+                                                              float* __restrict__ out) {
+  const int h = blockIdx.z, i = blockIdx.y;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const int covered = (n / bpf) * bpf;          // the block term stops at the last whole frame
+  float v = 0.f + __ldg(d + static_cast<int64_t>(h) * (2 * n - 1) + (j - i + n - 1));
+  v += 2.f * __ldg(c + static_cast<int64_t>(h) * n + j);
+  if (i < covered && j < covered && i / bpf == j / bpf) v += __ldg(b_d + h);
+  out[(static_cast<int64_t>(h) * n + i) * n + j] = v;
+}
+}  // namespace
+}  // namespace moddit
+
+extern "C" int moddit_reconstruct_map(const float* d, const float* c, const float* b_d, int H, int n,
+                                      int blocks_per_frame, float* out, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(d && c && b_d && out, "reconstruct_map: null pointer");
+  MODDIT_CHECK_ARG(H > 0 && H <= 65535 && n > 0 && n <= 65535 && blocks_per_frame > 0,
+                   "reconstruct_map: H=%d n=%d blocks_per_frame=%d out of range", H, n, blocks_per_frame);
+  if (int rc = require_sm100()) return rc;
+  moddit::reconstruct_map_kernel<<<dim3(ceil_div(n, 256), n, H), 256, 0, as_stream(stream)>>>(d, c, b_d, n,
+                                                                                           blocks_per_frame, out);
+  MODDIT_CHECK_LAUNCH("reconstruct_map_kernel");
+  return MODDIT_OK;
+}
+
 extern "C" int moddit_mtm(int n, int blocks_per_frame, float regularization, float* mtm, void* stream) {
   clear_error();
   MODDIT_CHECK_ARG(mtm, "mtm: null pointer");

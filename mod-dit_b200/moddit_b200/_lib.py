@@ -43,6 +43,7 @@ SIGNATURES = {
     "moddit_mts_noalloc_max_bytes": (c_size_t, []),
     "moddit_mts_noalloc": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moddit_mtm": (c_int, [c_int, c_int, c_float, c_void_p, c_void_p]),
+    "moddit_reconstruct_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moddit_solve_factor_bytes": (c_size_t, [c_int]),
     "moddit_solve_prepare_workspace_bytes": (c_size_t, [c_int]),
     "moddit_solve_prepare": (c_int, [c_int, c_int, c_double, c_void_p, c_void_p, c_size_t, c_void_p]),

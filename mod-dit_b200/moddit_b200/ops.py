@@ -342,6 +342,20 @@ _FACTOR_CACHE: Dict[tuple, torch.Tensor] = {}
 _FACTOR_LOCK = threading.Lock()
 
 
+def reconstruct_map(d: torch.Tensor, c: torch.Tensor, b_d: torch.Tensor, blocks_per_frame: int) -> torch.Tensor:
+    """(H,2n-1), (H,n), (H,) float32 line intensities -> (H,n,n) float32 map they describe."""
+    dev = _need_cuda(d, c, b_d)
+    d, c, b_d = (t.to(torch.float32).contiguous() for t in (d, c, b_d))
+    H, n = c.shape
+    if d.shape != (H, 2 * n - 1) or b_d.shape != (H,):
+        raise ValueError("expected d (H, 2n-1), c (H, n), b_d (H,)")
+    out = torch.empty(H, n, n, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev), _timed("moddit_reconstruct_map", dev):
+        check(lib.moddit_reconstruct_map(_ptr(d), _ptr(c), _ptr(b_d), H, n, int(blocks_per_frame), _ptr(out),
+                                         _stream(dev)), "moddit_reconstruct_map")
+    return out
+
+
 def solve_factor(n: int, blocks_per_frame: int, regularization: float, device) -> torch.Tensor:
     """Inverse of the reduced system for this geometry, computed once per (device, n, bpf, lambda)."""
     device = torch.device(device)

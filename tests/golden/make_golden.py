@@ -126,6 +126,7 @@ def main():
         out[f"ls{ci}_d"] = feats["d"].numpy()
         out[f"ls{ci}_c"] = feats["c"].numpy()
         out[f"ls{ci}_bd"] = feats["b_d"].numpy()
+        out[f"ls{ci}_recon"] = ls.reconstruct_attention_map(feats, n, bpf).numpy()
         out[f"ls{ci}_zero_d_shape"] = np.array(zeros["d"].shape)
         assert float(zeros["d"].abs().sum() + zeros["c"].abs().sum() + zeros["b_d"].abs().sum()) == 0.0
     np.savez_compressed(os.path.join(HERE, "lstsq.npz"), **out)

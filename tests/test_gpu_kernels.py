@@ -235,3 +235,26 @@ def test_tile_lists_bit_exact(ops, bs, N, H):
     for h in range(H):
         for p in range(rc.shape[1]):
             assert np.array_equal(ent[h, p, :rc[h, p]], re[h, p, :rc[h, p]])
+
+
+def test_reconstruct_map_matches_reference_and_oracle(golden_dir):
+    """`reconstruct_attention_map` under its reference name: bit-exact against the map the reference builds
+    from its own solution (stored), and against the oracle on a ragged frame layout."""
+    from MoD.mod import cuda_lstsq as ls
+    g = np.load(os.path.join(golden_dir, "lstsq.npz"), allow_pickle=False)
+    for ci in range(4):
+        n, bpf, H = (int(x) for x in g[f"ls{ci}_meta"])
+        feats = {"d": torch.from_numpy(g[f"ls{ci}_d"]).cuda(), "c": torch.from_numpy(g[f"ls{ci}_c"]).cuda(),
+                 "b_d": torch.from_numpy(g[f"ls{ci}_bd"]).cuda()}
+        got = ls.reconstruct_attention_map(feats, n, bpf)
+        assert got.shape == (H, n, n) and got.dtype == torch.float32
+        assert torch.equal(got.cpu(), torch.from_numpy(g[f"ls{ci}_recon"]))
+    torch.manual_seed(4)
+    n, bpf, H = 301, 30, 3
+    feats = {"d": torch.randn(H, 2 * n - 1), "c": torch.randn(H, n), "b_d": torch.randn(H)}
+    want = orc.reconstruct_attention_map(feats, n, bpf)
+    got = ls.reconstruct_attention_map({k_: v_.cuda() for k_, v_ in feats.items()}, n, bpf)
+    assert torch.equal(got.cpu(), want)
+    S = torch.rand(H, n, n).half().cuda()
+    assert torch.equal(ls.compute_mts_pytorch(S, bpf), ls._load_cuda_extension().compute_mts(S, bpf))
+    assert ls.compute_mtm_pytorch(S, bpf, 1.0).shape == (3 * n, 3 * n)

@@ -67,6 +67,9 @@ def test_lstsq_matches_reference(golden_dir):
         assert torch.allclose(f["d"], torch.from_numpy(g[f"ls{ci}_d"]), **tol)
         assert torch.allclose(f["c"], torch.from_numpy(g[f"ls{ci}_c"]), **tol)
         assert torch.allclose(f["b_d"], torch.from_numpy(g[f"ls{ci}_bd"]), **tol)
+        ref_f = {"d": torch.from_numpy(g[f"ls{ci}_d"]), "c": torch.from_numpy(g[f"ls{ci}_c"]),
+                 "b_d": torch.from_numpy(g[f"ls{ci}_bd"])}
+        assert torch.equal(orc.reconstruct_attention_map(ref_f, n, bpf), torch.from_numpy(g[f"ls{ci}_recon"]))
         # the fp64 solve bounds both fp32 paths
         fp = orc.solve_features(mts, n, bpf, lam, precise=True)
         assert torch.allclose(fp["d"].float(), torch.from_numpy(g[f"ls{ci}_d"]), **tol)
