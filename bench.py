@@ -395,7 +395,7 @@ def run_ours(args):
             line["prologue"] = prologue
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.workload, args.gain, blocks=args.cpu_blocks)
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -542,10 +542,30 @@ def run_reference(args):
         "e2e": {"value": round(value, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_RESULT_OUT = None
+
+
+def keep_stdout_for_the_result():
+    """The result line must be the only thing on standard output, but libraries write there too (NCCL prints
+    its version on the first collective): point file descriptor 1 at standard error for everybody else and
+    keep a private handle on the real standard output for `emit`."""
+    global _RESULT_OUT
+    sys.stdout.flush()
+    _RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
+def emit(record) -> None:
+    out = _RESULT_OUT if _RESULT_OUT is not None else sys.stdout
+    out.write(json.dumps(record) + "\n")
+    out.flush()
 
 
 def main():
+    keep_stdout_for_the_result()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -570,7 +590,7 @@ def main():
                             reps=max(args.steps, 1))
         peak = float(load_peaks()["hbm_gbs"])
         rec.update(peak=peak, frac=round(rec["achieved"] / peak, 4))
-        print(json.dumps(rec), flush=True)
+        emit(rec)
     elif args.impl == "reference":
         run_reference(args)
     else:
