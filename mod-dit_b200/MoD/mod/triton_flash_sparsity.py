@@ -139,3 +139,73 @@ def flash_attn_with_sparsity_map(query, key, value, threshold, block_size, model
         query, key, lse, softmax_scale=sm_scale, log_threshold=ln_thresh, q_video_offset=q_video_offset,
         k_video_offset=k_video_offset, video_blocks=video_block_num, block_size=block_size)
     return out, sparsity_map
+
+
+# ---- self-test of the module (`python -m MoD.mod.triton_flash_sparsity`), as in the reference (:343-455) ----
+
+@torch.no_grad()
+def _naive_attn_with_sparsity(query, key, value, threshold, block_size, model_type="hunyuan", video_token_num=0,
+                              text_token_num=0):
+    """Checker for the self-test below, never used by the attention path: the full probability matrix with
+    tensor expressions in float32 on the inputs' device, the output from it, and per video block the share of
+    probabilities below the threshold (:345-370).  Memory grows with S^2: small sequences only."""
+    B, H, S, D = query.shape
+    if model_type not in ("hunyuan", "wan", "cogvideox"):
+        raise ValueError(f"Unknown model_type: {model_type}")
+    video = S if model_type == "wan" else video_token_num
+    first = text_token_num if model_type == "cogvideox" else 0
+    n = video // block_size
+    probs = torch.softmax(query.float() @ key.float().transpose(-1, -2) * D ** -0.5, dim=-1)
+    output = (probs @ value.float()).to(query.dtype)
+    tiles = probs[:, :, first:first + video, first:first + video].reshape(B, H, n, block_size, n, block_size)
+    return output, tiles.lt(threshold).float().mean(dim=(3, 5)).to(torch.float16)
+
+
+def test_correctness(B=1, H=4, S=640, D=128, block_size=64, threshold=0.01, model_type="hunyuan"):
+    """Output and map of the device path against the checker on seeded inputs; the reference's bounds (5e-2)."""
+    g = torch.Generator(device="cuda").manual_seed(42)
+    q, k, v = (torch.randn(B, H, S, D, device="cuda", dtype=torch.float16, generator=g) for _ in range(3))
+    text = 128
+    kw = dict(model_type=model_type, video_token_num=S - text, text_token_num=text)
+    out, sp = flash_attn_with_sparsity_map(q, k, v, threshold, block_size, **kw)
+    ref_out, ref_sp = _naive_attn_with_sparsity(q, k, v, threshold, block_size, **kw)
+    o_err = (out.float() - ref_out.float()).abs().max().item()
+    sp_err = (sp.float() - ref_sp.float()).abs().max().item()
+    print(f"  O max error:        {o_err:.6f}")
+    print(f"  Sparsity max error: {sp_err:.6f}")
+    assert o_err < 5e-2, f"O error too large: {o_err}"
+    assert sp_err < 5e-2, f"Sparsity error too large: {sp_err}"
+
+
+def benchmark(B=1, H=24, S=4096, D=128, block_size=128, threshold=0.01, warmup=10, rep=50):
+    """Milliseconds per call of the device path and of the checker (CUDA events on the current stream)."""
+    q, k, v = (torch.randn(B, H, S, D, device="cuda", dtype=torch.float16) for _ in range(3))
+    kw = dict(video_token_num=S - 128, text_token_num=128)
+
+    def time_ms(fn):
+        for _ in range(warmup):
+            fn(q, k, v, threshold, block_size, **kw)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(rep):
+            fn(q, k, v, threshold, block_size, **kw)
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / rep
+
+    ours, naive = time_ms(flash_attn_with_sparsity_map), time_ms(_naive_attn_with_sparsity)
+    print(f"  dense forward + replay map:    {ours:.2f} ms")
+    print(f"  tensor expressions:            {naive:.2f} ms")
+    print(f"  Speedup:                       {naive / ours:.1f}x")
+
+
+if __name__ == "__main__":
+    print("=== Correctness Tests ===")
+    for _model in ("hunyuan", "cogvideox"):
+        for _bs in (64, 128):
+            print(f"model_type={_model}, block_size={_bs}, D=128")
+            test_correctness(block_size=_bs, D=128, model_type=_model)
+    print("\nAll correctness tests passed!\n")
+    print("=== Benchmark (B=1, H=24, S=4096, D=128, block_size=128) ===")
+    benchmark()

@@ -316,3 +316,13 @@ def test_reference_named_map_functions_and_helpers(mod, capsys):
     am.print_peak_gpu_stats("after map:", q.device)
     assert "peak_alloc=" in capsys.readouterr().out
     assert am.get_cuda_arch_versions()[0] == "sm100"
+
+
+def test_module_self_test_runs(mod, capsys):
+    """`test_correctness` of the map module (the reference runs it from `__main__`, :372-400, 446-452)."""
+    tf = mod["tf"]
+    for model in ("hunyuan", "cogvideox"):
+        for bs in (64, 128):
+            tf.test_correctness(block_size=bs, D=128, model_type=model)
+    assert capsys.readouterr().out.count("Sparsity max error") == 4
+    tf.benchmark(H=2, S=1024, warmup=1, rep=2)
