@@ -203,3 +203,34 @@ def test_radial_mask_at_full_size():
     assert bool(tiles[0, 0].all()) and bool(tiles[0, 1].all())             # neighbouring frames are kept whole
     sparsity = 1.0 - m.float().mean().item()
     assert 0.5 < sparsity < 0.95
+
+
+def test_prologue_at_full_size(env):
+    """The processors' prologue at the full shape: with no normalisation and an identity rotation it is a pure
+    change of layout (bit-exact against a transpose) and its block means equal pooling the result; with a real
+    rotation every pair keeps its length up to the rounding of its two values, and sampled tokens equal the
+    CPU oracle bit for bit."""
+    ops = env["ops"]
+    q = env["q"]                                                   # (1, H, N, D) head-major
+    tok = q[0].transpose(0, 1).reshape(1, N, H * D).contiguous()   # the token-major projection it came from
+    one, zero = torch.ones(VIDEO, D // 2, device="cuda"), torch.zeros(VIDEO, D // 2, device="cuda")
+    (gq, _, _), (pq, _) = ops.qkv_prologue(tok, None, None, num_heads=H, rope_cos=one, rope_sin=zero,
+                                           rope_form="pair", rope_range=(0, VIDEO), pool_block_size=BS)
+    assert torch.equal(gq, q)
+    assert torch.equal(pq, ops.pool_blocks(q, BS))
+    del gq, pq, one, zero
+    g = torch.Generator(device="cuda").manual_seed(3)
+    ang = torch.rand(VIDEO, D // 2, device="cuda", generator=g) * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    (rq, _, _), _ = ops.qkv_prologue(tok, None, None, num_heads=H, rope_cos=cos, rope_sin=sin, rope_form="pair",
+                                     rope_range=(0, VIDEO))
+    assert torch.equal(rq[:, :, VIDEO:], q[:, :, VIDEO:])          # text tokens are not rotated
+    for h in (0, H - 1):
+        a = q[0, h, :VIDEO].float().unflatten(-1, (-1, 2)).pow(2).sum(-1).sqrt()
+        b = rq[0, h, :VIDEO].float().unflatten(-1, (-1, 2)).pow(2).sum(-1).sqrt()
+        assert bool(((a - b).abs() <= 2.0 ** -7 * a + 1e-6).all())
+    rows = torch.tensor([0, 1, 127, 128, 4097, 57600, VIDEO - 1, VIDEO, N - 1])
+    want = orc.qkv_prologue(tok[:, rows].cpu(), tok[:, rows].cpu(), tok[:, rows].cpu(), num_heads=H,
+                            rope_cos=cos[rows[:7]].cpu(), rope_sin=sin[rows[:7]].cpu(), rope_form="pair",
+                            rope_range=(0, 7))[0]
+    assert torch.equal(rq[:, :, rows.cuda()].cpu(), want)
