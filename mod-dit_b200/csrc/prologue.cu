@@ -93,7 +93,7 @@ struct PrologueArgs {
 // so the rotary table rows of the block are fetched from HBM once and shared through L2.
 // kRope is the table form (MODDIT_ROPE_*); whether anything is rotated is decided at run time.
 template <typename T, int D, int kNorm, int kRope>
-__global__ void __launch_bounds__(kThreads, 3) qkv_prologue_kernel(const __grid_constant__ PrologueArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) qkv_prologue_kernel(const __grid_constant__ PrologueArgs a) {
   constexpr int kTpr = D / 8;               // threads per row
   constexpr int kRpp = kThreads / kTpr;     // rows per pass
   constexpr float kInvD = 1.0f / D;         // D is a power of two: the product equals the division
