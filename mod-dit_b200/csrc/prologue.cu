@@ -4,13 +4,15 @@
 // the data.  Follows MoD/models/hunyuan/attention_processor.py:57-106, MoD/models/wan/attention_processor.py:70-93
 // and 123-125, MoD/models/cogvideox/attention_processor.py:113-135.
 //
-// One CTA = one block of `block_size` tokens of one head of one of the three tensors.  D/8 threads cover a row
-// with one 16-byte load each (a 2*D-byte piece of the token's row), so the row statistics are a shuffle
-// reduction over D/8 lanes and a rotary pair never leaves its thread; the head-major store is contiguous
-// over the whole block.  Thread-to-row mapping and summation order of the optional block means are those of
-// pool_blocks_kernel, so the means equal the ones pooled afterwards from the stored tensor bit for bit.
+// One CTA = eight rows per thread of one head of one of the three tensors: one token block of 128 rows at
+// D = 128, several shorter blocks otherwise.  D/8 threads cover a row with one 16-byte load each (a 2*D-byte
+// piece of the token's row), so the row statistics are a shuffle reduction over D/8 lanes and a rotary pair
+// never leaves its thread; the head-major store is contiguous over the CTA's rows.  Thread-to-row mapping and
+// summation order of the optional block means are those of pool_blocks_kernel, so the means equal the ones
+// pooled afterwards from the stored tensor bit for bit.  1/sqrt is the hardware approximation, as in the
+// tensor library's own device code.
 // Bound: HBM.  Algorithmic bytes per token and tensor: 2*H*D read + 2*H*D written (+ the rotary tables:
-// 8*D bytes per token, shared by the heads through L2).
+// 4*D or 8*D bytes per token, fetched once for all heads and shared through L2).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
