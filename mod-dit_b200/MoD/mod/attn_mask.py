@@ -346,7 +346,9 @@ def SparseAttentionWithMap(
     block_size = warmup_state['block_size']
     video_token_num = warmup_state.get('video_token_num', 0)
 
-    if use_dense:
+    if use_dense or warmup_state['sparse_type'] == 'full':
+        # 'full' is accepted by create_adaptive_mask_state but has no branch in the reference (:598-729); here it
+        # means what its name says: dense attention on every step
         query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
         valid = _valid_kv(pre_defined_mask, seq_len)
         output, _ = dense_attention_with_lse(query, key, value, kv_len=valid)

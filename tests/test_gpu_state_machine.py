@@ -221,6 +221,9 @@ def test_use_dense_and_unsupported_types(mod):
     out, info = am.SparseAttentionWithMap(q, q, q, state, LOG, use_dense=True, use_cuda=True)
     ref = orc.masked_attention(q.cpu(), q.cpu(), q.cpu(), torch.ones(1, 8, 8, dtype=torch.bool), 64)
     assert (out.float().cpu() - ref).abs().max().item() <= 2e-2 and info["mask"] is None
+    state["sparse_type"] = "full"              # dense on every step
+    full, info = am.SparseAttentionWithMap(q, q, q, state, LOG, current_step=20)
+    assert torch.equal(full, out) and info["mask"] is None
     state["sparse_type"] = "svg"
     with pytest.raises(NotImplementedError):
         am.SparseAttentionWithMap(q, q, q, state, LOG, current_step=0)
