@@ -188,6 +188,36 @@ def main():
     out["count"] = np.array(len(radial_cases))
     np.savez_compressed(os.path.join(HERE, "radial.npz"), **out)
 
+    # ---- 4b. the rotary function the Wan processor defines inside its __call__ ------------------------
+    # (MoD/models/wan/attention_processor.py:78-90): the processor module needs `diffusers`, which is absent, so
+    # the nested function is lifted out of the parsed file and run as it stands
+    import ast
+    import textwrap
+    src = open(os.path.join(args.reference, "MoD", "models", "wan", "attention_processor.py")).read()
+    nested = [node for node in ast.walk(ast.parse(src))
+              if isinstance(node, ast.FunctionDef) and node.name == "apply_rotary_emb"]
+    assert len(nested) == 1
+    scope = {"torch": torch}
+    exec(textwrap.dedent(ast.get_source_segment(src, nested[0])), scope)
+    out = {}
+    for ci, (dtype, S, Hn, Dh) in enumerate([(torch.bfloat16, 9, 2, 16), (torch.float16, 5, 3, 64),
+                                             (torch.float32, 7, 1, 128)]):
+        g = torch.Generator().manual_seed(500 + ci)
+        x = torch.randn(2, S, Hn, Dh, generator=g).to(dtype)
+        ang = torch.rand(S, Dh // 2, generator=g) * 6.28
+        # tables shaped like the model's: (1, S, 1, D); even and odd entries differ on purpose
+        cos = (ang.cos().repeat_interleave(2, 1) * torch.linspace(0.9, 1.1, Dh)).view(1, S, 1, Dh)
+        sin = (ang.sin().repeat_interleave(2, 1) * torch.linspace(1.1, 0.9, Dh)).view(1, S, 1, Dh)
+        y = scope["apply_rotary_emb"](x, cos, sin)
+        assert y.dtype == dtype
+        out[f"rot{ci}_dtype"] = np.array(str(dtype).replace("torch.", ""))
+        out[f"rot{ci}_x"] = x.float().numpy()
+        out[f"rot{ci}_cos"] = cos.view(S, Dh).numpy()
+        out[f"rot{ci}_sin"] = sin.view(S, Dh).numpy()
+        out[f"rot{ci}_y"] = y.float().numpy()
+    out["count"] = np.array(3)
+    np.savez_compressed(os.path.join(HERE, "rotary.npz"), **out)
+
     # ---- 5. state keys -----------------------------------------------------------------------------
     state = st.create_adaptive_mask_state("hunyuan", 24, 115200, 256, 3840, 30)
     with open(os.path.join(HERE, "state_keys.txt"), "w") as fh:

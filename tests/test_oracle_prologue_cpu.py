@@ -48,3 +48,26 @@ def test_rotary_range_leaves_other_tokens_alone():
     assert torch.equal(part[0][:, :, :10], plain[0][:, :, :10]) and torch.equal(part[0][:, :, 30:], plain[0][:, :, 30:])
     shifted = orc.qkv_prologue(q[:, 10:30], k[:, 10:30], v[:, 10:30], num_heads=H, rope_cos=cos[:20], rope_sin=sin[:20])
     assert torch.equal(part[1][:, :, 10:30], shifted[1])
+
+
+def test_wan_rotary_function_matches_the_reference(golden_dir):
+    """`_rope_even_cos_odd_sin` against outputs of the function the reference's Wan processor defines
+    (stored by tests/golden/make_golden.py, which runs that function as it stands): bit-exact, and through
+    `qkv_prologue` as well."""
+    import os
+
+    import numpy as np
+    g = np.load(os.path.join(golden_dir, "rotary.npz"), allow_pickle=False)
+    for ci in range(int(g["count"])):
+        dtype = getattr(torch, str(g[f"rot{ci}_dtype"]))
+        x = torch.from_numpy(g[f"rot{ci}_x"]).to(dtype)                 # (B, S, H, D)
+        cos, sin = torch.from_numpy(g[f"rot{ci}_cos"]), torch.from_numpy(g[f"rot{ci}_sin"])
+        want = torch.from_numpy(g[f"rot{ci}_y"]).to(dtype)
+        assert torch.equal(orc._rope_even_cos_odd_sin(x, cos, sin), want)
+        if dtype == torch.float32:
+            continue
+        B, S, Hn, Dh = x.shape
+        flat = x.reshape(B, S, Hn * Dh)
+        got = orc.qkv_prologue(flat, flat, flat, num_heads=Hn, rope_cos=cos, rope_sin=sin,
+                               rope_form="even_cos_odd_sin")[0]
+        assert torch.equal(got, want.transpose(1, 2))
