@@ -21,3 +21,16 @@ def test_reference_arm_prints_one_json_line():
     assert rec["cpu_baseline"]["value"] == rec["value"] and rec["cpu_baseline"]["sample"]
     assert rec["e2e"] == {"value": rec["value"], "unit": rec["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert rec["gpu_launches"] == 0 and "workload" in rec["config"]
+
+
+def test_reference_arm_under_torchrun_prints_on_rank_zero_only():
+    """Launched with one process per GPU, the reference arm runs on rank 0 alone; the other ranks exit 0."""
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29541", os.path.join(ROOT, "bench.py"),
+                          "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "1", "--ref-blocks", "2",
+                          "--workload", "small"], capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [ln for ln in res.stdout.splitlines() if ln.strip().startswith("{")]
+    assert len(lines) == 1
+    rec = json.loads(lines[0])
+    assert rec["impl"] == "reference" and rec["cpu_baseline"]["kind"] == "port"
