@@ -113,8 +113,7 @@ def compute_pooled_map(query, key, warmup_state, pooled_qk=None) -> torch.Tensor
     """Mean-pooled stand-in for the sparsity map: (B,H,n,n) float16, same polarity as the exact map.
     `pooled_qk`: block means of query and key computed elsewhere (then query and key are not read)."""
     bs = warmup_state['block_size']
-    n = _video_blocks(warmup_state, query.shape[2])
-    off = warmup_state['text_token_num'] // bs if warmup_state['model_type'] == 'cogvideox' else 0
+    _, n, off = _geometry(warmup_state, query.shape[2])
     if pooled_qk is not None:
         qbar, kbar = pooled_qk
     else:
@@ -124,10 +123,29 @@ def compute_pooled_map(query, key, warmup_state, pooled_qk=None) -> torch.Tensor
                            scale=query.shape[3] ** -0.5)
 
 
-def _video_blocks(warmup_state, seq_len):
-    if warmup_state['model_type'] == 'wan':
-        return seq_len // warmup_state['block_size']
-    return warmup_state['video_token_num'] // warmup_state['block_size']
+def block_geometry(model_type: str, block_size: int, video_token_num: int, text_token_num: int,
+                   seq_len: int) -> Tuple[int, int, int]:
+    """(blocks in the sequence, video blocks n, index of the first video block) on the block grid that starts
+    at token 0.
+
+    For block-aligned shapes these are the reference's floor divisions (:165, :542-557; it accepts nothing
+    else).  Shapes it rejects are laid out so that nothing is dropped: the sequence has ceil(seq_len / block_size)
+    blocks, the last one short; a block that holds any text token counts as a text block (kept whole, like all
+    text rows and columns), so the video blocks are the full-video blocks after (cogvideox) or before (hunyuan)
+    the text.  CogVideoX-1.5 at 44,880 video + 224 text tokens and block 64: 705 blocks, 4 text blocks (the fourth
+    half text, half video), 701 video blocks of which the last holds 48 tokens."""
+    nb = (seq_len + block_size - 1) // block_size
+    if model_type == 'wan':
+        return nb, nb, 0
+    if model_type == 'cogvideox':
+        first = min(nb, (text_token_num + block_size - 1) // block_size)
+        return nb, nb - first, first
+    return nb, min(nb, video_token_num // block_size), 0
+
+
+def _geometry(warmup_state, seq_len) -> Tuple[int, int, int]:
+    return block_geometry(warmup_state['model_type'], warmup_state['block_size'], warmup_state['video_token_num'],
+                          warmup_state['text_token_num'], seq_len)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -156,13 +174,15 @@ def _valid_kv(pre_defined_mask: Optional[torch.Tensor], seq_len: int) -> int:
 
 
 def _engine_lists(mask: torch.Tensor, block_size: int, seq_len: int):
+    """(work lists, True when the mask is known on the host to keep every block)."""
     if mask.dim() == 2:
         mask = mask.unsqueeze(0)
     nb = (seq_len + block_size - 1) // block_size
     if mask.shape[-1] != nb or mask.shape[-2] != nb:
         # a mask over the video region only (use_dense passes one): it can only be all-true
         mask = torch.ones(1, nb, nb, device=mask.device, dtype=torch.bool)
-    return _ops.tile_lists(mask, block_size, seq_len)
+        return _ops.tile_lists(mask, block_size, seq_len), True
+    return _ops.tile_lists(mask, block_size, seq_len), False
 
 
 def _events(ready):
@@ -177,22 +197,30 @@ def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_
 
     Video query rows (index < video_token_num) see the keys below the valid length rounded up to 64, text
     rows see exactly the valid keys - the split the reference gets from its two third-party kernels.
-    One kernel launch covers both; the result is (B,H,S,D).
+    One kernel launch covers both; the result is (B,H,S,D).  When the mask is a stand-in that keeps every
+    block (a caller passing a mask of another shape, as the dense steps do), every row sees exactly the valid
+    keys, like the reference's dense branch (:268-276).  Whether a full-shape mask happens to be all true is
+    not looked up (the reference pays a host synchronisation per call for that): it goes down the sparse
+    branch with the 64-rounded border.
     """
     seq_len = query.shape[2]
     query, key = query.contiguous(), key.contiguous()
-    lists = _lists if _lists is not None else _engine_lists(mask, block_size, seq_len)
+    all_kept = False
+    if _lists is not None:
+        lists = _lists
+    else:
+        lists, all_kept = _engine_lists(mask, block_size, seq_len)
     counts, entries, order = lists.counts, lists.entries, lists.order
     for ev in _events(_value_ready):   # inputs produced on another stream (e.g. still arriving from peers)
         torch.cuda.current_stream(query.device).wait_event(ev)
     value = value.contiguous()
     if pre_defined_mask is None:
-        return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, check_status=False,
+        return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, check_status="deferred",
                                     scatter=_scatter)
     valid = _valid_kv(pre_defined_mask, seq_len)
-    border = min(seq_len, (valid + 63) // 64 * 64)
+    border = valid if all_kept else min(seq_len, (valid + 63) // 64 * 64)
     return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, q_split=video_token_num,
-                                kv_len_lo=border, kv_len_hi=valid, check_status=False, scatter=_scatter)
+                                kv_len_lo=border, kv_len_hi=valid, check_status="deferred", scatter=_scatter)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -223,20 +251,18 @@ def _mode_codes(mode, device) -> torch.Tensor:
 def generate_mask_from_lines(warmup_state: Dict, num_heads: int, n: int, blocks_per_frame: int,
                              selected_lines: torch.Tensor, mode, device: torch.device) -> torch.Tensor:
     """Bool block mask from the selected lines (:440-559); `n` is the sequence length in tokens."""
-    block_size = warmup_state['block_size']
-    video_blocks = warmup_state['video_token_num'] // block_size
     model_type = warmup_state.get('model_type')
     if model_type not in _lib.LAYOUT:
-        return torch.ones(num_heads, n // block_size, n // block_size, dtype=torch.bool, device=device)
-    if model_type == 'wan' and video_blocks == 0:
-        video_blocks = n // block_size
+        nb = (n + warmup_state['block_size'] - 1) // warmup_state['block_size']
+        return torch.ones(num_heads, nb, nb, dtype=torch.bool, device=device)
+    total_blocks, video_blocks, first = _geometry(warmup_state, n)
     selected_lines = torch.as_tensor(selected_lines, device=device)
     if selected_lines.dim() == 1:
         selected_lines = selected_lines.unsqueeze(1)
     return _ops.mask_from_lines(selected_lines.long(), _mode_codes(mode, device), n=video_blocks,
                                 blocks_per_frame=blocks_per_frame, model_type=model_type,
-                                text_blocks=warmup_state['text_token_num'] // block_size,
-                                total_blocks=n // block_size)
+                                text_blocks=first if model_type == 'cogvideox' else total_blocks - video_blocks,
+                                total_blocks=total_blocks)
 
 
 def predict_mask_from_warmup(warmup_state: Dict, n: int, top_k: int = 10, layer_idx: int = 0) -> Dict:
@@ -245,7 +271,7 @@ def predict_mask_from_warmup(warmup_state: Dict, n: int, top_k: int = 10, layer_
     blocks_per_frame = warmup_state['blocks_per_frame']
     if not is_warmup_complete(warmup_state):
         device = torch.device("cuda")
-        nb = n // warmup_state['block_size']
+        nb = _geometry(warmup_state, n)[0]
         return {'mode': ['full'] * num_heads, 'block_diagonal': [False] * num_heads, 'selected_lines': [],
                 'mask': torch.ones(num_heads, nb, nb, dtype=torch.bool, device=device)}
     history = warmup_state['features_history']
@@ -278,10 +304,7 @@ def _lists_for(warmup_state: Dict, seq_len: int):
 
 def _video_region(warmup_state: Dict, mask: torch.Tensor) -> Tuple[torch.Tensor, int]:
     """(full mask, first video block) so the history merge can index the video region in place."""
-    bs = warmup_state['block_size']
-    if warmup_state['model_type'] == 'cogvideox':
-        return mask, warmup_state['text_token_num'] // bs
-    return mask, 0
+    return mask, _geometry(warmup_state, mask.shape[-1] * warmup_state['block_size'])[2]
 
 
 def _select_and_build(warmup_state: Dict, num_heads: int, seq_len: int, device, dark_map=None):
@@ -295,13 +318,9 @@ def _select_and_build(warmup_state: Dict, num_heads: int, seq_len: int, device, 
 
 
 def _embed_video_mask(warmup_state: Dict, video_mask: torch.Tensor, seq_len: int) -> torch.Tensor:
-    model_type = warmup_state['model_type']
-    if model_type == 'wan':
+    if warmup_state['model_type'] == 'wan':
         return video_mask
-    bs = warmup_state['block_size']
-    nb = seq_len // bs
-    n = video_mask.shape[-1]
-    off = warmup_state['text_token_num'] // bs if model_type == 'cogvideox' else 0
+    nb, n, off = _geometry(warmup_state, seq_len)
     mask = torch.ones(video_mask.shape[0], nb, nb, dtype=torch.bool, device=video_mask.device)
     mask[:, off:off + n, off:off + n] = video_mask
     return mask
@@ -345,6 +364,9 @@ def SparseAttentionWithMap(
     num_heads = query.size(1)
     block_size = warmup_state['block_size']
     video_token_num = warmup_state.get('video_token_num', 0)
+    # a kernel of an earlier call that gave up a bounded wait is reported here, one call late and without a
+    # synchronisation (every attention launch below queues an asynchronous copy of its status words)
+    _ops.check_posted_status(query.device)
 
     if use_dense or warmup_state['sparse_type'] == 'full':
         # 'full' is accepted by create_adaptive_mask_state but has no branch in the reference (:598-729); here it
@@ -392,6 +414,7 @@ def SparseAttentionWithMap(
                                          dark_map=warmup_state['prev_full_maps'])
             _store_mask(warmup_state, mask, seq_len)
             logger.info(f"Layer {layer_idx}, Mask Sparsity: {1 - warmup_state['mask'].float().mean():.3%}")
+            _ops.check_health(query.device)         # the two maps the first mask was fitted to are valid
         return output, warmup_state['mask']
 
     if warmup_state.get('mask', None) is None:
@@ -412,7 +435,7 @@ def SparseAttentionWithMap(
         warmup_state['features_history'].pop(0)
         next_mask = _select_and_build(warmup_state, num_heads, seq_len, query.device, dark_map=merged)
         _store_mask(warmup_state, next_mask, seq_len)
-        _ops.raise_on_status(query.device)          # one synchronising health check per refresh
+        _ops.check_health(query.device)             # one synchronising check per refresh (forward and replay map)
     else:
         output = AttentionSparseEngine(query, key, value, warmup_state['mask'], pre_defined_mask=pre_defined_mask,
                                        video_token_num=video_token_num, block_size=block_size,
@@ -481,7 +504,7 @@ def _spargeattn_step(query, key, value, warmup_state):
     warmup_state['mask'] = mask
     lists = _ops.tile_lists(mask, bs, seq_len)
     output = _ops.sparse_attn_fwd(query, key, value, lists.counts, lists.entries, order=lists.order,
-                                  check_status=False)
+                                  check_status="deferred")
     return output, {'mode': 'warmup', 'mask': None}
 
 

@@ -118,7 +118,7 @@ def dense_attention_with_lse(query, key, value, softmax_scale=None, kv_len=None)
     """Dense flash forward of (B,H,S,D) tensors; returns (O, LSE (B,H,S) float32 natural log)."""
     counts, entries = _dense_lists(query.device, query.shape[2])
     return _ops.sparse_attn_fwd(query, key, value, counts, entries, softmax_scale=softmax_scale,
-                                kv_len_lo=kv_len, kv_len_hi=kv_len, return_lse=True, check_status=False)
+                                kv_len_lo=kv_len, kv_len_hi=kv_len, return_lse=True, check_status="deferred")
 
 
 @torch.no_grad()

@@ -24,6 +24,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
@@ -77,16 +79,6 @@ __device__ __forceinline__ void report(int32_t* status, int code, int role, int 
     status[3] = where;
   }
 }
-
-#ifdef MODDIT_PROFILE
-// Experiment-only build: cycle totals per role, summed over all CTAs.
-__device__ unsigned long long g_prof[32];
-#define PROF_T() clock64()
-#define PROF_ADD(i, v) atomicAdd(&g_prof[i], static_cast<unsigned long long>(v))
-#else
-#define PROF_T() 0ll
-#define PROF_ADD(i, v) ((void)0)
-#endif
 
 template <bool kBF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -153,11 +145,14 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
 
-  // Register budget: the softmax warpgroups hold a 128-value row per thread, the control warps need little.
+  // Register budget: the softmax warpgroups hold a 128-value row per thread, the control warps need little
+  // (128 control threads give up what 256 softmax threads take: 168 -> 72 / 216 at D = 128 and 56 / 224 at
+  // D = 64, the splits that leave each instantiation without a single spill).
   // The control branch and the softmax branch are disjoint in the control-flow graph so that each gets
   // its own register allocation.
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  if constexpr (D == 128) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -234,15 +229,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
         }
       };
       // waits for the two half rows of P in turn; returns false if a wait gave up
-      auto pv_when_ready = [&](int x, int s, uint32_t acc, uint32_t parity, long long& waited) -> bool {
-        long long t = PROF_T();
+      auto pv_when_ready = [&](int x, int s, uint32_t acc, uint32_t parity) -> bool {
         if (!ptx::mbar_wait(bar(kPLoA + 2 * x), parity, abort_flag)) return false;
-        waited += PROF_T() - t;
         ptx::tc_fence_after();
         issue_pv_half(x, s, 0, acc);
-        t = PROF_T();
         if (!ptx::mbar_wait(bar(kPHiA + 2 * x), parity, abort_flag)) return false;
-        waited += PROF_T() - t;
         ptx::tc_fence_after();
         issue_pv_half(x, s, 1, 1u);
         return true;
@@ -262,8 +253,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
           ptx::tc_commit(bar(kEmpty1));     // K stage 0 is free for the K tile of entry 2 (loaded with V of entry 1)
         }
       }
-      long long pt_kv = 0, pt_p = 0, pt_qk = 0, pt_pv = 0;
-      const long long pt_begin = PROF_T();
       int fl_carry = (cnt > 0) ? (ent[0] & 0xff) : 0;
       for (int e = 0; e < cnt && ok; ++e) {
         const int s = e & 1;
@@ -271,49 +260,30 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
         const bool next = (e + 1) < cnt;
         const int fln = next ? (ent[e + 1] & 0xff) : 0;   // issued here, first used after the P V of tile A
         fl_carry = fln;
-        long long pt0 = PROF_T();
         ok = ptx::mbar_wait(bar(kFull0 + s), (e >> 1) & 1, abort_flag);
-        pt_kv += PROF_T() - pt0;
         if (!ok) { report(status, 2, 1, e); break; }
         if (fl & 0x0f) {
-          pt0 = PROF_T();
-          long long waited = 0;
-          ok = pv_when_ready(0, s, acc[0], par_p[0], waited);
-          pt_p += waited;
-          pt_pv += PROF_T() - pt0 - waited;
+          ok = pv_when_ready(0, s, acc[0], par_p[0]);
           if (!ok) { report(status, 3, 1, e); break; }
           par_p[0] ^= 1;
           acc[0] = 1;
         }
-        pt0 = PROF_T();
         if (fln & 0x0f) issue_qk(0, s ^ 1);
-        pt_qk += PROF_T() - pt0;
         if (fl & 0xf0) {
-          pt0 = PROF_T();
-          long long waited = 0;
-          ok = pv_when_ready(1, s, acc[1], par_p[1], waited);
-          pt_p += waited;
-          pt_pv += PROF_T() - pt0 - waited;
+          ok = pv_when_ready(1, s, acc[1], par_p[1]);
           if (!ok) { report(status, 3, 1, e); break; }
           par_p[1] ^= 1;
           acc[1] = 1;
         }
-        pt0 = PROF_T();
         if (fln & 0xf0) issue_qk(1, s ^ 1);
-        pt_qk += PROF_T() - pt0;
         ptx::tc_commit(bar(kEmpty0 + s));
       }
       ptx::tc_commit(bar(kOFinal));
-      PROF_ADD(0, PROF_T() - pt_begin);   // MMA loop total
-      PROF_ADD(1, pt_kv);                 // waiting for K/V tiles
-      PROF_ADD(2, pt_p);                  // waiting for P
-      PROF_ADD(3, cnt);
-      PROF_ADD(4, pt_qk);                 // issuing QK^T MMAs
-      PROF_ADD(5, pt_pv);                 // issuing PV MMAs
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    if constexpr (D == 128) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     // ------------------------------------------------------------------ softmax + epilogue
     const int x = (warp - 4) / 4;                 // 0: tile A, 1: tile B
     const int wq = warp % 4;                      // tensor-memory lane quarter of this warp
@@ -331,28 +301,21 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
     uint32_t par_s = 0;
     int done = 0;
     bool ok = true;
-    long long ps_wait = 0, ps_ld = 0, ps_comp = 0, ps_st = 0;
-    const long long ps_begin = PROF_T();
     for (int e = 0; e < cnt; ++e) {
       const int en = ent[e];
       const int sub = (en >> (4 * x)) & 0xf;
       if (!sub) continue;
       const int col0 = (en >> 8) * kTile;
-      const long long ps0 = PROF_T();
       ok = ptx::mbar_wait(bar(kSFullA + x), par_s, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report(status, 4, 2 + x, e); break; }
       par_s ^= 1;
       ptx::tc_fence_after();
-      const long long ps0b = PROF_T();
-      ps_wait += ps0b - ps0;
 
       float v[kTile];
 #pragma unroll
       for (int c = 0; c < 4; ++c) ptx::tmem_ld32(tS + c * 32, reinterpret_cast<uint32_t*>(v) + c * 32);
       ptx::tmem_ld_wait();
-      const long long ps1 = PROF_T();
-      ps_ld += ps1 - ps0b;
 
       if (sub != 0xf || col0 + kTile > kvl_min) {
         const int lim = kvl - col0;               // columns >= lim are beyond the valid keys
@@ -393,7 +356,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
           for (int i = 0; i < 32; ++i) o[i] *= alpha;
           ptx::tmem_st32(tO + c * 32, reinterpret_cast<const uint32_t*>(o));
         }
-        PROF_ADD(13 + 8 * x, lane == 0 && wq == 0 ? 1 : 0);
       }
       // P = exp2(S*scale - m), two fp32 lanes per instruction where the hardware has packed forms; each
       // half row is handed to the MMA warp as soon as it is stored, so P*V starts while the other half
@@ -425,20 +387,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
       ptx::unpack_f32x2(sum2b, s2, s3);
       const float sum = (s0 + s1) + (s2 + s3);
       l += sum;
-      const long long ps2 = PROF_T();
-      const long long ps3 = ps2;
-      ps_comp += ps2 - ps1;
-      ps_st += ps3 - ps2;
       ++done;
     }
 
     if (lane == 0 && wq == 0) {
-      PROF_ADD(8 + 8 * x, PROF_T() - ps_begin);   // softmax loop total (warp 0 of the group)
-      PROF_ADD(9 + 8 * x, ps_wait);               // waiting for S
-      PROF_ADD(10 + 8 * x, ps_ld);                // tensor-memory loads
-      PROF_ADD(11 + 8 * x, ps_comp);              // max / exp / pack / store issue
-      PROF_ADD(12 + 8 * x, ps_st);                // store completion + arrive
-      PROF_ADD(14 + 8 * x, done);
     }
     if (ok) {
       ok = ptx::mbar_wait(bar(kOFinal), 0, abort_flag);
@@ -507,7 +459,15 @@ int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N
   const int npairs = (ntq + 1) / 2;
   auto kernel = sparse_attn_fwd_kernel<D, kBF16>;
   const size_t smem = smem_bytes<D>();
-  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  // the shared-memory opt-in is a per-device property of the kernel: set once per device, not per call
+  static std::atomic<unsigned long long> opted_in{0};
+  int dev = 0;
+  MODDIT_CHECK_CUDA(cudaGetDevice(&dev));
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (dev >= 64 || !(opted_in.load(std::memory_order_acquire) & bit)) {
+    MODDIT_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    if (dev < 64) opted_in.fetch_or(bit, std::memory_order_release);
+  }
   const float scale_log2 = softmax_scale * 1.4426950408889634f;
   kernel<<<dim3(npairs * Hm, BH / Hm), kThreads, smem, st>>>(tq, tk, tv, counts, entries, order, Hm, ntq, N, scale_log2, q_split,
                                                    kvl_lo, kvl_hi, out, lse, status, scatter);
@@ -519,16 +479,6 @@ int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N
 }  // namespace moddit
 
 using namespace moddit;
-
-#ifdef MODDIT_PROFILE
-extern "C" int moddit_debug_profile(unsigned long long* host32) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(host32, g_prof, sizeof(unsigned long long) * 32);
-  unsigned long long zeros[32] = {};
-  cudaMemcpyToSymbol(g_prof, zeros, sizeof(zeros));
-  return 0;
-}
-#endif
 
 static int sparse_attn_dispatch(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
                                 const int32_t* counts, const int32_t* entries, const int32_t* order, int Hm,

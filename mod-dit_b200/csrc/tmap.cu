@@ -19,7 +19,28 @@ static void lookup_encode() {
   if (g_lookup_error == cudaSuccess && qres == cudaDriverEntryPointSuccess) g_encode = reinterpret_cast<EncodeFn>(fn);
 }
 
+// The descriptor is a pure function of these arguments, and a caller runs the same tensors through the same
+// kernels step after step: the last few encodings are kept per host thread (the driver call costs microseconds,
+// which is visible once a step is a few milliseconds long).
+namespace {
+struct CachedMap {
+  const void* base;
+  int dtype, BH, N, D, box_rows;
+  CUtensorMap map;
+};
+constexpr int kCachedMaps = 16;
+thread_local CachedMap t_maps[kCachedMaps];
+thread_local int t_maps_used = 0, t_maps_next = 0;
+}  // namespace
+
 int make_tmap_rows(CUtensorMap* map, const void* base, int dtype, int BH, int N, int D, int box_rows) {
+  for (int i = 0; i < t_maps_used; ++i) {
+    const CachedMap& c = t_maps[i];
+    if (c.base == base && c.dtype == dtype && c.BH == BH && c.N == N && c.D == D && c.box_rows == box_rows) {
+      *map = c.map;
+      return MODDIT_OK;
+    }
+  }
   std::call_once(g_once, lookup_encode);
   if (!g_encode) return fail(MODDIT_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver (%s)",
                              cudaGetErrorString(g_lookup_error));
@@ -32,6 +53,10 @@ int make_tmap_rows(CUtensorMap* map, const void* base, int dtype, int BH, int N,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (res != CUDA_SUCCESS) return fail(MODDIT_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(res));
+  CachedMap& slot = t_maps[t_maps_next];
+  slot = CachedMap{base, dtype, BH, N, D, box_rows, *map};
+  t_maps_next = (t_maps_next + 1) % kCachedMaps;
+  if (t_maps_used < kCachedMaps) ++t_maps_used;
   return MODDIT_OK;
 }
 

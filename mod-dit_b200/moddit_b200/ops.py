@@ -572,6 +572,7 @@ def copy_rows_multi(src_ptrs, dst_ptrs, src_pitch: int, dst_pitch: int, width_by
 # ---------------------------------------------------------------------------------------------
 
 _STATUS: Dict[int, torch.Tensor] = {}
+_POSTED: Dict[int, list] = {}        # device index -> [pinned int32[4] copy of the status words, event or None]
 
 
 def _status_words(dev: torch.device) -> torch.Tensor:
@@ -583,6 +584,12 @@ def _status_words(dev: torch.device) -> torch.Tensor:
     return st
 
 
+def _status_error(vals) -> "_lib.ModditError":
+    return _lib.ModditError(
+        f"sparse_attn_fwd: a bounded wait expired inside the kernel (code={vals[0]} block={vals[1]} "
+        f"role={vals[2]} position={vals[3]}); the output is invalid")
+
+
 def raise_on_status(device) -> None:
     """Synchronising check of the sparse forward's status words on `device`."""
     device = torch.device(device)
@@ -590,18 +597,71 @@ def raise_on_status(device) -> None:
     vals = st.tolist()
     if vals[0] != 0:
         st.zero_()
+        raise _status_error(vals)
+
+
+def post_status(device) -> None:
+    """Queues a copy of the status words into pinned host memory behind the work already on the current stream
+    and records an event after it.  Costs no synchronisation; `check_posted_status` looks at the copy later."""
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    slot = _POSTED.get(idx)
+    if slot is None:
+        slot = [torch.zeros(4, dtype=torch.int32).pin_memory(), None]
+        _POSTED[idx] = slot
+    if slot[1] is not None and not slot[1].query():
+        return                                   # the previous copy has not landed yet: it reports the same words
+    slot[0].copy_(_status_words(device), non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(device))
+    slot[1] = ev
+
+
+def check_posted_status(device) -> None:
+    """Looks at the last posted copy of the status words if it has arrived (never waits): raises ModditError when
+    a kernel launched before that copy gave up a bounded wait.  Called at the start of every attention-layer
+    call, so a fault surfaces one call later without a synchronisation per step."""
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    slot = _POSTED.get(idx)
+    if slot is None or slot[1] is None or not slot[1].query():
+        return
+    slot[1] = None
+    vals = slot[0].tolist()
+    if vals[0] != 0:
+        _status_words(device).zero_()
+        raise _status_error(vals)
+
+
+def check_health(device) -> None:
+    """Synchronising check of every kernel status this library keeps on `device` (sparse/dense forward and
+    replay map): for the end of a denoising step or of a run."""
+    device = torch.device(device)
+    raise_on_status(device)
+    vals = replay_status(device)
+    if vals[0] != 0:
         raise _lib.ModditError(
-            f"sparse_attn_fwd: a bounded wait expired inside the kernel (code={vals[0]} block={vals[1]} "
-            f"role={vals[2]} position={vals[3]}); the output is invalid")
+            f"replay_map: a bounded wait expired inside the kernel (code={vals[0]} block={vals[1]} role={vals[2]} "
+            f"position={vals[3]}); the sparsity maps written since the last check are invalid")
+
+
+def _after_launch(dev, check_status) -> None:
+    if check_status == "deferred":
+        post_status(dev)
+    elif check_status:
+        raise_on_status(dev)
 
 
 def sparse_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, counts: torch.Tensor,
                     entries: torch.Tensor, *, order: Optional[torch.Tensor] = None,
                     softmax_scale: Optional[float] = None,
                     q_split: Optional[int] = None, kv_len_lo: Optional[int] = None,
-                    kv_len_hi: Optional[int] = None, return_lse: bool = False, check_status: bool = True,
+                    kv_len_hi: Optional[int] = None, return_lse: bool = False, check_status=True,
                     out: Optional[torch.Tensor] = None, scatter=None):
-    """Block-sparse attention forward of (B,H,N,D) tensors over the work lists from `tile_lists`."""
+    """Block-sparse attention forward of (B,H,N,D) tensors over the work lists from `tile_lists`.
+
+    check_status: True reads the kernel's status words after the launch (synchronises); "deferred" queues an
+    asynchronous copy of them (`post_status`) for a later `check_posted_status`; False does neither."""
     dev = _need_cuda(q, k, v, counts, entries)
     _need_contig(q=q, k=k, v=v, counts=counts, entries=entries)
     if q.shape != k.shape or q.shape != v.shape or q.dtype != k.dtype or q.dtype != v.dtype:
@@ -628,8 +688,7 @@ def sparse_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, counts: t
                 scale, N if q_split is None else int(q_split), N if kv_len_lo is None else int(kv_len_lo),
                 N if kv_len_hi is None else int(kv_len_hi), table, len(peer_ptrs), int(head_base), _ptr(lse),
                 _ptr(st), _stream(dev)), "moddit_sparse_attn_fwd_scatter")
-        if check_status:
-            raise_on_status(dev)
+        _after_launch(dev, check_status)
         return (None, lse) if return_lse else None
     if out is None:
         out = torch.empty_like(q)
@@ -639,6 +698,5 @@ def sparse_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, counts: t
                                          N if kv_len_lo is None else int(kv_len_lo),
                                          N if kv_len_hi is None else int(kv_len_hi), _ptr(out), _ptr(lse),
                                          _ptr(st), _stream(dev)), "moddit_sparse_attn_fwd")
-    if check_status:
-        raise_on_status(dev)
+    _after_launch(dev, check_status)
     return (out, lse) if return_lse else out
