@@ -22,6 +22,14 @@ a head shard, the path runs on the local heads and the output goes back the same
 
 `--impl reference` times the reference's own CPU path for this hot path (the oracle port of it: the
 reference itself is Python that needs its checkout, which does not exist on the benchmark box).
+
+`--sweep mass|reference` runs the specification's step-adaptive sweep instead: 50 denoising steps at the
+workload's shape whose positional gain rises linearly from 0.2 to 1.0 of `--gain` (inputs regenerated per step
+from seed 4000 + step, outside the timed regions), every step timed on its own.  `mass`: mean-pooled producer
+and cumulative-mass selector every step, so the block sparsity follows the locality (about 60 % to 90 % with
+the defaults, `--sweep-tau 0.4 --gain 1.1`).  `reference`: the reference's own schedule (dense warm-up steps,
+exact replay map on the two collecting steps and on every predict_T-th step after them, top-k lines), which
+gives the amortised cost of its refresh steps.  The line carries per-step arrays in `sweep`.
 """
 from __future__ import annotations
 
@@ -129,14 +137,16 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
-def make_state(cfg, heads_local):
+def make_state(cfg, heads_local, warmup_steps=2, producer="pooled", selector="topk_lines", tau=0.9):
     from MoD.mod.state import create_adaptive_mask_state
     T, Hh, Ww = cfg["grid"]
     video = T * Hh * Ww
     state = create_adaptive_mask_state(cfg["model_type"], heads_local, video, cfg["text_tokens"], Hh * Ww, T,
-                                       warmup_steps=2, top_k=cfg["top_k"], predict_T=cfg["predict_T"],
+                                       warmup_steps=warmup_steps, top_k=cfg["top_k"], predict_T=cfg["predict_T"],
                                        threshold=1e-4, block_size=cfg["block_size"])
-    state["score_producer"] = "pooled"
+    state["score_producer"] = producer
+    state["selector"] = selector
+    state["mass_threshold"] = tau
     return state
 
 
@@ -144,105 +154,182 @@ def kept_flops(mask: torch.Tensor, block_size: int, head_dim: int) -> float:
     return float(mask.sum().item()) * 4.0 * block_size * block_size * head_dim
 
 
-def run_ours(args):
-    import torch.distributed as dist
-    from MoD.mod.attn_mask import SparseAttentionWithMap
-    from moddit_b200 import dist as mdist
-    from moddit_b200 import ops, synth
+def bind_to_gpu_numa_node(local_rank: int):
+    """Runs this process on the CPUs of the NUMA node its GPU hangs off, before any pinned buffer exists, so that
+    the pinned pages (first touched here) are local to the GPU's PCIe root.  Returns what it found, for the record."""
+    info = {"numa_node": None, "cpus": None}
+    try:
+        bus = torch.cuda.get_device_properties(local_rank).pci_bus_id
+        dom = torch.cuda.get_device_properties(local_rank).pci_domain_id
+        dev_id = torch.cuda.get_device_properties(local_rank).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev_id:02x}.0/numa_node"
+        with open(path) as fh:
+            node = int(fh.read().strip())
+        info["numa_node"] = node
+        if node >= 0:
+            with open(f"/sys/devices/system/node/node{node}/cpulist") as fh:
+                cpus = set()
+                for part in fh.read().strip().split(","):
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+            allowed = cpus & os.sched_getaffinity(0)
+            if allowed:
+                os.sched_setaffinity(0, allowed)
+                info["cpus"] = len(allowed)
+    except Exception as exc:            # sysfs layout differs or affinity is not ours to set: leave things as they are
+        info["error"] = repr(exc)[:120]
+    return info
 
-    world = int(os.environ.get("WORLD_SIZE", "1")) if args.gpus > 1 else 1
-    rank = int(os.environ.get("RANK", "0")) if world > 1 else 0
-    local_rank = int(os.environ.get("LOCAL_RANK", "0")) if world > 1 else 0
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    cfg = synth.WORKLOADS[args.workload]
-    H, D, bs = cfg["heads"], cfg["head_dim"], cfg["block_size"]
-    if H % world:
-        raise SystemExit(f"{H} heads do not divide over {world} GPUs")
-    hb, he = mdist.shard_bounds(H, world, rank)
-    logger = logging.getLogger("bench")
-    logger.setLevel(logging.WARNING)
 
-    q, k, v = synth.make_qkv(heads=H, grid=cfg["grid"], head_dim=D, text_tokens=cfg["text_tokens"],
-                             text_first=cfg["text_first"], seed=1, gain=args.gain, corr=1.0, device=dev,
-                             head_begin=hb, head_end=he)
-    N = q.shape[2]
-    if world > 1:
-        # what a sequence-parallel caller holds: its sequence shard of all heads
-        q_in, k_in, v_in = (mdist.head_to_seq(t) for t in (q, k, v))
-        del q, k, v
-    else:
-        q_in, k_in, v_in = q, k, v
-    state = make_state(cfg, he - hb)
+class Harness:
+    """What both the default run and the sweep need: ranks, the workload, the re-shard plumbing and one layer call."""
 
-    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
-    qk_stream = torch.cuda.Stream(device=dev) if world > 1 else None
-    resharder, value_group = None, None
-    reshard = "none"
-    if world > 1:
+    def __init__(self, args):
+        import torch.distributed as dist
+        from moddit_b200 import dist as mdist
+        from moddit_b200 import ops, synth
+        self.dist, self.mdist, self.ops, self.synth, self.args = dist, mdist, ops, synth, args
+        self.world = int(os.environ.get("WORLD_SIZE", "1")) if args.gpus > 1 else 1
+        self.rank = int(os.environ.get("RANK", "0")) if self.world > 1 else 0
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0")) if self.world > 1 else 0
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        self.numa = bind_to_gpu_numa_node(self.local_rank) if self.world > 1 else {"numa_node": None}
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.cfg = synth.WORKLOADS[args.workload]
+        self.H, self.D, self.bs = self.cfg["heads"], self.cfg["head_dim"], self.cfg["block_size"]
+        if self.H % self.world:
+            raise SystemExit(f"{self.H} heads do not divide over {self.world} GPUs")
+        self.hb, self.he = mdist.shard_bounds(self.H, self.world, self.rank)
+        self.gain = args.gain if args.gain is not None else self.cfg.get("gain", 2.0)
+        self.logger = logging.getLogger("bench")
+        self.logger.setLevel(logging.WARNING)
+        T, Hh, Ww = self.cfg["grid"]
+        self.N = T * Hh * Ww + self.cfg["text_tokens"]
+        self.comm_stream = torch.cuda.Stream(device=self.dev) if self.world > 1 else None
+        self.qk_stream = torch.cuda.Stream(device=self.dev) if self.world > 1 else None
+        self.resharder, self.value_group, self.reshard = None, None, "none"
+        if self.world > 1:
+            self._setup_resharder()
+
+    def _setup_resharder(self):
+        mdist, dist, dev = self.mdist, self.dist, self.dev
+        if self.N % self.world:
+            raise SystemExit(f"{self.N} tokens do not divide over {self.world} sequence shards")
         try:
-            resharder = mdist.PeerResharder(H, N, D, q_in.dtype, dev)
-            resharder.enable_pooling(bs)
-            reshard = "peer-memory copies (copy engines) + fused output scatter; query/key pooled on the sequence shards"
+            self.resharder = mdist.PeerResharder(self.H, self.N, self.D, torch.bfloat16, dev)
+            self.resharder.enable_pooling(self.bs)
+            self.reshard = ("peer-memory copies (copy engines) + fused output scatter; query/key pooled on the "
+                            "sequence shards")
             try:                   # one exchange up front: a box without peer DMA fails here, on every rank alike
-                resharder.seq_to_head(v_in, 2, channel=1)
+                probe = torch.zeros(1, self.H, self.N // self.world, self.D, device=dev, dtype=torch.bfloat16)
+                self.resharder.seq_to_head(probe, 2, channel=1)
                 torch.cuda.synchronize(dev)
             except RuntimeError as exc:
                 print(f"[bench] copy-engine peer copies unavailable ({exc!r}); using the copy kernel", file=sys.stderr)
-                resharder.bulk_copy = "kernel"
-                reshard = "peer-memory copies (copy kernel) + fused output scatter; query/key pooled on the sequence shards"
+                self.resharder.bulk_copy = "kernel"
+                self.reshard = ("peer-memory copies (copy kernel) + fused output scatter; query/key pooled on the "
+                                "sequence shards")
         except Exception as exc:   # symmetric memory unavailable on this box: NCCL all-to-all does the same exchange
             print(f"[bench] peer-memory re-shard unavailable ({exc!r}); using NCCL all-to-all", file=sys.stderr)
-            value_group = dist.new_group(backend="nccl")
-            reshard = "NCCL all-to-all"
+            self.resharder = None
+            self.value_group = dist.new_group(backend="nccl")
+            self.reshard = "NCCL all-to-all"
 
-    def layer(qs, ks, vs, step):
+    def inputs(self, seed, gain):
+        """What the caller of the layer holds: q, k, v of the local heads (one GPU) or its sequence shard of all
+        heads (several GPUs, as a sequence-parallel pipeline would)."""
+        q, k, v = self.synth.make_workload_qkv(self.args.workload, seed=seed, gain=gain, device=self.dev,
+                                               head_begin=self.hb, head_end=self.he)
+        if self.world > 1:
+            out = tuple(self.mdist.head_to_seq(t) for t in (q, k, v))
+            del q, k, v
+            return out
+        return q, k, v
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def layer(self, qs, ks, vs, step, state, use_dense=False):
+        from MoD.mod.attn_mask import SparseAttentionWithMap
+        world, dev, resharder, mdist = self.world, self.dev, self.resharder, self.mdist
         ready, scatter, qk_ready, pooled = None, None, None, None
+        pooled_mode = state.get("score_producer") == "pooled" and not use_dense
         if world > 1:
             main = torch.cuda.current_stream(dev)
-            comm_stream.wait_stream(main)
-            with torch.cuda.stream(comm_stream):
+            self.comm_stream.wait_stream(main)
+            with torch.cuda.stream(self.comm_stream):
                 # value is not needed until the attention kernel: it travels while the mask is predicted
                 vs_h = (resharder.seq_to_head(vs, 2, channel=1) if resharder is not None
-                        else mdist.seq_to_head(vs, group=value_group))
+                        else mdist.seq_to_head(vs, group=self.value_group))
                 ready = torch.cuda.Event()
-                ready.record(comm_stream)
+                ready.record(self.comm_stream)
             if resharder is not None:
                 # the mask needs only block means of query and key: they are pooled on the sequence shards and
                 # sent to the head owners, so the prediction runs while the rows themselves still travel
-                qk_stream.wait_stream(main)
-                with torch.cuda.stream(qk_stream):
+                self.qk_stream.wait_stream(main)
+                with torch.cuda.stream(self.qk_stream):
                     qh, kh = resharder.seq_to_head_many([qs, ks], [0, 1], channel=0)
                     qk_ready = torch.cuda.Event()
-                    qk_ready.record(qk_stream)
-                pooled = resharder.pool_to_head(qs, ks, channel=0)
+                    qk_ready.record(self.qk_stream)
+                if pooled_mode:
+                    pooled = resharder.pool_to_head(qs, ks, channel=0)
+                else:
+                    main.wait_event(qk_ready)
+                    qk_ready = None
                 qs, ks = qh, kh
                 scatter = resharder.begin_output(channel=0)
             else:
                 qs, ks = mdist.seq_to_head(qs), mdist.seq_to_head(ks)
             vs = vs_h
             vs.record_stream(main)
-        out, _ = SparseAttentionWithMap(qs, ks, vs, state, logger, current_step=step, value_ready=ready,
-                                        output_scatter=scatter, qk_ready=qk_ready, pooled_qk=pooled)
+        kw = {}
+        if pooled is not None or qk_ready is not None:
+            kw = dict(qk_ready=qk_ready, pooled_qk=pooled)
+        out, _ = SparseAttentionWithMap(qs, ks, vs, state, self.logger, current_step=step, value_ready=ready,
+                                        output_scatter=scatter, use_dense=use_dense, **kw)
         if world > 1:
             if resharder is None:
                 out = mdist.head_to_seq(out)
             else:
-                # sparse steps wrote their rows straight into the peers' buffers; dense (priming) steps did not
+                # sparse steps wrote their rows straight into the peers' buffers; dense steps did not
                 out = resharder.finish_output(channel=0) if out is None else resharder.head_to_seq(out, channel=0)
         return out
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    def reduce(self, maxed, summed):
+        vals = torch.tensor(maxed, device=self.dev, dtype=torch.float64)
+        sums = torch.tensor(summed, device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(vals, op=self.dist.ReduceOp.MAX)
+            self.dist.all_reduce(sums, op=self.dist.ReduceOp.SUM)
+        return vals.tolist(), sums.tolist()
+
+    def workload_string(self):
+        cfg = self.cfg
+        return (f"{self.args.workload}: B=1 H={self.H} D={self.D} N={self.N} block={self.bs} top_k={cfg['top_k']} "
+                f"pooled mask prediction every step")
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def run_ours(args):
+    hx = Harness(args)
+    ops, dev, world, rank = hx.ops, hx.dev, hx.world, hx.rank
+    cfg, H, D, bs, N = hx.cfg, hx.H, hx.D, hx.bs, hx.N
+    q_in, k_in, v_in = hx.inputs(1, hx.gain)
+    state = make_state(cfg, hx.he - hx.hb)
+    layer = lambda qs, ks, vs, step: hx.layer(qs, ks, vs, step, state)     # noqa: E731
+    barrier = hx.barrier
 
     # two untimed priming steps fill the feature history (the first one runs dense attention)
     for step in range(2):
         layer(q_in, k_in, v_in, step)
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(hx.local_rank)
     if rank == 0:
         sampler.start()               # running before the warm-up so that short timed regions still get samples
     for i in range(args.warmup):
@@ -250,34 +337,58 @@ def run_ours(args):
     ops.raise_on_status(dev)
 
     # ---- value: inputs resident in HBM ------------------------------------------------------------
-    barrier()
-    sampler.mark_begin()
-    # inside the timed region only the dominant kernel is bracketed by events (its launches feed the roofline)
+    # The timed region (exactly `steps` steps between a barrier + synchronize on both sides, maximum over ranks)
+    # is run `repeats` times back to back - as many as make about a second of work, so that short multi-GPU
+    # steps are not at the mercy of one scheduling hiccup and the clock sampler sees the load - and the median
+    # repeat is the reported one; minimum and maximum are printed beside it.
+    # Inside the timed regions only the dominant kernel is bracketed by events (its launches feed the roofline)
     # and every launch is counted; the per-stage breakdown comes from a few untimed steps afterwards, so that
-    # two event records per entry-point call do not load the host while short multi-GPU steps are timed
-    ops.stage_timing(True, only=("moddit_sparse_attn_fwd",))
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(args.steps):
-        layer(q_in, k_in, v_in, 2 + args.warmup + i)
-    ev1.record()
-    barrier()
+    # two event records per entry-point call do not load the host while short multi-GPU steps are timed.
+    step_no = 2 + args.warmup
+    repeat_ms, repeat_attn, launches = [], [], 0
+    repeats = 1
+    r = 0
+    sampler.mark_begin()
+    while r < repeats:
+        barrier()
+        ops.stage_timing(True, only=("moddit_sparse_attn_fwd",))
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(args.steps):
+            layer(q_in, k_in, v_in, step_no)
+            step_no += 1
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        attn = sum(t for _, t in ops.stage_records()) / args.steps
+        launches = ops.launches_recorded()
+        (ms_max, attn_max), _ = hx.reduce([ms, attn], [0.0])
+        repeat_ms.append(ms_max)
+        repeat_attn.append(attn_max)
+        if r == 0:
+            want = args.repeats if args.repeats > 0 else int(min(25, max(1, -(-1000.0 // max(ms_max, 1e-3)))))
+            repeats = max(1, want)
+        r += 1
     sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
-    total_ms = ev0.elapsed_time(ev1)
-    attn_ms = sum(ms for _, ms in ops.stage_records()) / args.steps
-    launches = ops.launches_recorded()
+    order = sorted(range(repeats), key=lambda i: repeat_ms[i])
+    mid = order[(repeats - 1) // 2]
+    total_ms, attn_ms = repeat_ms[mid], repeat_attn[mid]
     breakdown_steps = max(1, min(args.steps, 5))
+    # one more step goes first, unrecorded: its attention kernel keeps the GPU busy while the host enqueues the
+    # recorded steps, so that the events bracket kernels waiting in the queue and not the host's launch latency
+    layer(q_in, k_in, v_in, step_no)
     ops.stage_timing(True)
     for i in range(breakdown_steps):
-        layer(q_in, k_in, v_in, 2 + args.warmup + args.steps + i)
+        layer(q_in, k_in, v_in, step_no + 1 + i)
     records = ops.stage_records()
     ops.stage_timing(False)
-    ops.raise_on_status(dev)
+    ops.check_health(dev)
 
     mask = state["mask"]
     flops_local = kept_flops(mask, bs, D)
-    sparsity_local = 1.0 - float(mask.float().mean().item())
+    per_head = 1.0 - mask.float().mean(dim=(1, 2))
+    sparsity_local = float(per_head.mean().item())
     stage_ms = {}
     for name, ms in records:
         stage_ms[name] = stage_ms.get(name, 0.0) + ms
@@ -288,7 +399,7 @@ def run_ours(args):
 
     # ---- e2e: inputs in pinned host memory, output copied back ----------------------------------
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    e2e_ms, h2d, d2h = 0.0, 0, 0
+    e2e_ms, h2d, d2h, h2d_gbs, d2h_gbs = 0.0, 0, 0, 0.0, 0.0
     if not args.no_e2e:
         # Double-buffered pipeline, as a serving loop would run it: step i's inputs are copied host->device
         # on one stream while step i-1 computes on the main stream and step i-2's output is copied back on
@@ -305,6 +416,19 @@ def run_ours(args):
         out_done = [torch.cuda.Event() for _ in range(2)]
         for ev in in_free + out_done:
             ev.record(main)
+
+        # the two copy directions alone, all ranks at once (what the host side of this box gives each GPU)
+        barrier()
+        c0, c1, c2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        c0.record()
+        for d, h in zip(dev_in[0], host_in):
+            d.copy_(h, non_blocking=True)
+        c1.record()
+        host_out[0].copy_(dev_in[0][0], non_blocking=True)
+        c2.record()
+        barrier()
+        h2d_gbs = h2d / (c0.elapsed_time(c1) * 1e-3) / 1e9
+        d2h_gbs = d2h / (c1.elapsed_time(c2) * 1e-3) / 1e9
 
         def e2e_step(i, step):
             b = i % 2
@@ -348,14 +472,11 @@ def run_ours(args):
         prologue = time_prologue(ops, dev, H, D, N, cfg, bs)
 
     # ---- reduce over ranks ------------------------------------------------------------------------
-    vals = torch.tensor([total_ms, e2e_ms, attn_ms, pred_ms, comm_ms], device=dev, dtype=torch.float64)
-    sums = torch.tensor([flops_local, sparsity_local, float(launches), float(h2d), float(d2h)], device=dev,
-                        dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-    total_ms, e2e_ms, attn_ms, pred_ms, comm_ms = vals.tolist()
-    flops_total, sparsity_sum, launches_total, h2d_total, d2h_total = sums.tolist()
+    (e2e_ms, pred_ms, comm_ms, h2d_slow, d2h_slow, sp_max), sums = hx.reduce(
+        [e2e_ms, pred_ms, comm_ms, -h2d_gbs, -d2h_gbs, float(per_head.max().item())],
+        [flops_local, sparsity_local, float(launches), float(h2d), float(d2h), h2d_gbs, d2h_gbs])
+    (_, sp_min_neg), _ = hx.reduce([0.0, -float(per_head.min().item())], [0.0])
+    flops_total, sparsity_sum, launches_total, h2d_total, d2h_total, h2d_gbs_sum, d2h_gbs_sum = sums
 
     if rank == 0:
         peaks = load_peaks()
@@ -369,22 +490,29 @@ def run_ours(args):
                 "peak_source": f"of {peaks['_source']} (burst)", "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
                 "frac_of_sustained": round(achieved / float(peaks["bf16_tflops_sustained"]), 4),
                 "frac_of_nominal_2250": round(achieved / 2250.0, 4), "kernel_ms": round(attn_ms, 3),
-                "flops_per_launch": flops_local, "traffic": load_traffic(args.workload, (he - hb) / H)}
+                "flops_per_launch": flops_local, "traffic": load_traffic(args.workload, (hx.he - hx.hb) / H)}
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: B=1 H={H} D={D} N={N} block={bs} top_k={cfg['top_k']} "
-                                   f"pooled mask prediction every step",
-                       "sparsity": round(sparsity_sum / world, 4), "parallelism": f"head-sharded x{world}", "reshard": reshard,
-                       "l2": "inputs larger than L2", "gain": args.gain, "seed": 1},
+            "config": bench_config(args.workload, cfg, N, hx.gain, world),
+            "sparsity": round(sparsity_sum / world, 4),
+            "sparsity_per_head": {"min": round(-sp_min_neg, 4), "max": round(sp_max, 4)},
+            "reshard": hx.reshard,
+            "repeats": {"n": repeats, "reported": "median", "ms_per_step_min": round(min(repeat_ms) / args.steps, 3),
+                        "ms_per_step_max": round(max(repeat_ms) / args.steps, 3)},
             "mask_pred_ms": round(pred_ms, 3), "mask_pred_pct": round(100.0 * pred_ms / max(pred_ms + attn_ms, 1e-9), 2),
             "attn_ms": round(attn_ms, 3), "reshard_copy_ms": round(comm_ms, 3),
             "stage_ms_per_step": {n: round(ms / breakdown_steps, 4) for n, ms in sorted(stage_ms.items())},
             "clocks": clocks,
             "e2e": None if e2e_value is None else {
                 "value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms / e2e_steps, 3),
-                "steps": e2e_steps, "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total)},
+                "steps": e2e_steps, "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total),
+                "copy_only_gbs_per_rank": {"h2d_slowest": round(-h2d_slow, 1), "h2d_mean": round(h2d_gbs_sum / world, 1),
+                                           "d2h_slowest": round(-d2h_slow, 1), "d2h_mean": round(d2h_gbs_sum / world, 1),
+                                           "note": "all ranks copying at once, no compute; pinned buffers allocated "
+                                                   "after binding to the GPU's NUMA node"},
+                "numa": hx.numa},
             "gpu_launches": int(launches_total),
             "roofline": roof,
         }
@@ -394,10 +522,130 @@ def run_ours(args):
             prologue["frac"] = round(prologue["achieved"] / peak_gbs, 4)
             line["prologue"] = prologue
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(args.workload, args.gain, blocks=args.cpu_blocks)
+            line["cpu_baseline"] = cpu_baseline(args.workload, hx.gain, blocks=args.cpu_blocks)
         emit(line)
-    if world > 1:
-        dist.destroy_process_group()
+    hx.close()
+
+
+def bench_config(workload, cfg, N, gain, world):
+    """The `config` object both arms print: the workload, nothing that depends on which arm ran it."""
+    return {"workload": f"{workload}: B=1 H={cfg['heads']} D={cfg['head_dim']} N={N} block={cfg['block_size']} "
+                        f"top_k={cfg['top_k']} pooled mask prediction every step",
+            "parallelism": f"head-sharded x{world}", "l2": "inputs larger than L2", "gain": gain, "seed": 1}
+
+
+def run_sweep(args):
+    """The specification's step-adaptive sweep (see the module docstring)."""
+    hx = Harness(args)
+    ops, dev, world, rank, cfg = hx.ops, hx.dev, hx.world, hx.rank, hx.cfg
+    D, bs = hx.D, hx.bs
+    steps = args.sweep_steps
+    ref_mode = args.sweep == "reference"
+    warm = 12 if ref_mode else 1
+    state = make_state(cfg, hx.he - hx.hb, warmup_steps=max(warm, 2) if ref_mode else 2,
+                       producer="replay" if ref_mode else "pooled",
+                       selector="topk_lines" if ref_mode else "cumulative_mass", tau=args.sweep_tau)
+    predict_T = cfg["predict_T"]
+    sampler = ClockSampler(hx.local_rank)
+    if rank == 0:
+        sampler.start()
+    # untimed: load every kernel once (a dense call and, in mass mode, a predicted call on the first step's input)
+    g0 = hx.gain * 0.2
+    q_in, k_in, v_in = hx.inputs(4000, g0)
+    scratch = make_state(cfg, hx.he - hx.hb, producer=state["score_producer"], selector=state["selector"],
+                         tau=args.sweep_tau)
+    for s_ in range(3):
+        hx.layer(q_in, k_in, v_in, s_, scratch)
+    del scratch
+    ops.check_health(dev)
+    rows = []
+    sampler.mark_begin()
+    for step in range(steps):
+        frac = 0.2 + 0.8 * step / max(steps - 1, 1)
+        del q_in, k_in, v_in
+        q_in, k_in, v_in = hx.inputs(4000 + step, hx.gain * frac)
+        if ref_mode:
+            regime = ("dense" if step < warm - 2 else "collect" if step < warm else
+                      "refresh" if (step - warm) % predict_T == predict_T - 1 else "sparse")
+        else:
+            regime = "dense" if step == 0 else "sparse"      # the first call has no feature history yet
+        hx.barrier()
+        ops.stage_timing(True)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # A step is timed alone (its inputs are new), so the GPU would sit idle while the host enqueues the step's
+        # launches one by one and the events would measure the host.  A few milliseconds of busy-waiting on the
+        # device go first, untimed: the step's kernels queue up behind them as they would behind the previous
+        # layer of a running pipeline.
+        torch.cuda._sleep(int(args.sweep_lead_ms * 1.0e-3 * 1.5e9))
+        e0.record()
+        hx.layer(q_in, k_in, v_in, step, state, use_dense=(ref_mode and regime == "dense"))
+        e1.record()
+        hx.barrier()
+        ms = e0.elapsed_time(e1)
+        stage = {}
+        for name, t in ops.stage_records():
+            stage[name] = stage.get(name, 0.0) + t
+        ops.stage_timing(False)
+        attn = stage.get("moddit_sparse_attn_fwd", 0.0)
+        copies = stage.get("moddit_copy_rows", 0.0) + stage.get("moddit_copy_rows_dma", 0.0)
+        replay = stage.get("moddit_replay_map", 0.0)
+        pred = sum(stage.values()) - attn - copies
+        mask = state.get("mask")
+        if regime in ("dense", "collect", "refresh") or mask is None:
+            nb = -(-hx.N // bs)
+            flops = float(hx.he - hx.hb) * nb * nb * 4.0 * bs * bs * D       # these steps run dense attention
+            sparsity = 0.0
+        else:
+            flops = kept_flops(mask, bs, D)
+            sparsity = 1.0 - float(mask.float().mean().item())
+        (ms, attn, pred, replay), (flops, sparsity) = hx.reduce([ms, attn, pred, replay], [flops, sparsity])
+        rows.append(dict(step=step, gain=round(hx.gain * frac, 4), regime=regime, ms=round(ms, 3),
+                         sparsity=round(sparsity / world, 4), tflops=round(flops / (ms * 1e-3) / 1e12, 1),
+                         attn_ms=round(attn, 3), mask_pred_ms=round(pred, 3), replay_ms=round(replay, 3),
+                         mask_pred_pct=round(100.0 * pred / max(pred + attn, 1e-9), 2)))
+    sampler.mark_end()
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_health(dev)
+    if rank == 0:
+        def stats(key, pick):
+            vals = sorted(r_[key] for r_ in rows if pick(r_))
+            if not vals:
+                return None
+            return {"min": vals[0], "median": vals[len(vals) // 2], "max": vals[-1], "n": len(vals)}
+        sparse = lambda r_: r_["regime"] == "sparse"          # noqa: E731
+        total_ms = sum(r_["ms"] for r_ in rows)
+        kept_tf = sum(r_["tflops"] * r_["ms"] * 1e-3 for r_ in rows)
+        line = {
+            "metric": METRIC, "value": round(kept_tf / (total_ms * 1e-3), 2), "unit": "TFLOP/s", "n_gpus": world,
+            "steps": steps, "warmup": 3, "ms_per_step": round(total_ms / steps, 3), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload} sweep: B=1 H={hx.H} D={D} N={hx.N} block={bs}, {steps} steps, "
+                                   f"positional gain {hx.gain} x lerp(0.2, 1.0), seed 4000 + step",
+                       "mode": ("reference schedule: dense warm-up, exact replay map on collecting and refresh steps, "
+                                f"top_k={cfg['top_k']} lines, predict_T={predict_T}, warmup_steps={warm}") if ref_mode else
+                               f"mean-pooled producer + cumulative-mass selector (tau={args.sweep_tau}) every step",
+                       "parallelism": f"head-sharded x{world}", "l2": "inputs larger than L2 and regenerated per step"},
+            "reshard": hx.reshard, "clocks": clocks,
+            "sweep": {"total_ms": round(total_ms, 2),
+                      "sparse_steps": {"sparsity": stats("sparsity", sparse), "ms": stats("ms", sparse),
+                                       "tflops": stats("tflops", sparse), "mask_pred_pct": stats("mask_pred_pct", sparse),
+                                       "mask_pred_ms": stats("mask_pred_ms", sparse)},
+                      "ms_by_regime": {name: stats("ms", lambda r_, name=name: r_["regime"] == name)
+                                       for name in ("dense", "collect", "refresh", "sparse")},
+                      "per_step": {key: [r_[key] for r_ in rows] for key in
+                                   ("gain", "regime", "sparsity", "ms", "tflops", "mask_pred_pct", "attn_ms",
+                                    "mask_pred_ms", "replay_ms")}},
+        }
+        if ref_mode:
+            by = {name: [r_["ms"] for r_ in rows if r_["regime"] == name] for name in ("dense", "collect", "refresh", "sparse")}
+            mean = lambda xs: sum(xs) / len(xs) if xs else 0.0          # noqa: E731
+            after = [r_ for r_ in rows if r_["step"] >= warm]
+            line["sweep"]["after_warmup"] = {
+                "steps": len(after), "ms_per_step": round(mean([r_["ms"] for r_ in after]), 3),
+                "sparse_ms_mean": round(mean(by["sparse"]), 3), "refresh_ms_mean": round(mean(by["refresh"]), 3),
+                "refresh_share_of_time_pct": round(100.0 * sum(by["refresh"]) / max(sum(r_["ms"] for r_ in after), 1e-9), 2)}
+        emit(line)
+    hx.close()
 
 
 def time_prologue(ops, dev, H, D, N, cfg, bs, reps=10):
@@ -474,15 +722,12 @@ def cpu_sample(workload: str, gain: float, blocks: int):
     T, Hh, Ww = cfg["grid"]
     key = (workload, gain)
     if key not in _CPU_INPUTS:      # inputs are made once, outside every timed region
-        _CPU_INPUTS[key] = synth.make_qkv(heads=cfg["heads"], grid=cfg["grid"], head_dim=D,
-                                          text_tokens=cfg["text_tokens"], text_first=cfg["text_first"], seed=1,
-                                          gain=gain, device="cpu", dtype=torch.bfloat16, head_begin=0, head_end=1)
+        _CPU_INPUTS[key] = synth.make_workload_qkv(workload, seed=1, gain=gain, device="cpu", head_begin=0, head_end=1)
     q, k, v = _CPU_INPUTS[key]
     N = q.shape[2]
     video = T * Hh * Ww
-    n = video // bs
     bpf = (Hh * Ww) // bs
-    off = cfg["text_tokens"] // bs if cfg["text_first"] else 0
+    _, n, off = orc.block_geometry(cfg["model_type"], bs, video, cfg["text_tokens"], N)
     t0 = time.perf_counter()
     feats = []
     for rep in range(2):   # two feature sets are needed before a mask exists; both are part of the path
@@ -520,11 +765,12 @@ def run_reference(args):
         return
     torch.set_num_threads(os.cpu_count() or 1)
     cfg = _load_synth().WORKLOADS[args.workload]
+    gain = args.gain if args.gain is not None else cfg.get("gain", 2.0)
     for _ in range(args.warmup):
-        cpu_sample(args.workload, args.gain, 1)
+        cpu_sample(args.workload, gain, 1)
     tot_f, tot_s, desc = 0.0, 0.0, ""
     for _ in range(args.steps):
-        f, s, desc = cpu_sample(args.workload, args.gain, args.ref_blocks)
+        f, s, desc = cpu_sample(args.workload, gain, args.ref_blocks)
         tot_f += f
         tot_s += s
     value = tot_f / tot_s / 1e12
@@ -534,9 +780,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": round(value, 5), "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(tot_s / args.steps * 1e3, 2),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: B=1 H={cfg['heads']} D={cfg['head_dim']} N={N} "
-                               f"block={cfg['block_size']} top_k={cfg['top_k']} pooled mask prediction every step",
-                   "note": "each step is a bounded sample of the workload on the host cores"},
+        "config": bench_config(args.workload, cfg, N, gain, args.gpus),
+        "note": "each step is a bounded sample of the workload on the host cores (see cpu_baseline.sample)",
         "cpu_baseline": {"value": round(value, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": desc},
         "e2e": {"value": round(value, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -572,7 +817,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", default="hunyuan")
-    ap.add_argument("--gain", type=float, default=2.0, help="strength of the positional term of the synthetic q/k")
+    ap.add_argument("--gain", type=float, default=None,
+                    help="strength of the positional term of the synthetic q/k (default: the workload's, 2.0; 1.1 "
+                         "for --sweep mass)")
+    ap.add_argument("--repeats", type=int, default=0,
+                    help="how often the timed region runs (0: as often as makes about a second, at most 25)")
+    ap.add_argument("--sweep", choices=("mass", "reference"), default=None,
+                    help="run the 50-step locality sweep instead of the fixed-input benchmark")
+    ap.add_argument("--sweep-steps", type=int, default=50)
+    ap.add_argument("--sweep-lead-ms", type=float, default=6.0,
+                    help="device busy-wait before each timed sweep step, so that its launches are queued, not awaited")
+    ap.add_argument("--sweep-tau", type=float, default=0.4, help="cumulative-mass threshold of --sweep mass")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--cpu-blocks", type=int, default=480, help="query blocks in the cpu_baseline sample")
     ap.add_argument("--ref-blocks", type=int, default=32, help="query blocks per step of --impl reference")
@@ -593,6 +848,10 @@ def main():
         emit(rec)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.sweep:
+        if args.gain is None and args.sweep == "mass":
+            args.gain = 1.1
+        run_sweep(args)
     else:
         run_ours(args)
 

@@ -371,6 +371,8 @@ def SparseAttentionWithMap(
     if use_dense or warmup_state['sparse_type'] == 'full':
         # 'full' is accepted by create_adaptive_mask_state but has no branch in the reference (:598-729); here it
         # means what its name says: dense attention on every step
+        for ev in _events((kwargs.get('value_ready'), kwargs.get('qk_ready'))):   # inputs still arriving on other streams
+            torch.cuda.current_stream(query.device).wait_event(ev)
         query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
         valid = _valid_kv(pre_defined_mask, seq_len)
         output, _ = dense_attention_with_lse(query, key, value, kv_len=valid)

@@ -44,4 +44,9 @@ int require_sm100();
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Opt-in to `bytes` of dynamic shared memory for `kernel` on the current device.  The attribute is a per-device
+// property of the kernel: the driver call is made only when a launch needs more than any earlier one did, not
+// once per call.  Returns MODDIT_OK or a failure code (message set).
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 }  // namespace moddit

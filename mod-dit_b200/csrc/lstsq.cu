@@ -51,7 +51,6 @@ __global__ void __launch_bounds__(kMtsThreads) mts_partial_kernel(
     int64_t mask_head_stride, int64_t mask_row_stride, int mask_off, __half* __restrict__ merged, int n, int bpf,
     float* __restrict__ part_f, double* __restrict__ part_blk) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __half* tile = reinterpret_cast<__half*>(smem_raw);            // [kTileRows][n]
   __shared__ double red[32];
 
   const int h = blockIdx.y;
@@ -62,21 +61,19 @@ __global__ void __launch_bounds__(kMtsThreads) mts_partial_kernel(
   const int64_t span0 = (static_cast<int64_t>(h) * n + i0) * n;  // first element of the tile
   const int len = rows * n;
 
+  // The tile [kTileRows][n] starts `mis` halves into the buffer, `mis` being how far the tile's first element in
+  // global memory sits past a 16-byte boundary: 16-byte chunks of the source are then 16-byte chunks of the copy.
+  const __half* src = map + span0;
+  const int mis = static_cast<int>((reinterpret_cast<uintptr_t>(src) >> 1) & 7);
+  __half* tile = reinterpret_cast<__half*>(smem_raw) + mis;
   if (prev == nullptr) {
     // contiguous span of rows*n halves: scalar head until 16-byte aligned, 128-bit body, scalar tail
-    const __half* src = map + span0;
-    const int mis = static_cast<int>((reinterpret_cast<uintptr_t>(src) >> 1) & 7);
     const int head = min(len, (8 - mis) & 7);
     for (int e = tid; e < head; e += kMtsThreads) tile[e] = src[e];
     const int body = (len - head) / 8;
     const uint4* vsrc = reinterpret_cast<const uint4*>(src + head);
-    for (int e = tid; e < body; e += kMtsThreads) {
-      const uint4 v = __ldg(vsrc + e);
-      // shared destination is only 2-byte aligned in general: store as halves
-      const __half* hv = reinterpret_cast<const __half*>(&v);
-#pragma unroll
-      for (int u = 0; u < 8; ++u) tile[head + e * 8 + u] = hv[u];
-    }
+    uint4* vdst = reinterpret_cast<uint4*>(tile + head);
+    for (int e = tid; e < body; e += kMtsThreads) vdst[e] = __ldg(vsrc + e);
     for (int e = head + body * 8 + tid; e < len; e += kMtsThreads) tile[e] = src[e];
   } else {
     const uint8_t* kh = keep + static_cast<int64_t>(h) * mask_head_stride;
@@ -429,7 +426,7 @@ extern "C" int moddit_mts(const void* map_f16, const void* prev_f16, const uint8
     return fail(MODDIT_E_WORKSPACE, "mts: workspace of %zu bytes needed, got %zu", moddit_mts_workspace_bytes(H, n),
                 workspace_bytes);
   if (!aligned16(workspace)) return fail(MODDIT_E_ALIGN, "mts: workspace must be 16-byte aligned");
-  const size_t smem = static_cast<size_t>(kTileRows) * n * sizeof(__half);
+  const size_t smem = (static_cast<size_t>(kTileRows) * n + 8) * sizeof(__half);   // + the alignment shift
   if (smem > 200 * 1024) return fail(MODDIT_E_UNSUPPORTED, "mts: n=%d rows do not fit shared memory", n);
   if (int rc = require_sm100()) return rc;
   const int tiles = ceil_div(n, kTileRows);
@@ -437,8 +434,7 @@ extern "C" int moddit_mts(const void* map_f16, const void* prev_f16, const uint8
   float* part_f = static_cast<float*>(workspace);
   double* part_blk = reinterpret_cast<double*>(static_cast<unsigned char*>(workspace) + (f + 15) / 16 * 16);
   cudaStream_t st = as_stream(stream);
-  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(mts_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem)));
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(mts_partial_kernel), smem)) return rc;
   mts_partial_kernel<<<dim3(tiles, H), kMtsThreads, smem, st>>>(
       static_cast<const __half*>(map_f16), static_cast<const __half*>(prev_f16), keep_mask, mask_head_stride,
       mask_row_stride, mask_off, static_cast<__half*>(merged_out_f16), n, blocks_per_frame, part_f, part_blk);
@@ -471,7 +467,7 @@ extern "C" int moddit_mts_noalloc(const void* map_f16, int H, int n, int blocks_
                 "mts_noalloc: H=%d, n=%d needs %zu bytes of scratch but the built-in array holds %zu; use moddit_mts "
                 "with a caller-provided workspace",
                 H, n, need, kStaticScratchBytes);
-  const size_t smem = static_cast<size_t>(kTileRows) * n * sizeof(__half);
+  const size_t smem = (static_cast<size_t>(kTileRows) * n + 8) * sizeof(__half);   // + the alignment shift
   if (smem > 200 * 1024) return fail(MODDIT_E_UNSUPPORTED, "mts_noalloc: n=%d rows do not fit shared memory", n);
   if (int rc = require_sm100()) return rc;
   int dev = 0;
@@ -492,8 +488,7 @@ extern "C" int moddit_mts_noalloc(const void* map_f16, int H, int n, int blocks_
   float* part_f = static_cast<float*>(scratch);
   double* part_blk = reinterpret_cast<double*>(static_cast<unsigned char*>(scratch) + (f + 15) / 16 * 16);
   cudaStream_t st = as_stream(stream);
-  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(mts_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem)));
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(mts_partial_kernel), smem)) return rc;
   // every partial that the second kernel reads is written by the first, so nothing has to start at zero
   mts_partial_kernel<<<dim3(tiles, H), kMtsThreads, smem, st>>>(static_cast<const __half*>(map_f16), nullptr, nullptr,
                                                                  0, 0, 0, nullptr, n, blocks_per_frame, part_f,
@@ -627,8 +622,7 @@ extern "C" int moddit_solve(const float* mts, const void* factor, int H, int n, 
   cudaStream_t st = as_stream(stream);
   const size_t sm_rhs = sizeof(double) * ((2 * n - 1) + kSolveThreads);
   const size_t sm_back = sizeof(double) * (n + kSolveThreads);
-  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(solve_rhs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(sm_rhs)));
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(solve_rhs_kernel), sm_rhs)) return rc;
   solve_rhs_kernel<<<H, kSolveThreads, sm_rhs, st>>>(mts, w, wb, n, g);
   MODDIT_CHECK_LAUNCH("solve_rhs_kernel");
   solve_gemv_kernel<<<dim3(ceil_div(m, 128), H, kGemvSplit), 128, sizeof(double) * ceil_div(m, kGemvSplit), st>>>(

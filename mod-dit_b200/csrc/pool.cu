@@ -4,8 +4,8 @@
 // keeps eight fp32 column sums, row groups are combined through shared memory in a fixed order.
 // Algorithmic traffic: N*D*2 bytes read + ceil(N/bs)*D*4 bytes written per head.
 //
-// pooled_map: one CTA per (32 query blocks, head): fp32 logits against all key blocks (4x4 register
-// tiles, 128-bit shared-memory loads) are kept in shared memory, then each warp normalises its rows and
+// pooled_map: one CTA per (32 query blocks, head): fp32 logits against all key blocks (warp-level tensor-core
+// products of the means split into two bfloat16 terms) are kept in shared memory, then each warp normalises its rows and
 // writes 1 - exp(logit - row maximum) as float16 (0 at the brightest block of a row, 1 where there is nothing;
 // relative to the row maximum so that the float16 grid resolves the bright blocks).
 #include <cuda_bf16.h>
@@ -223,22 +223,51 @@ constexpr int kMapThreads = 256;
 constexpr int kMapRows = 32;    // query blocks per CTA
 constexpr int kMapCols = 128;   // key blocks per staged tile
 
-// Every thread owns a 4 x 4 patch of the 32 x 128 logit tile and walks the head dimension four floats at
-// a time with 128-bit shared-memory loads (rows padded by four floats: conflict-free for the key tile,
-// broadcast for the query rows).
+// Logits on the tensor cores (warp-level mma.sync m16n8k16: the contraction is 5 GFLOP at the largest shape, far too
+// small to pay for a tcgen05 pipeline).  The float32 block means are split into two bfloat16 terms, x = hi + lo,
+// and a product is hi*hi + hi*lo + lo*hi with float32 accumulation: 16 mantissa bits per factor, a relative error
+// of about 2^-16 per product, well inside the float16 grid of the map.  Both operands sit in shared memory as
+// bfloat16 rows padded by 16 bytes (ldmatrix reads eight rows of 16 bytes at a time: odd multiples of 16 bytes
+// between rows keep them on different banks).  Warp w owns key columns [16w, 16w+16) of every staged key tile for
+// all 32 query rows of the CTA.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// four floats -> their bfloat16 heads and the bfloat16 of what the heads leave over
+__device__ __forceinline__ void split4(const float4& v, uint2& hi, uint2& lo) {
+  const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+  const float2 f0 = __bfloat1622float2(h0), f1 = __bfloat1622float2(h1);
+  const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - f0.x, v.y - f0.y);
+  const __nv_bfloat162 l1 = __floats2bfloat162_rn(v.z - f1.x, v.w - f1.y);
+  hi = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+  lo = make_uint2(*reinterpret_cast<const uint32_t*>(&l0), *reinterpret_cast<const uint32_t*>(&l1));
+}
+
 __global__ void __launch_bounds__(kMapThreads) pooled_map_kernel(const float* __restrict__ qbar,
                                                                  const float* __restrict__ kbar, int nb, int D,
                                                                  int q_off, int k_off, int n, float scale,
                                                                  __half* __restrict__ map) {
-  extern __shared__ __align__(16) float smem[];
-  const int ld = D + 4;
-  float* qs = smem;                             // [kMapRows][ld]
-  float* ks = qs + kMapRows * ld;               // [kMapCols][ld]
-  float* lg = ks + kMapCols * ld;               // [kMapRows][n]
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int ld = D + 8;                          // bfloat16 elements per staged row (16 bytes of padding)
+  __nv_bfloat16* qhi = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [kMapRows][ld]
+  __nv_bfloat16* qlo = qhi + kMapRows * ld;
+  __nv_bfloat16* khi = qlo + kMapRows * ld;                              // [kMapCols][ld]
+  __nv_bfloat16* klo = khi + kMapCols * ld;
+  float* lg = reinterpret_cast<float*>(klo + kMapCols * ld);             // [kMapRows][n]
 
   const int bh = blockIdx.y;
   const int i0 = blockIdx.x * kMapRows;
   const int tid = threadIdx.x;
+  const int warp = tid / 32, lane = tid % 32;
   const float* qh = qbar + (static_cast<int64_t>(bh) * nb + q_off) * D;
   const float* kh = kbar + (static_cast<int64_t>(bh) * nb + k_off) * D;
   const int d4 = D / 4;
@@ -248,51 +277,69 @@ __global__ void __launch_bounds__(kMapThreads) pooled_map_kernel(const float* __
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i0 + r < n) v = __ldg(reinterpret_cast<const float4*>(qh + static_cast<int64_t>(i0 + r) * D) + c);
     v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
-    *reinterpret_cast<float4*>(qs + r * ld + 4 * c) = v;
+    uint2 hi, lo;
+    split4(v, hi, lo);
+    *reinterpret_cast<uint2*>(qhi + r * ld + 4 * c) = hi;
+    *reinterpret_cast<uint2*>(qlo + r * ld + 4 * c) = lo;
   }
-  const int tc = tid % 32;                      // columns tc, tc+32, tc+64, tc+96 of the tile
-  const int tr = tid / 32;                      // rows 4*tr .. 4*tr+3
+  // ldmatrix addresses of this lane: A = 16 x 16 tile of the query rows (matrices: rows 0-7 / 8-15 x k 0-7 / 8-15),
+  // B = two 8-column tiles of the key rows x 16 k (matrices: (tile 0, k 0-7), (tile 0, k 8-15), (tile 1, ...))
+  const uint32_t a_off = static_cast<uint32_t>(((lane % 16) * ld + (lane / 16) * 8) * 2);
+  const uint32_t b_off = static_cast<uint32_t>(((16 * warp + (lane / 16) * 8 + (lane % 8)) * ld + ((lane / 8) % 2) * 8) * 2);
+  const uint32_t s_qhi = static_cast<uint32_t>(__cvta_generic_to_shared(qhi));
+  const uint32_t s_qlo = static_cast<uint32_t>(__cvta_generic_to_shared(qlo));
+  const uint32_t s_khi = static_cast<uint32_t>(__cvta_generic_to_shared(khi));
+  const uint32_t s_klo = static_cast<uint32_t>(__cvta_generic_to_shared(klo));
+  const int g = lane / 4, t2 = 2 * (lane % 4);
   for (int j0 = 0; j0 < n; j0 += kMapCols) {
     __syncthreads();
     for (int e = tid; e < kMapCols * d4; e += kMapThreads) {
       const int r = e / d4, c = e - r * d4;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (j0 + r < n) v = __ldg(reinterpret_cast<const float4*>(kh + static_cast<int64_t>(j0 + r) * D) + c);
-      *reinterpret_cast<float4*>(ks + r * ld + 4 * c) = v;
+      uint2 hi, lo;
+      split4(v, hi, lo);
+      *reinterpret_cast<uint2*>(khi + r * ld + 4 * c) = hi;
+      *reinterpret_cast<uint2*>(klo + r * ld + 4 * c) = lo;
     }
     __syncthreads();
-    float acc[4][4];
+    float acc[2][2][4];
 #pragma unroll
-    for (int a = 0; a < 4; ++a)
+    for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
-    for (int d = 0; d < D; d += 4) {
-      float4 qv[4], kv[4];
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int a = 0; a < 4; ++a) qv[a] = *reinterpret_cast<const float4*>(qs + (4 * tr + a) * ld + d);
+        for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t bh_[4], bl_[4];
+      ldmatrix_x4(bh_, s_khi + b_off + ks * 32);
+      ldmatrix_x4(bl_, s_klo + b_off + ks * 32);
 #pragma unroll
-      for (int b = 0; b < 4; ++b) kv[b] = *reinterpret_cast<const float4*>(ks + (tc + 32 * b) * ld + d);
+      for (int mt = 0; mt < 2; ++mt) {
+        uint32_t ah[4], al[4];
+        ldmatrix_x4(ah, s_qhi + a_off + (mt * 16 * ld + ks * 16) * 2);
+        ldmatrix_x4(al, s_qlo + a_off + (mt * 16 * ld + ks * 16) * 2);
 #pragma unroll
-      for (int a = 0; a < 4; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          acc[a][b] = fmaf(qv[a].x, kv[b].x, acc[a][b]);
-          acc[a][b] = fmaf(qv[a].y, kv[b].y, acc[a][b]);
-          acc[a][b] = fmaf(qv[a].z, kv[b].z, acc[a][b]);
-          acc[a][b] = fmaf(qv[a].w, kv[b].w, acc[a][b]);
+        for (int nt = 0; nt < 2; ++nt) {
+          mma_bf16(acc[mt][nt], al, bh_[2 * nt], bh_[2 * nt + 1]);      // small terms first
+          mma_bf16(acc[mt][nt], ah, bl_[2 * nt], bl_[2 * nt + 1]);
+          mma_bf16(acc[mt][nt], ah, bh_[2 * nt], bh_[2 * nt + 1]);
         }
-    }
-#pragma unroll
-    for (int a = 0; a < 4; ++a)
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const int j = j0 + tc + 32 * b;
-        if (j < n) lg[(4 * tr + a) * n + j] = acc[a][b];
       }
+    }
+    // accumulator element i of a 16 x 8 tile: row g + 8 * (i / 2), column t2 + (i % 2)
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int j = j0 + 16 * warp + 8 * nt + t2 + (i % 2);
+          if (j < n) lg[(mt * 16 + g + 8 * (i / 2)) * n + j] = acc[mt][nt][i];
+        }
   }
   __syncthreads();
   // per row: darkness = 1 - exp(logit - row maximum); warp w handles rows w, w+8, ...
-  const int warp = tid / 32, lane = tid % 32;
   for (int r = warp; r < kMapRows; r += kMapThreads / 32) {
     const int i = i0 + r;
     if (i >= n) break;
@@ -307,7 +354,8 @@ __global__ void __launch_bounds__(kMapThreads) pooled_map_kernel(const float* __
 }
 
 size_t pooled_map_smem(int D, int n) {
-  return sizeof(float) * (static_cast<size_t>(kMapRows + kMapCols) * (D + 4) + static_cast<size_t>(kMapRows) * n);
+  return sizeof(__nv_bfloat16) * (static_cast<size_t>(2 * (kMapRows + kMapCols)) * (D + 8)) +
+         sizeof(float) * static_cast<size_t>(kMapRows) * n;
 }
 
 }  // namespace
@@ -422,12 +470,11 @@ extern "C" int moddit_pooled_map(const float* qbar, const float* kbar, int BH, i
   cudaStream_t st = as_stream(stream);
   __half* map = static_cast<__half*>(map_f16);
   const size_t sm = pooled_map_smem(D, n);
-  if ((D & 3) != 0 || !aligned16(qbar) || !aligned16(kbar))
-    return fail(MODDIT_E_ALIGN, "pooled_map: head_dim must be a multiple of 4 and the inputs 16-byte aligned");
+  if ((D & 15) != 0 || !aligned16(qbar) || !aligned16(kbar))
+    return fail(MODDIT_E_ALIGN, "pooled_map: head_dim must be a multiple of 16 and the inputs 16-byte aligned");
   if (sm > 227 * 1024)
     return fail(MODDIT_E_UNSUPPORTED, "pooled_map: n=%d video blocks do not fit the shared-memory row buffer", n);
-  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(pooled_map_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(sm)));
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(pooled_map_kernel), sm)) return rc;
   pooled_map_kernel<<<dim3(ceil_div(n, kMapRows), BH), kMapThreads, sm, st>>>(qbar, kbar, nb, D, q_block_offset,
                                                                                k_block_offset, n, scale, map);
   MODDIT_CHECK_LAUNCH("pooled_map_kernel");

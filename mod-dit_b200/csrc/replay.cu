@@ -275,7 +275,7 @@ int launch(const void* q, const void* k, const float* lse, int dtype, int BH, in
   const size_t smem = fixed_smem_bytes<D>() + static_cast<size_t>(ntk) * 4 * sizeof(int);
   if (smem > 227 * 1024) return fail(MODDIT_E_UNSUPPORTED, "replay_map: %d key tiles do not fit the shared-memory counters", ntk);
   auto kernel = replay_map_kernel<D, kBF16>;
-  MODDIT_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
   kernel<<<dim3(ntk, BH), kThreads, smem, st>>>(tq, tk, lse, N, bs, scale, log_thr, q_off, k_off, n,
                                                 static_cast<__half*>(map), status);
   MODDIT_CHECK_LAUNCH("replay_map_kernel");

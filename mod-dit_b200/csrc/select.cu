@@ -15,19 +15,24 @@ __device__ __forceinline__ uint32_t order_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-constexpr int kSelectThreads = 256;
+constexpr int kSelectThreads = 1024;
 
-// ceil(L / 256) CTAs per head.  Every CTA builds all keys[] in shared memory and ranks its own slice of
-// the elements: the rank of element i is the number of elements that sort before it under (key, index);
-// ranks < k are written to selected[h][rank].
+// One CTA per head: the L = 3n - 1 extrapolated line intensities become 64-bit keys (value order << 32 | index),
+// padded to a power of two P with all-ones keys, and are bitonic-sorted ascending in shared memory; the first k
+// of the order are the selection (smallest value first, equal values lowest index first - the same total order
+// as ranking every element against every other, at L log^2 L instead of L^2 compares).
 __global__ void __launch_bounds__(kSelectThreads) select_lines_kernel(
     const float* __restrict__ cur_c, const float* __restrict__ cur_d, const float* __restrict__ last_c,
-    const float* __restrict__ last_d, int n, int k, float predict_T, int64_t* __restrict__ selected) {
-  extern __shared__ uint32_t keys[];
-  const int h = blockIdx.y;
+    const float* __restrict__ last_d, int n, int k, int P, float predict_T, int64_t* __restrict__ selected) {
+  extern __shared__ __align__(8) unsigned long long sort_keys[];
+  const int h = blockIdx.x;
   const int nd = 2 * n - 1;
   const int L = n + nd;
-  for (int i = threadIdx.x; i < L; i += kSelectThreads) {
+  for (int i = threadIdx.x; i < P; i += kSelectThreads) {
+    if (i >= L) {
+      sort_keys[i] = ~0ull;
+      continue;
+    }
     float cur, last;
     if (i < n) {
       cur = cur_c[static_cast<int64_t>(h) * n + i];
@@ -38,24 +43,26 @@ __global__ void __launch_bounds__(kSelectThreads) select_lines_kernel(
     }
     // cur + (cur - last) / predict_T with IEEE operations in this order (no contraction)
     const float pred = __fadd_rn(cur, __fdiv_rn(__fsub_rn(cur, last), predict_T));
-    keys[i] = order_key(pred);
+    sort_keys[i] = (static_cast<unsigned long long>(order_key(pred)) << 32) | static_cast<uint32_t>(i);
   }
   __syncthreads();
-  for (int i = blockIdx.x * kSelectThreads + threadIdx.x; i < L; i += gridDim.x * kSelectThreads) {
-    const uint32_t ki = keys[i];
-    int rank = 0;
-    int j = 0;
-    for (; j + 3 < L; j += 4) {          // four independent compares per iteration
-      const uint32_t k0 = keys[j], k1 = keys[j + 1], k2 = keys[j + 2], k3 = keys[j + 3];
-      rank += ((k0 < ki) || (k0 == ki && j < i)) + ((k1 < ki) || (k1 == ki && j + 1 < i)) +
-              ((k2 < ki) || (k2 == ki && j + 2 < i)) + ((k3 < ki) || (k3 == ki && j + 3 < i));
+  for (int size = 2; size <= P; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < P / 2; t += kSelectThreads) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi = lo + stride;
+        const bool up = ((lo & size) == 0);
+        const unsigned long long a = sort_keys[lo], b = sort_keys[hi];
+        if ((a > b) == up) {
+          sort_keys[lo] = b;
+          sort_keys[hi] = a;
+        }
+      }
+      __syncthreads();
     }
-    for (; j < L; ++j) {
-      const uint32_t kj = keys[j];
-      rank += (kj < ki) || (kj == ki && j < i);
-    }
-    if (rank < k) selected[static_cast<int64_t>(h) * k + rank] = i;
   }
+  for (int r = threadIdx.x; r < k; r += kSelectThreads)
+    selected[static_cast<int64_t>(h) * k + r] = static_cast<int64_t>(static_cast<uint32_t>(sort_keys[r]));
 }
 
 __global__ void head_modes_kernel(const float* __restrict__ b_d, int H, float threshold, int32_t* __restrict__ modes) {
@@ -63,10 +70,12 @@ __global__ void head_modes_kernel(const float* __restrict__ b_d, int H, float th
   if (h < H) modes[h] = (b_d[h] <= threshold) ? MODDIT_MODE_BLOCK_DIAGONAL : MODDIT_MODE_SPARSE;
 }
 
-constexpr int kMaskRows = 8;
+constexpr int kMaskRows = 32;
 constexpr int kMaskThreads = 256;
 
-// One CTA per (8 mask rows, head): flags of selected columns / diagonals are rebuilt in shared memory.
+// One CTA per (32 mask rows, head): flags of selected columns / diagonals are rebuilt in shared memory, then every
+// thread decides two neighbouring blocks of a row at a time and stores them together (rows start on even
+// addresses when the row length is even; odd lengths fall back to single bytes).
 __global__ void __launch_bounds__(kMaskThreads) mask_from_lines_kernel(
     const int64_t* __restrict__ selected, int k, const int32_t* __restrict__ modes, int n, int bpf, int voff, int nbt,
     uint8_t* __restrict__ mask) {
@@ -82,20 +91,25 @@ __global__ void __launch_bounds__(kMaskThreads) mask_from_lines_kernel(
     if (idx >= 0 && idx < 3 * n - 1) flags[idx] = 1;   // [0,n): column; n + (offset + n - 1): diagonal
   }
   __syncthreads();
+  auto kept = [&](int i, bool text_row, int C) -> bool {
+    const int j = C - voff;
+    if (text_row || j < 0 || j >= n || mode == MODDIT_MODE_FULL) return true;
+    return col_sel[j] || off_sel[j - i + n - 1] || (mode == MODDIT_MODE_BLOCK_DIAGONAL && (i / bpf) == (j / bpf));
+  };
+  const bool pairs = (nbt & 1) == 0;
   for (int rr = 0; rr < kMaskRows; ++rr) {
     const int R = blockIdx.x * kMaskRows + rr;
     if (R >= nbt) break;
     const int i = R - voff;
     uint8_t* dst = mask + (static_cast<int64_t>(h) * nbt + R) * nbt;
     const bool text_row = (i < 0 || i >= n);
-    for (int C = threadIdx.x; C < nbt; C += kMaskThreads) {
-      const int j = C - voff;
-      bool keep = text_row || j < 0 || j >= n || mode == MODDIT_MODE_FULL;
-      if (!keep) {
-        keep = col_sel[j] || off_sel[j - i + n - 1] ||
-               (mode == MODDIT_MODE_BLOCK_DIAGONAL && (i / bpf) == (j / bpf));
+    if (pairs) {
+      for (int C = 2 * threadIdx.x; C < nbt; C += 2 * kMaskThreads) {
+        const uint16_t two = static_cast<uint16_t>((kept(i, text_row, C) ? 1u : 0u) | (kept(i, text_row, C + 1) ? 0x100u : 0u));
+        *reinterpret_cast<uint16_t*>(dst + C) = two;
       }
-      dst[C] = keep ? 1 : 0;
+    } else {
+      for (int C = threadIdx.x; C < nbt; C += kMaskThreads) dst[C] = kept(i, text_row, C) ? 1 : 0;
     }
   }
 }
@@ -189,23 +203,22 @@ __global__ void __launch_bounds__(kMassThreads) select_mass_kernel(const __half*
 // ---- work lists ---------------------------------------------------------------------------------
 constexpr int kListThreads = 256;
 
-// One CTA per (pair of 128-row query tiles, mask head); ordered compaction with ballots.
+// One warp per (pair of 128-row query tiles, mask head): the warp walks the key tiles 32 at a time, a ballot
+// marks the tiles some sub-block of the pair keeps, and every kept tile is written at its running position (the
+// list stays in increasing key-tile order).  No shared memory, no block-wide synchronisation.
 __global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t* __restrict__ mask, int nbq, int nbk,
                                                                   int sub, int ntq, int ntk, int kv_block_limit,
-                                                                  int32_t* __restrict__ counts,
+                                                                  int npairs, int32_t* __restrict__ counts,
                                                                   int32_t* __restrict__ entries) {
-  __shared__ int warp_tot[kListThreads / 32];
-  __shared__ int base_s;
-  const int p = blockIdx.x, h = blockIdx.y;
-  const int npairs = gridDim.x;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int p = blockIdx.x * (kListThreads / 32) + warp, h = blockIdx.y;
+  if (p >= npairs) return;
   const uint8_t* mh = mask + static_cast<int64_t>(h) * nbq * nbk;
   int32_t* out = entries + (static_cast<int64_t>(h) * npairs + p) * ntk;
   const int lim = min(nbk, kv_block_limit);
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  if (threadIdx.x == 0) base_s = 0;
-  __syncthreads();
-  for (int t0 = 0; t0 < ntk; t0 += kListThreads) {
-    const int t = t0 + threadIdx.x;
+  int base = 0;
+  for (int t0 = 0; t0 < ntk; t0 += 32) {
+    const int t = t0 + lane;
     int fl = 0;
     if (t < ntk) {
       for (int x = 0; x < 2; ++x) {
@@ -220,20 +233,10 @@ __global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t*
       }
     }
     const unsigned bal = __ballot_sync(0xffffffffu, fl != 0);
-    if (lane == 0) warp_tot[warp] = __popc(bal);
-    __syncthreads();
-    int off = base_s;
-    for (int wv = 0; wv < warp; ++wv) off += warp_tot[wv];
-    if (fl) out[off + __popc(bal & ((1u << lane) - 1))] = (t << 8) | fl;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int s = 0;
-      for (int wv = 0; wv < kListThreads / 32; ++wv) s += warp_tot[wv];
-      base_s += s;
-    }
-    __syncthreads();
+    if (fl) out[base + __popc(bal & ((1u << lane) - 1))] = (t << 8) | fl;
+    base += __popc(bal);
   }
-  if (threadIdx.x == 0) counts[static_cast<int64_t>(h) * npairs + p] = base_s;
+  if (lane == 0) counts[static_cast<int64_t>(h) * npairs + p] = base;
 }
 
 // Start order of the (head, query-tile pair) work items of the sparse forward: order[pos] = head * npairs + pair.
@@ -336,9 +339,12 @@ extern "C" int moddit_select_lines(const float* cur_c, const float* cur_d, const
   if (int rc = require_sm100()) return rc;
   const int L = 3 * n - 1;
   const int k = top_k < L ? top_k : L;
-  const int split = ceil_div(L, kSelectThreads);     // one element per thread
-  select_lines_kernel<<<dim3(split, H), kSelectThreads, sizeof(uint32_t) * L, as_stream(stream)>>>(cur_c, cur_d, last_c, last_d, n,
-                                                                                      k, predict_T, selected);
+  int P = 2;
+  while (P < L) P <<= 1;
+  const size_t smem = sizeof(unsigned long long) * P;     // at most 128 KB (n <= 4096)
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(select_lines_kernel), smem)) return rc;
+  select_lines_kernel<<<H, kSelectThreads, smem, as_stream(stream)>>>(cur_c, cur_d, last_c, last_d, n, k, P, predict_T,
+                                                                      selected);
   MODDIT_CHECK_LAUNCH("select_lines_kernel");
   return MODDIT_OK;
 }
@@ -422,8 +428,8 @@ extern "C" int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, 
   if (ntq >= (1 << 23)) return fail(MODDIT_E_UNSUPPORTED, "tile_lists: N=%d too large", N);
   if (int rc = require_sm100()) return rc;
   const int npairs = (ntq + 1) / 2;
-  tile_lists_kernel<<<dim3(npairs, Hm), kListThreads, 0, as_stream(stream)>>>(mask, nbq, nbk, 128 / block_size, ntq,
-                                                                              ntq, kv_block_limit, counts, entries);
+  tile_lists_kernel<<<dim3(ceil_div(npairs, kListThreads / 32), Hm), kListThreads, 0, as_stream(stream)>>>(
+      mask, nbq, nbk, 128 / block_size, ntq, ntq, kv_block_limit, npairs, counts, entries);
   MODDIT_CHECK_LAUNCH("tile_lists_kernel");
   if (order != nullptr) {
     order_pairs_kernel<<<Hm, 256, sizeof(int32_t) * npairs, as_stream(stream)>>>(counts, npairs, order);

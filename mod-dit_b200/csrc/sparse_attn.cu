@@ -24,8 +24,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include <atomic>
-
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
@@ -459,15 +457,7 @@ int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N
   const int npairs = (ntq + 1) / 2;
   auto kernel = sparse_attn_fwd_kernel<D, kBF16>;
   const size_t smem = smem_bytes<D>();
-  // the shared-memory opt-in is a per-device property of the kernel: set once per device, not per call
-  static std::atomic<unsigned long long> opted_in{0};
-  int dev = 0;
-  MODDIT_CHECK_CUDA(cudaGetDevice(&dev));
-  const unsigned long long bit = 1ull << (dev & 63);
-  if (dev >= 64 || !(opted_in.load(std::memory_order_acquire) & bit)) {
-    MODDIT_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    if (dev < 64) opted_in.fetch_or(bit, std::memory_order_release);
-  }
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
   const float scale_log2 = softmax_scale * 1.4426950408889634f;
   kernel<<<dim3(npairs * Hm, BH / Hm), kThreads, smem, st>>>(tq, tk, tv, counts, entries, order, Hm, ntq, N, scale_log2, q_split,
                                                    kvl_lo, kvl_hi, out, lse, status, scatter);

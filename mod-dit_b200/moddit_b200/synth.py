@@ -86,6 +86,16 @@ def make_qkv(*, heads: int, grid: Tuple[int, int, int], head_dim: int, text_toke
     return q, k, v
 
 
+def make_workload_qkv(name: str, *, seed: int = 1, gain: Optional[float] = None, device="cuda",
+                      dtype=torch.bfloat16, head_begin: int = 0, head_end: Optional[int] = None):
+    """q, k, v of the named entry of WORKLOADS (its grid, text layout, per-head mixture and positional gain)."""
+    cfg = WORKLOADS[name]
+    return make_qkv(heads=cfg["heads"], grid=cfg["grid"], head_dim=cfg["head_dim"], text_tokens=cfg["text_tokens"],
+                    text_first=cfg["text_first"], seed=seed, gain=cfg.get("gain", 2.0) if gain is None else gain,
+                    corr=1.0, axis_mix=cfg.get("axis_mix"), device=device, dtype=dtype, head_begin=head_begin,
+                    head_end=head_end)
+
+
 WORKLOADS = {
     # name: model_type, heads, head_dim, block, grid (T,Hh,Ww), text tokens, text first, top_k, predict_T
     "hunyuan": dict(model_type="hunyuan", heads=24, head_dim=128, block_size=128, grid=(30, 48, 80),

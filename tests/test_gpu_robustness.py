@@ -102,3 +102,58 @@ def test_nvtx_ranges_can_be_switched_on(ops):
         assert torch.equal(ops.pool_blocks(x, 128), want)
     finally:
         ops.nvtx_ranges(False)
+
+
+@pytest.mark.parametrize("mode", ["pooled", "replay", "radial", "spargeattn", "full", "use_dense"])
+def test_an_expired_wait_is_reported_by_the_next_call_in_every_mode(ops, mode):
+    """A kernel that gives up a bounded wait leaves a code in the device's status words.  No kernel is made to
+    fail here: the test writes the words itself, as such a kernel would have, behind one healthy call; the next
+    call of the state machine - whatever the mode - must raise, and the call after that must run again."""
+    from MoD.mod.attn_mask import SparseAttentionWithMap
+    from MoD.mod.state import create_adaptive_mask_state
+    from moddit_b200._lib import ModditError
+    q, k, v = _inputs(H=2, grid=(4, 16, 16), D=128, text=0, seed=13)
+    video = q.shape[2]
+    sparse_type = mode if mode in ("radial", "spargeattn", "full") else "mod-dit"
+    state = create_adaptive_mask_state("wan", 2, video, 0, 256, 4, warmup_steps=2, top_k=4, predict_T=3, block_size=128,
+                                       sparse_type=sparse_type)
+    if mode == "pooled":
+        state["score_producer"] = "pooled"
+    kw = dict(use_dense=True) if mode == "use_dense" else {}
+    dev = q.device
+    ops.check_health(dev)
+    for step in range(3):                                   # healthy calls: priming steps and one later step
+        SparseAttentionWithMap(q, k, v, state, LOG, current_step=step, **kw)
+    torch.cuda.synchronize(dev)
+    ops.check_posted_status(dev)                            # nothing to report
+    ops._status_words(dev).copy_(torch.tensor([3, 17, 1, 5], dtype=torch.int32))
+    SparseAttentionWithMap(q, k, v, state, LOG, current_step=3, **kw)     # its launch posts the words
+    torch.cuda.synchronize(dev)
+    with pytest.raises(ModditError, match="bounded wait expired.*code=3 block=17 role=1 position=5"):
+        SparseAttentionWithMap(q, k, v, state, LOG, current_step=4, **kw)
+    assert ops._status_words(dev).tolist() == [0, 0, 0, 0]  # cleared: the caller may carry on
+    SparseAttentionWithMap(q, k, v, state, LOG, current_step=4, **kw)
+    torch.cuda.synchronize(dev)
+    ops.check_health(dev)
+
+
+def test_all_true_stand_in_mask_uses_exactly_the_valid_keys(ops):
+    """A mask of another shape stands for "keep everything" (the dense steps pass one): like the reference's dense
+    branch (MoD/mod/attn_mask.py:268-276) every row then sees exactly the valid keys, not the 64-rounded border."""
+    from MoD.mod.attn_mask import AttentionSparseEngine
+    from oracle import moddit_oracle as orc
+    g = torch.Generator(device="cuda").manual_seed(17)       # plain noise: every key matters to every query
+    q, k, v = (torch.randn(1, 2, 640, 128, device="cuda", generator=g).bfloat16() for _ in range(3))
+    S, video = q.shape[2], 512
+    valid = video + 37                                      # not a multiple of 64
+    pdm = (torch.arange(S, device="cuda") < valid).unsqueeze(0).expand(S, S).contiguous()
+    stand_in = torch.ones(2, 4, 4, device="cuda", dtype=torch.bool)       # video-region shape, not the sequence's
+    out = AttentionSparseEngine(q, k, v, stand_in, pre_defined_mask=pdm, video_token_num=video, block_size=128)
+    nb = S // 128
+    ref = orc.masked_attention(q.cpu(), k.cpu(), v.cpu(), torch.ones(1, nb, nb, dtype=torch.bool), 128,
+                               q_split=video, kv_len_lo=valid, kv_len_hi=valid)
+    assert (out.float().cpu() - ref).abs().max().item() <= 2e-2
+    rounded = orc.masked_attention(q.cpu(), k.cpu(), v.cpu(), torch.ones(1, nb, nb, dtype=torch.bool), 128,
+                                   q_split=video, kv_len_lo=(valid + 63) // 64 * 64, kv_len_hi=valid)
+    assert (ref - rounded).abs().max().item() > 1e-3        # the two rules do differ on this input
+    assert (out.float().cpu() - ref).abs().max().item() < (out.float().cpu() - rounded).abs().max().item()
