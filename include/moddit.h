@@ -91,6 +91,17 @@ int moddit_replay_map(const void* q, const void* k, const float* lse, int dtype,
                       int block_size, float softmax_scale, float log_threshold, int q_video_offset,
                       int k_video_offset, int video_blocks, void* map_f16, void* stream);
 
+/* The same map through a second, independently written kernel (warp-level mma.sync products from register
+ * fragments; no TMA, no tensor memory, no waits, hence no status words).  Same arguments and result definition as
+ * moddit_replay_map; the two differ only by the order of float32 additions inside a dot product, i.e. in a few
+ * comparisons within rounding of the threshold.  It stands where the reference has a second kernel for the same
+ * job, the Triton `_sparsity_kernel` behind `_triton_sparsity_map` (MoD/mod/triton_flash_sparsity.py:28-98,181-225),
+ * so that the reference test which checks one replay kernel against the other (tests/test_flash_sparsity.py:61-104)
+ * still compares two code paths. */
+int moddit_replay_map_mma(const void* q, const void* k, const float* lse, int dtype, int BH, int N, int D,
+                          int block_size, float softmax_scale, float log_threshold, int q_video_offset,
+                          int k_video_offset, int video_blocks, void* map_f16, void* stream);
+
 /* Reads and clears the status words of the replay kernel on the current device (code, block, role,
  * position; all zero unless a bounded wait inside the kernel expired, in which case the maps written
  * since the last call are invalid).  Synchronises `stream`.  No reference counterpart: the reference
@@ -125,7 +136,11 @@ int moddit_mts(const void* map_f16, const void* prev_f16, const uint8_t* keep_ma
  *   - sizes whose scratch need, moddit_mts_workspace_bytes(H, n), exceeds the array are refused with
  *     MODDIT_E_UNSUPPORTED (HunyuanVideo's H=24, n=900 needs 5.1 MB and fits);
  *   - the call allocates and frees nothing.  The first call on each device looks up the array's device
- *     address (cudaGetSymbolAddress); make that first call outside any stream capture;
+ *     address (cudaGetSymbolAddress); make that first call outside any stream capture.  With the CUDA
+ *     runtime's default lazy module loading, that first call is also when the driver loads this part of the
+ *     library onto the device and sets the 8 MiB aside: in a process whose framework takes all remaining
+ *     device memory, make one warm-up call at start-up, before the framework does (or run with
+ *     CUDA_MODULE_LOADING=EAGER, which moves the reservation to library load);
  *   - all calls on a device share the one array and it keeps the last call's contents.  Nothing in it
  *     has to start at zero (each call overwrites what it later reads), but two calls whose kernels can
  *     overlap on the GPU (different streams without an ordering between them) race on it.

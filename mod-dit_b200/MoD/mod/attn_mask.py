@@ -555,3 +555,101 @@ def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, curr
                                    _lists=warmup_state['_tile_lists'][1], _value_ready=(value_ready, qk_ready),
                                    _scatter=output_scatter)
     return output, {'mask': mask}
+
+
+# ------------------------------------------------------------------------------------------------
+# both classifier-free-guidance branches in one call
+# ------------------------------------------------------------------------------------------------
+
+_CFG_CONFIG_KEYS = ('model_type', 'num_heads', 'video_token_num', 'text_token_num', 'blocks_per_frame', 'frame_size',
+                    'num_frames', 'warmup_steps', 'top_k', 'threshold', 'block_size', 'predict_T', 'sparse_type')
+_CFG_OPTION_KEYS = ('score_producer', 'selector', 'mass_threshold', 'spargeattn_topk', 'spargeattn_sim_threshold')
+
+
+def _cat_heads(parts):
+    if any(p is None for p in parts):
+        return None
+    return torch.cat(list(parts), dim=0)
+
+
+def _merge_branch_states(states) -> Dict:
+    """One state over the heads of all branches (branch b owns heads [b*H, (b+1)*H)), from states that may
+    already have run some steps on their own."""
+    first = states[0]
+    for st in states[1:]:
+        for key in _CFG_CONFIG_KEYS + _CFG_OPTION_KEYS:
+            if st.get(key) != first.get(key):
+                raise ValueError(f"the branches' states differ in '{key}': {first.get(key)!r} vs {st.get(key)!r}")
+        if st.get('current_steps') != first.get('current_steps'):
+            raise ValueError("the branches' states are at different steps")
+    merged = {key: first[key] for key in first if not key.startswith('_')}
+    merged['num_heads'] = first['num_heads'] * len(states)
+    hist = [st.get('features_history') for st in states]
+    if all(h for h in hist):
+        merged['features_history'] = [{key: torch.cat([h[i][key] for h in hist], dim=0) for key in hist[0][i]}
+                                      for i in range(len(hist[0]))]
+    else:
+        merged['features_history'] = None if first.get('features_history') is None else []
+    merged['prev_full_maps'] = _cat_heads([st.get('prev_full_maps') for st in states])
+    merged['mask'] = _cat_heads([st.get('mask') for st in states])
+    modes = [st.get('mode') for st in states]
+    if all(m is not None for m in modes):
+        merged['mode'] = (torch.cat(list(modes)) if torch.is_tensor(modes[0]) else [x for m in modes for x in m])
+    else:
+        merged.pop('mode', None)
+    return merged
+
+
+def _share_out_branch_states(merged: Dict, states) -> None:
+    """Every branch's state dict sees its own heads of the merged state (views: nothing is copied)."""
+    nb = len(states)
+    H = merged['num_heads'] // nb
+    for b, st in enumerate(states):
+        lo, hi = b * H, (b + 1) * H
+        st['current_steps'] = merged.get('current_steps', st.get('current_steps'))
+        hist = merged.get('features_history')
+        st['features_history'] = hist if not hist else [{key: f[key][lo:hi] for key in f} for f in hist]
+        for key in ('prev_full_maps', 'mask'):
+            val = merged.get(key)
+            st[key] = None if val is None else (val if val.shape[0] == 1 else val[lo:hi])
+        if 'mode' in merged:
+            st['mode'] = merged['mode'][lo:hi]
+        st.pop('_tile_lists', None)
+
+
+def SparseAttentionWithMapCFG(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, warmup_states,
+                              logger: logging.Logger, pre_defined_mask: Optional[torch.Tensor] = None,
+                              current_step: int = 0, layer_idx: int = 0, use_dense: bool = False, **kwargs):
+    """Both guidance branches of a layer in one call: `query`, `key`, `value` are (P, H, S, D) with one branch per
+    batch item and `warmup_states` holds the P per-branch state dicts.
+
+    The reference's Wan and CogVideoX processors call `SparseAttentionWithMap` once per branch, each with its own
+    state (MoD/models/wan/attention_processor.py:144-169, MoD/models/cogvideox/attention_processor.py:185-202).
+    Every stage of the path is independent per head, so the branches are run here as P*H heads of one problem:
+    one launch of every kernel (the sparse forward walks P*H work lists), one merged state kept under
+    `warmup_states[0]['_cfg_merged']`, and after the call every branch's dict shows its own heads of it (mask,
+    features, maps) as views.  Output and masks equal those of P separate calls bit for bit.
+    Returns (output (P, H, S, D), mask info of the merged state).
+    """
+    states = list(warmup_states)
+    P = len(states)
+    if query.dim() != 4 or query.shape[0] != P:
+        raise ValueError(f"expected (P={P}, H, S, D) tensors, one batch item per state")
+    if pre_defined_mask is not None:
+        raise ValueError("the two-branch form has no padded-text rule (no model with guidance branches passes one)")
+    H = query.shape[1]
+    if H != states[0]['num_heads']:
+        raise ValueError(f"{H} heads against a state built for {states[0]['num_heads']}")
+    merged = states[0].get('_cfg_merged')
+    if merged is None:
+        merged = _merge_branch_states(states)
+        states[0]['_cfg_merged'] = merged
+
+    def fold(t):
+        t = t.contiguous()
+        return t.view(1, P * H, t.shape[2], t.shape[3])
+
+    out, info = SparseAttentionWithMap(fold(query), fold(key), fold(value), merged, logger, None, current_step,
+                                       layer_idx, use_dense, **kwargs)
+    _share_out_branch_states(merged, states)
+    return out.view(P, H, out.shape[2], out.shape[3]), info

@@ -77,16 +77,20 @@ def _validate_inputs(query, key, value, threshold, block_size, model_type, video
 
 def _triton_sparsity_map(query, key, lse, *, softmax_scale, log_threshold, q_video_offset, k_video_offset,
                          video_blocks, block_size) -> torch.Tensor:
-    """Kept for callers of the reference's Triton entry point; runs the same sm_100a replay kernel."""
+    """The reference's second replay kernel (Triton, :28-98,181-225).  Nothing here uses Triton: the name runs
+    this library's second, independently written replay kernel (warp-level mma.sync products from registers, no
+    TMA and no tensor memory), so a caller that checks one replay path against the other - the reference's own test
+    does - still compares two implementations."""
     return _ops.replay_map(query, key, lse, softmax_scale=float(softmax_scale), log_threshold=float(log_threshold),
                            q_video_offset=int(q_video_offset), k_video_offset=int(k_video_offset),
-                           video_blocks=int(video_blocks), block_size=int(block_size))
+                           video_blocks=int(video_blocks), block_size=int(block_size), kernel="mma")
 
 
 def _compute_sparsity_map(query, key, lse, *, softmax_scale, log_threshold, q_video_offset, k_video_offset,
                           video_blocks, block_size) -> torch.Tensor:
-    """Validates MOD_DIT_SPARSITY_BACKEND as the reference does (auto | cuda | triton); every accepted
-    value runs the one sm_100a kernel, and an unsupported device is an error rather than a fallback."""
+    """Validates MOD_DIT_SPARSITY_BACKEND as the reference does (auto | cuda | triton).  `auto` and `cuda` run the
+    tcgen05 replay kernel, `triton` the second, independently written one (there is no Triton here); an unsupported
+    device is an error rather than a fallback."""
     backend = os.environ.get("MOD_DIT_SPARSITY_BACKEND", "auto").lower()
     if backend not in {"auto", "cuda", "triton"}:
         raise ValueError("MOD_DIT_SPARSITY_BACKEND must be one of: auto, cuda, triton")

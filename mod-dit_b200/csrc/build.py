@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 OUT_DIR = os.path.join(os.path.dirname(HERE), "moddit_b200")
 LIB = os.path.join(OUT_DIR, "libmoddit.so")
-SOURCES = ["api.cu", "tmap.cu", "pool.cu", "prologue.cu", "lstsq.cu", "select.cu", "replay.cu", "sparse_attn.cu"]
+SOURCES = ["api.cu", "tmap.cu", "pool.cu", "prologue.cu", "lstsq.cu", "select.cu", "replay.cu", "replay_mma.cu", "sparse_attn.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", HERE,

@@ -73,43 +73,49 @@ __global__ void head_modes_kernel(const float* __restrict__ b_d, int H, float th
 constexpr int kMaskRows = 32;
 constexpr int kMaskThreads = 256;
 
-// One CTA per (32 mask rows, head): flags of selected columns / diagonals are rebuilt in shared memory, then every
-// thread decides two neighbouring blocks of a row at a time and stores them together (rows start on even
-// addresses when the row length is even; odd lengths fall back to single bytes).
+// One CTA per (32 mask rows, head).  Shared memory holds, per video column, one byte "column selected" and the
+// column's frame index (so the per-frame block-diagonal test is a compare, not a division per element), and one
+// byte per diagonal offset.  Every thread decides two neighbouring blocks of a row at a time and stores them
+// together (rows start on even addresses when the row length is even; odd lengths fall back to single bytes).
 __global__ void __launch_bounds__(kMaskThreads) mask_from_lines_kernel(
     const int64_t* __restrict__ selected, int k, const int32_t* __restrict__ modes, int n, int bpf, int voff, int nbt,
     uint8_t* __restrict__ mask) {
-  extern __shared__ uint8_t flags[];   // [n] columns | [2n-1] diagonals
+  extern __shared__ __align__(4) uint8_t flags[];   // [n] columns | [2n-1] diagonals | pad | [n] frame (uint16)
   uint8_t* col_sel = flags;
   uint8_t* off_sel = flags + n;
+  uint16_t* frame = reinterpret_cast<uint16_t*>(flags + ((3 * n - 1 + 3) & ~3));
   const int h = blockIdx.y;
   const int mode = modes[h];
+  const bool frames_on = (mode == MODDIT_MODE_BLOCK_DIAGONAL);
   for (int i = threadIdx.x; i < 3 * n - 1; i += kMaskThreads) flags[i] = 0;
+  // with the per-frame test off every column gets a frame no row has
+  for (int j = threadIdx.x; j < n; j += kMaskThreads) frame[j] = frames_on ? static_cast<uint16_t>(j / bpf) : 0xffffu;
   __syncthreads();
   for (int t = threadIdx.x; t < k; t += kMaskThreads) {
     const int64_t idx = selected[static_cast<int64_t>(h) * k + t];
     if (idx >= 0 && idx < 3 * n - 1) flags[idx] = 1;   // [0,n): column; n + (offset + n - 1): diagonal
   }
   __syncthreads();
-  auto kept = [&](int i, bool text_row, int C) -> bool {
-    const int j = C - voff;
-    if (text_row || j < 0 || j >= n || mode == MODDIT_MODE_FULL) return true;
-    return col_sel[j] || off_sel[j - i + n - 1] || (mode == MODDIT_MODE_BLOCK_DIAGONAL && (i / bpf) == (j / bpf));
-  };
+  const bool all = (mode == MODDIT_MODE_FULL);
   const bool pairs = (nbt & 1) == 0;
   for (int rr = 0; rr < kMaskRows; ++rr) {
     const int R = blockIdx.x * kMaskRows + rr;
     if (R >= nbt) break;
     const int i = R - voff;
     uint8_t* dst = mask + (static_cast<int64_t>(h) * nbt + R) * nbt;
-    const bool text_row = (i < 0 || i >= n);
+    const bool whole_row = all || i < 0 || i >= n;              // text rows and 'full' heads keep everything
+    const uint16_t fi = (frames_on && !whole_row) ? static_cast<uint16_t>(i / bpf) : 0xfffeu;
+    const uint8_t* diag = off_sel + (n - 1 - i);               // diag[j] = flag of offset j - i
+    auto kept = [&](int C) -> uint32_t {
+      const int j = C - voff;
+      if (whole_row || j < 0 || j >= n) return 1u;
+      return (col_sel[j] | diag[j] | (frame[j] == fi ? 1 : 0)) ? 1u : 0u;
+    };
     if (pairs) {
-      for (int C = 2 * threadIdx.x; C < nbt; C += 2 * kMaskThreads) {
-        const uint16_t two = static_cast<uint16_t>((kept(i, text_row, C) ? 1u : 0u) | (kept(i, text_row, C + 1) ? 0x100u : 0u));
-        *reinterpret_cast<uint16_t*>(dst + C) = two;
-      }
+      for (int C = 2 * threadIdx.x; C < nbt; C += 2 * kMaskThreads)
+        *reinterpret_cast<uint16_t*>(dst + C) = static_cast<uint16_t>(kept(C) | (kept(C + 1) << 8));
     } else {
-      for (int C = threadIdx.x; C < nbt; C += kMaskThreads) dst[C] = kept(i, text_row, C) ? 1 : 0;
+      for (int C = threadIdx.x; C < nbt; C += kMaskThreads) dst[C] = static_cast<uint8_t>(kept(C));
     }
   }
 }
@@ -378,7 +384,8 @@ extern "C" int moddit_mask_from_lines(const int64_t* selected, int k, const int3
     return fail(MODDIT_E_ARG, "mask_from_lines: unknown layout %d", layout);
   }
   if (int rc = require_sm100()) return rc;
-  mask_from_lines_kernel<<<dim3(ceil_div(nbt, kMaskRows), H), kMaskThreads, 3 * n, as_stream(stream)>>>(
+  const size_t smem = static_cast<size_t>((3 * n - 1 + 3) & ~3) + sizeof(uint16_t) * n;
+  mask_from_lines_kernel<<<dim3(ceil_div(nbt, kMaskRows), H), kMaskThreads, smem, as_stream(stream)>>>(
       selected, k, modes, n, blocks_per_frame, voff, nbt, mask);
   MODDIT_CHECK_LAUNCH("mask_from_lines_kernel");
   return MODDIT_OK;

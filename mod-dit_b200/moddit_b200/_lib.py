@@ -36,6 +36,8 @@ SIGNATURES = {
                                   c_void_p, c_void_p]),
     "moddit_replay_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_float, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "moddit_replay_map_mma": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                      c_float, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moddit_replay_status": (c_int, [c_void_p, c_void_p]),
     "moddit_mts_workspace_bytes": (c_size_t, [c_int, c_int]),
     "moddit_mts": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_int, c_int, c_int,

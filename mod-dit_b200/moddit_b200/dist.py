@@ -147,6 +147,8 @@ class PeerResharder:
     guarantees that all ranks have finished reading the previous contents.
     """
 
+    COPY_STREAMS = 4      # side streams the copy-engine pieces of one exchange are spread over
+
     def __init__(self, heads: int, seq_len: int, head_dim: int, dtype: torch.dtype, device: torch.device,
                  group: Optional[dist.ProcessGroup] = None, n_inputs: int = 3, timeout_ms: int = 20000,
                  bulk_copy: str = "dma"):
@@ -166,6 +168,7 @@ class PeerResharder:
         if bulk_copy not in ("dma", "kernel"):
             raise ValueError("bulk_copy must be 'dma' (copy engines) or 'kernel' (this library's copy kernel)")
         self.bulk_copy = bulk_copy
+        self._copy_streams = None
         self.inputs, self.in_handles = [], []
         for _ in range(n_inputs):
             t = symm_mem.empty((1, self.hp, self.N, self.D), dtype=dtype, device=device)
@@ -218,8 +221,24 @@ class PeerResharder:
         with the kernels of the step, a peer gets the whole link), or this library's copy kernel, one launch
         per 24 pieces."""
         if self.bulk_copy == "dma":
-            for s_, d_ in zip(src, dst):
-                self._ops.copy_rows_dma(s_, d_, src_pitch, dst_pitch, width, rows, self.device)
+            # The pieces go to different peers over different links: issued on one stream they would run one after
+            # another (each a short 2-D copy that cannot fill a link by itself), so they are spread over a few side
+            # streams that fork from the current stream and join it again - several copy engines and links at once.
+            cur = torch.cuda.current_stream(self.device)
+            if self._copy_streams is None:
+                self._copy_streams = [torch.cuda.Stream(device=self.device) for _ in range(self.COPY_STREAMS)]
+            lanes = self._copy_streams[:max(1, min(len(self._copy_streams), len(src)))]
+            fork = torch.cuda.Event()
+            fork.record(cur)
+            for st in lanes:
+                st.wait_event(fork)
+            for i, (s_, d_) in enumerate(zip(src, dst)):
+                with torch.cuda.stream(lanes[i % len(lanes)]):
+                    self._ops.copy_rows_dma(s_, d_, src_pitch, dst_pitch, width, rows, self.device)
+            for st in lanes:
+                done = torch.cuda.Event()
+                done.record(st)
+                cur.wait_event(done)
             return
         for i in range(0, len(src), 24):
             self._ops.copy_rows_multi(src[i:i + 24], dst[i:i + 24], src_pitch, dst_pitch, width, rows, self.device)

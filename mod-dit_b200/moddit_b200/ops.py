@@ -241,7 +241,11 @@ def pooled_map(qbar: torch.Tensor, kbar: torch.Tensor, *, q_block_offset: int, k
 
 def replay_map(q: torch.Tensor, k: torch.Tensor, lse: torch.Tensor, *, softmax_scale: float,
                log_threshold: float, q_video_offset: int, k_video_offset: int, video_blocks: int,
-               block_size: int) -> torch.Tensor:
+               block_size: int, kernel: str = "tcgen05") -> torch.Tensor:
+    """Exact sparsity map.  kernel: "tcgen05" (`moddit_replay_map`) or "mma" (`moddit_replay_map_mma`, the second,
+    independently written path)."""
+    if kernel not in ("tcgen05", "mma"):
+        raise ValueError("kernel must be 'tcgen05' or 'mma'")
     dev = _need_cuda(q, k, lse)
     if q.dim() != 4 or k.dim() != 4:
         raise RuntimeError("Q and K must have shape [B, H, S, D]")
@@ -259,10 +263,11 @@ def replay_map(q: torch.Tensor, k: torch.Tensor, lse: torch.Tensor, *, softmax_s
         raise RuntimeError("LSE must be float32")
     B, H, N, D = q.shape
     out = torch.empty(B, H, video_blocks, video_blocks, device=dev, dtype=torch.float16)
+    entry = lib.moddit_replay_map if kernel == "tcgen05" else lib.moddit_replay_map_mma
     with torch.cuda.device(dev), _timed("moddit_replay_map", dev):
-        rc = lib.moddit_replay_map(_ptr(q), _ptr(k), _ptr(lse), _DTYPE[q.dtype], B * H, N, D, block_size,
-                                   float(softmax_scale), float(log_threshold), int(q_video_offset),
-                                   int(k_video_offset), int(video_blocks), _ptr(out), _stream(dev))
+        rc = entry(_ptr(q), _ptr(k), _ptr(lse), _DTYPE[q.dtype], B * H, N, D, block_size, float(softmax_scale),
+                   float(log_threshold), int(q_video_offset), int(k_video_offset), int(video_blocks), _ptr(out),
+                   _stream(dev))
     if rc != 0:
         raise RuntimeError("moddit_replay_map: " + lib.moddit_last_error_string().decode())
     return out

@@ -329,3 +329,48 @@ def test_module_self_test_runs(mod, capsys):
             tf.test_correctness(block_size=bs, D=128, model_type=model)
     assert capsys.readouterr().out.count("Sparsity max error") == 4
     tf.benchmark(H=2, S=1024, warmup=1, rep=2)
+
+
+@pytest.mark.parametrize("model_type,text,producer", [("wan", 0, "replay"), ("cogvideox", 128, "replay"),
+                                                      ("wan", 0, "pooled")])
+def test_two_guidance_branches_in_one_call_equal_two_calls(mod, model_type, text, producer):
+    """`SparseAttentionWithMapCFG` (branches folded into heads, one launch per kernel) against the way the
+    reference's Wan / CogVideoX processors do it: one call and one state per branch.  Outputs and masks bit-equal
+    on every step: dense warm-up, collecting steps, sparse steps and a refresh."""
+    am, st = mod["am"], mod["st"]
+    H, T, Hh, Ww, D, bs = 2, 4, 16, 16, 64, 64
+    video = T * Hh * Ww
+    S = video + text
+    branches = [_locality(70 + b, H, T, Hh, Ww, D, text, model_type == "cogvideox") for b in range(2)]
+    q, k, v = (torch.cat([br[i] for br in branches], dim=0).cuda() for i in range(3))       # (2, H, S, D)
+    warm, pT = 3, 3
+
+    def new_state():
+        s_ = st.create_adaptive_mask_state(model_type, H, video, text, Hh * Ww, T, warmup_steps=warm, top_k=6,
+                                           predict_T=pT, threshold=1e-3, block_size=bs)
+        s_["score_producer"] = producer
+        return s_
+    single, both = [new_state(), new_state()], [new_state(), new_state()]
+    for step in range(0, warm + pT + 1):
+        g = torch.Generator(device="cuda").manual_seed(500 + step)
+        qs = q + 0.05 * torch.randn(q.shape, device="cuda", generator=g).bfloat16()
+        outs = [am.SparseAttentionWithMap(qs[b:b + 1], k[b:b + 1], v[b:b + 1], single[b], LOG, current_step=step)[0]
+                for b in range(2)]
+        out2, _ = am.SparseAttentionWithMapCFG(qs, k, v, both, LOG, current_step=step)
+        assert out2.shape == qs.shape
+        for b in range(2):
+            assert torch.equal(out2[b:b + 1], outs[b]), (step, b)
+            ma, mb = single[b].get("mask"), both[b].get("mask")
+            assert (ma is None) == (mb is None)
+            if ma is not None:
+                assert torch.equal(ma, mb), (step, b)
+            if single[b].get("features_history"):
+                for fa, fb in zip(single[b]["features_history"], both[b]["features_history"]):
+                    assert all(torch.equal(fa[k_], fb[k_]) for k_ in fa)
+    assert both[0]["mask"] is not None and not bool(both[0]["mask"].all())
+    with pytest.raises(ValueError, match="differ in 'top_k'"):
+        other = new_state()
+        other["top_k"] = 7
+        am.SparseAttentionWithMapCFG(q, k, v, [new_state(), other], LOG, current_step=0)
+    from moddit_b200 import ops
+    ops.check_health(torch.device("cuda"))

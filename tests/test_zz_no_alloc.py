@@ -38,6 +38,13 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
         assert torch.allclose(out[:, -1], ref[:, -1], rtol=1e-6)
         again = ops.mts_noalloc(S, bpf)
         assert torch.equal(again, out)
+        # torch's counter only sees torch's allocator; the driver's own figure must not move either once the first
+        # call has loaded the library's module onto the device (that load is when the built-in array is set aside)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        rc = lib.moddit_mts_noalloc(ctypes.c_void_p(S.data_ptr()), H, n, bpf, ctypes.c_void_p(out.data_ptr()), stream)
+        torch.cuda.synchronize()
+        assert rc == 0 and torch.cuda.mem_get_info()[0] == free_before
 
 
 def test_noalloc_rejects_sizes_beyond_the_built_in_scratch():
