@@ -15,6 +15,15 @@ __device__ __forceinline__ uint32_t order_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// Synchronisation after one compare-exchange stage of a shared-memory bitonic sort in which thread t handles the
+// pairs t, t + blockDim, ...: with stride <= 32 the 32 pairs of a warp lie inside one aligned run of 64 elements that
+// no other warp touches, so a stage only needs a block-wide barrier if it, or the stage after it, reaches further.
+__device__ __forceinline__ void bitonic_stage_sync(int stride, int size, int P) {
+  const int next = (stride > 1) ? (stride >> 1) : ((size < P) ? size : 0);
+  if (stride > 32 || next > 32) __syncthreads();
+  else __syncwarp();
+}
+
 constexpr int kSelectThreads = 1024;
 
 // One CTA per head: the L = 3n - 1 extrapolated line intensities become 64-bit keys (value order << 32 | index),
@@ -58,9 +67,10 @@ __global__ void __launch_bounds__(kSelectThreads) select_lines_kernel(
           sort_keys[hi] = a;
         }
       }
-      __syncthreads();
+      bitonic_stage_sync(stride, size, P);
     }
   }
+  __syncthreads();
   for (int r = threadIdx.x; r < k; r += kSelectThreads)
     selected[static_cast<int64_t>(h) * k + r] = static_cast<int64_t>(static_cast<uint32_t>(sort_keys[r]));
 }
@@ -162,9 +172,10 @@ __global__ void __launch_bounds__(kMassThreads) select_mass_kernel(const __half*
           key[hi] = a;
         }
       }
-      __syncthreads();
+      bitonic_stage_sync(stride, size, P);
     }
   }
+  __syncthreads();
   // inclusive prefix of w over the sorted order (padding has w = 2^24 - 0xffffffff wraps; mask it out)
   const int per = (P + kMassThreads - 1) / kMassThreads;
   const int beg = min(P, static_cast<int>(threadIdx.x) * per), end = min(P, beg + per);
@@ -230,10 +241,13 @@ __global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t*
       for (int x = 0; x < 2; ++x) {
         const int qt = 2 * p + x;
         if (qt >= ntq) continue;
+        if (sub == 1) {                 // block size 128: one mask block is the whole tile, all four flags at once
+          if (qt < nbq && t < lim && mh[static_cast<int64_t>(qt) * nbk + t]) fl |= 0xf << (4 * x);
+          continue;
+        }
         for (int rh = 0; rh < 2; ++rh)
           for (int ch = 0; ch < 2; ++ch) {
-            const int bi = (sub == 1) ? qt : qt * 2 + rh;
-            const int bj = (sub == 1) ? t : t * 2 + ch;
+            const int bi = qt * 2 + rh, bj = t * 2 + ch;
             if (bi < nbq && bj < lim && mh[static_cast<int64_t>(bi) * nbk + bj]) fl |= 1 << (4 * x + 2 * rh + ch);
           }
       }

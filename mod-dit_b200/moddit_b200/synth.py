@@ -112,6 +112,9 @@ WORKLOADS = {
                  text_first=False, top_k=20, predict_T=5),
     "medium": dict(model_type="hunyuan", heads=8, head_dim=128, block_size=128, grid=(8, 64, 64), text_tokens=256,
                    text_first=False, top_k=80, predict_T=5),
+    # a CogVideoX-like case (head_dim 64, block 64, text first) small enough to capture under a profiler
+    "medium64": dict(model_type="cogvideox", heads=16, head_dim=64, block_size=64, grid=(4, 64, 64), text_tokens=256,
+                     text_first=True, top_k=60, predict_T=5),
     "small": dict(model_type="hunyuan", heads=4, head_dim=128, block_size=128, grid=(8, 32, 32), text_tokens=256,
                   text_first=False, top_k=30, predict_T=5),
 }
