@@ -293,14 +293,28 @@ __global__ void __launch_bounds__(kMapThreads) pooled_map_kernel(const float* __
   const int g = lane / 4, t2 = 2 * (lane % 4);
   for (int j0 = 0; j0 < n; j0 += kMapCols) {
     __syncthreads();
-    for (int e = tid; e < kMapCols * d4; e += kMapThreads) {
-      const int r = e / d4, c = e - r * d4;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (j0 + r < n) v = __ldg(reinterpret_cast<const float4*>(kh + static_cast<int64_t>(j0 + r) * D) + c);
-      uint2 hi, lo;
-      split4(v, hi, lo);
-      *reinterpret_cast<uint2*>(khi + r * ld + 4 * c) = hi;
-      *reinterpret_cast<uint2*>(klo + r * ld + 4 * c) = lo;
+    // stage the key tile: eight independent 16-byte loads in flight per thread before any is used (one load at a
+    // time, each waiting for the memory system, was most of this kernel's time)
+    for (int e0 = tid; e0 < kMapCols * d4; e0 += 8 * kMapThreads) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int e = e0 + u * kMapThreads;
+        const int r = e / d4, c = e - r * d4;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < kMapCols * d4 && j0 + r < n)
+          v[u] = __ldg(reinterpret_cast<const float4*>(kh + static_cast<int64_t>(j0 + r) * D) + c);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int e = e0 + u * kMapThreads;
+        if (e >= kMapCols * d4) break;
+        const int r = e / d4, c = e - r * d4;
+        uint2 hi, lo;
+        split4(v[u], hi, lo);
+        *reinterpret_cast<uint2*>(khi + r * ld + 4 * c) = hi;
+        *reinterpret_cast<uint2*>(klo + r * ld + 4 * c) = lo;
+      }
     }
     __syncthreads();
     float acc[2][2][4];

@@ -234,27 +234,40 @@ __global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t*
   int32_t* out = entries + (static_cast<int64_t>(h) * npairs + p) * ntk;
   const int lim = min(nbk, kv_block_limit);
   int base = 0;
-  for (int t0 = 0; t0 < ntk; t0 += 32) {
-    const int t = t0 + lane;
-    int fl = 0;
-    if (t < ntk) {
-      for (int x = 0; x < 2; ++x) {
-        const int qt = 2 * p + x;
-        if (qt >= ntq) continue;
-        if (sub == 1) {                 // block size 128: one mask block is the whole tile, all four flags at once
-          if (qt < nbq && t < lim && mh[static_cast<int64_t>(qt) * nbk + t]) fl |= 0xf << (4 * x);
-          continue;
-        }
-        for (int rh = 0; rh < 2; ++rh)
-          for (int ch = 0; ch < 2; ++ch) {
-            const int bi = qt * 2 + rh, bj = t * 2 + ch;
-            if (bi < nbq && bj < lim && mh[static_cast<int64_t>(bi) * nbk + bj]) fl |= 1 << (4 * x + 2 * rh + ch);
+  // four steps of 32 key tiles at a time: all their mask bytes are requested before the first ballot, so the warp
+  // waits for the memory system once per 128 key tiles instead of once per 32
+  for (int t0 = 0; t0 < ntk; t0 += 128) {
+    int fls[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int t = t0 + 32 * u + lane;
+      int fl = 0;
+      if (t < ntk) {
+        for (int x = 0; x < 2; ++x) {
+          const int qt = 2 * p + x;
+          if (qt >= ntq) continue;
+          if (sub == 1) {               // block size 128: one mask block is the whole tile, all four flags at once
+            const uint8_t m = (qt < nbq && t < lim) ? mh[static_cast<int64_t>(qt) * nbk + t] : uint8_t(0);
+            fl |= m ? (0xf << (4 * x)) : 0;
+            continue;
           }
+          for (int rh = 0; rh < 2; ++rh)
+            for (int ch = 0; ch < 2; ++ch) {
+              const int bi = qt * 2 + rh, bj = t * 2 + ch;
+              const uint8_t m = (bi < nbq && bj < lim) ? mh[static_cast<int64_t>(bi) * nbk + bj] : uint8_t(0);
+              fl |= m ? (1 << (4 * x + 2 * rh + ch)) : 0;
+            }
+        }
       }
+      fls[u] = fl;
     }
-    const unsigned bal = __ballot_sync(0xffffffffu, fl != 0);
-    if (fl) out[base + __popc(bal & ((1u << lane) - 1))] = (t << 8) | fl;
-    base += __popc(bal);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int t = t0 + 32 * u + lane;
+      const unsigned bal = __ballot_sync(0xffffffffu, fls[u] != 0);
+      if (fls[u]) out[base + __popc(bal & ((1u << lane) - 1))] = (t << 8) | fls[u];
+      base += __popc(bal);
+    }
   }
   if (lane == 0) counts[static_cast<int64_t>(h) * npairs + p] = base;
 }
