@@ -179,6 +179,22 @@ size_t moddit_solve_workspace_bytes(int H, int n);
 int moddit_solve(const float* mts, const void* factor, int H, int n, int blocks_per_frame,
                  double regularization, float* X, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same solve for small systems in the form the specification words it: the normal equations M^T M + reg*I
+ * (3n x 3n, float32, closed form) are built in one CTA's shared memory and Cholesky-factored there
+ * (moddit_solve_small_prepare, once per (n, blocks_per_frame, reg): the reference caches its factor the same way,
+ * MoD/mod/cuda_lstsq.py:153-186); per call the factor is brought into shared memory and one warp per head runs the
+ * forward and back substitution for that head's right-hand side (moddit_solve_small).  Float32 arithmetic like the
+ * reference's torch.linalg.cholesky + torch.cholesky_solve on the same system (:177,203); no workspace.
+ * Limited to n <= moddit_solve_small_max_n() (3n = 224 unknowns fit shared memory; the first configuration of the
+ * specification has n = 64); larger n return MODDIT_E_UNSUPPORTED - use moddit_solve_prepare + moddit_solve, whose
+ * structured elimination has no such limit.
+ *   factor : moddit_solve_small_factor_bytes(n) bytes (the lower-triangular factor, (3n)^2 float32)
+ *   mts    : (H, 3n) float32      X : (H, 3n) float32, same unknown order as moddit_solve */
+int moddit_solve_small_max_n(void);
+size_t moddit_solve_small_factor_bytes(int n);
+int moddit_solve_small_prepare(int n, int blocks_per_frame, float regularization, float* factor, void* stream);
+int moddit_solve_small(const float* mts, const float* factor, int H, int n, float* X, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Line selection.  Replaces `choose_topk_lines` (MoD/mod/attn_mask.py:351-370): extrapolate
  * cur + (cur-last)/predict_T for verticals c (H,n) and diagonals d (H,2n-1), concatenate [c | d],

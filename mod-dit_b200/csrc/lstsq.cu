@@ -147,11 +147,8 @@ __global__ void __launch_bounds__(256) mts_finish_kernel(const float* __restrict
   mts[static_cast<int64_t>(h) * F + x] = out;
 }
 
-__global__ void mtm_kernel(int n, int bpf, float reg, float* __restrict__ mtm) {
-  const int F = 3 * n;
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= static_cast<int64_t>(F) * F) return;
-  int a = static_cast<int>(idx / F), b = static_cast<int>(idx % F);
+// Element (a, b) of the structural Gram matrix M^T M + reg * I for unknowns [2n-1 diagonals | n columns | 1 block].
+__device__ __forceinline__ float mtm_entry(int a, int b, int n, int bpf, float reg) {
   const bool diag = (a == b);
   if (a > b) {  // symmetric: evaluate the upper triangle
     const int t = a;
@@ -183,7 +180,96 @@ __global__ void mtm_kernel(int n, int bpf, float reg, float* __restrict__ mtm) {
     v = static_cast<float>(nb * bpf * bpf);
   }
   if (diag) v = __fadd_rn(v, reg);
-  mtm[idx] = v;
+  return v;
+}
+
+__global__ void mtm_kernel(int n, int bpf, float reg, float* __restrict__ mtm) {
+  const int F = 3 * n;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(F) * F) return;
+  mtm[idx] = mtm_entry(static_cast<int>(idx / F), static_cast<int>(idx % F), n, bpf, reg);
+}
+
+// ---- small systems: normal equations in shared memory, Cholesky, one warp per head -------------------------------
+// For 3n <= kSmallMaxF unknowns the whole Gram matrix fits one CTA's shared memory in float32 (rows padded by one
+// word so that column walks do not collide on a bank).  `solve_small_factor_kernel` (once per geometry, like the
+// reference's cached factor, MoD/mod/cuda_lstsq.py:153-186) builds it from the closed form and factors it in place
+// (right-looking Cholesky, a warp per row of the trailing update); `solve_small_kernel` (per call) brings the
+// factor into shared memory and every warp takes the right-hand side of one head: forward and back substitution
+// as warp-wide dot products, float32 like the reference's torch.linalg.cholesky / cholesky_solve on this system
+// (MoD/mod/cuda_lstsq.py:177,203).
+constexpr int kSmallMaxF = 224;
+constexpr int kSmallFactorThreads = 1024;
+constexpr int kSmallThreads = 256;
+
+__global__ void __launch_bounds__(kSmallFactorThreads) solve_small_factor_kernel(int n, int bpf, float reg,
+                                                                                float* __restrict__ L) {
+  extern __shared__ __align__(16) float small_smem[];
+  const int F = 3 * n;
+  const int ld = F + 1;
+  float* A = small_smem;                                 // [F][ld], lower triangle becomes L
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  for (int e = tid; e < F * F; e += kSmallFactorThreads) {
+    const int a = e / F, b = e - a * F;
+    A[a * ld + b] = mtm_entry(a, b, n, bpf, reg);
+  }
+  __syncthreads();
+  for (int k = 0; k < F; ++k) {
+    const float piv = sqrtf(A[k * ld + k]);              // every thread reads the same word; thread 0 writes it below
+    __syncthreads();
+    if (tid == 0) A[k * ld + k] = piv;
+    const float inv = 1.0f / piv;
+    for (int i = k + 1 + tid; i < F; i += kSmallFactorThreads) A[i * ld + k] *= inv;
+    __syncthreads();
+    // trailing update of the lower triangle: A[i][j] -= L[i][k] * L[j][k] for k < j <= i; a warp per row
+    for (int i = k + 1 + warp; i < F; i += kSmallFactorThreads / 32) {
+      const float lik = A[i * ld + k];
+      for (int j = k + 1 + lane; j <= i; j += 32) A[i * ld + j] = fmaf(-lik, A[j * ld + k], A[i * ld + j]);
+    }
+    __syncthreads();
+  }
+  for (int e = tid; e < F * F; e += kSmallFactorThreads) {
+    const int a = e / F, b = e - a * F;
+    L[e] = (b <= a) ? A[a * ld + b] : 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(kSmallThreads) solve_small_kernel(const float* __restrict__ mts,
+                                                                    const float* __restrict__ L, int H, int n,
+                                                                    float* __restrict__ X) {
+  extern __shared__ __align__(16) float small_smem[];
+  const int F = 3 * n;
+  const int ld = F + 1;
+  float* A = small_smem;                                 // [F][ld]: the factor
+  float* ys = A + static_cast<size_t>(F) * ld;           // [warps][F] right-hand sides / solutions
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  for (int e = tid; e < F * F; e += kSmallThreads) {
+    const int a = e / F, b = e - a * F;
+    A[a * ld + b] = L[e];
+  }
+  __syncthreads();
+  const int h = blockIdx.x * (kSmallThreads / 32) + warp;
+  if (h >= H) return;                                     // no block-wide barrier below this line
+  float* y = ys + warp * F;
+  for (int i = lane; i < F; i += 32) y[i] = mts[static_cast<int64_t>(h) * F + i];
+  __syncwarp();
+  for (int i = 0; i < F; ++i) {                           // L y = b
+    float acc = 0.f;
+    for (int j = lane; j < i; j += 32) acc = fmaf(A[i * ld + j], y[j], acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[i] = (y[i] - acc) / A[i * ld + i];
+    __syncwarp();
+  }
+  for (int i = F - 1; i >= 0; --i) {                      // L^T x = y
+    float acc = 0.f;
+    for (int j = i + 1 + lane; j < F; j += 32) acc = fmaf(A[j * ld + i], y[j], acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[i] = (y[i] - acc) / A[i * ld + i];
+    __syncwarp();
+  }
+  for (int i = lane; i < F; i += 32) X[static_cast<int64_t>(h) * F + i] = y[i];
 }
 
 // ---- solve set-up -------------------------------------------------------------------------------
@@ -630,5 +716,50 @@ extern "C" int moddit_solve(const float* mts, const void* factor, int H, int n, 
   MODDIT_CHECK_LAUNCH("solve_gemv_kernel");
   solve_back_kernel<<<H, kSolveThreads, sm_back, st>>>(mts, w, wb, y, n, X);
   MODDIT_CHECK_LAUNCH("solve_back_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_solve_small_max_n(void) { return kSmallMaxF / 3; }
+
+extern "C" size_t moddit_solve_small_factor_bytes(int n) {
+  return (n > 0 && 3 * n <= kSmallMaxF) ? sizeof(float) * static_cast<size_t>(3 * n) * (3 * n) : 0;
+}
+
+static int check_small(const char* who, int n) {
+  if (n <= 0) return fail(MODDIT_E_ARG, "%s: n=%d must be positive", who, n);
+  if (3 * n > kSmallMaxF)
+    return fail(MODDIT_E_UNSUPPORTED, "%s: 3n=%d unknowns exceed the %d that fit shared memory; use moddit_solve", who,
+                3 * n, kSmallMaxF);
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_solve_small_prepare(int n, int blocks_per_frame, float regularization, float* factor,
+                                          void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(factor, "solve_small_prepare: null pointer");
+  MODDIT_CHECK_ARG(blocks_per_frame > 0, "solve_small_prepare: blocks_per_frame must be positive");
+  MODDIT_CHECK_ARG(regularization > 0.f, "solve_small_prepare: the system is singular without regularisation");
+  if (int rc = check_small("solve_small_prepare", n)) return rc;
+  if (int rc = require_sm100()) return rc;
+  const int F = 3 * n;
+  const size_t smem = sizeof(float) * static_cast<size_t>(F) * (F + 1);
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(solve_small_factor_kernel), smem)) return rc;
+  solve_small_factor_kernel<<<1, kSmallFactorThreads, smem, as_stream(stream)>>>(n, blocks_per_frame, regularization,
+                                                                                factor);
+  MODDIT_CHECK_LAUNCH("solve_small_factor_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_solve_small(const float* mts, const float* factor, int H, int n, float* X, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(mts && factor && X, "solve_small: null pointer");
+  MODDIT_CHECK_ARG(H > 0 && H <= 65535 * (kSmallThreads / 32), "solve_small: H=%d out of range", H);
+  if (int rc = check_small("solve_small", n)) return rc;
+  if (int rc = require_sm100()) return rc;
+  const int F = 3 * n;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(F) * (F + 1) + static_cast<size_t>(kSmallThreads / 32) * F);
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(solve_small_kernel), smem)) return rc;
+  solve_small_kernel<<<ceil_div(H, kSmallThreads / 32), kSmallThreads, smem, as_stream(stream)>>>(mts, factor, H, n, X);
+  MODDIT_CHECK_LAUNCH("solve_small_kernel");
   return MODDIT_OK;
 }

@@ -217,6 +217,102 @@ __global__ void __launch_bounds__(kMassThreads) select_mass_kernel(const __half*
   }
 }
 
+// The same selection without sorting, one warp per (query block, head), for n <= 1024 (32 values per lane in
+// registers).  In the sorted order (brightness descending, index ascending) the weight that precedes element e is
+//   before(e) = sum of the weights greater than w_e  +  w_e * (equal weights with a lower index),
+// and e is kept iff before(e) < target (or, in the count form, iff its rank - the same expression with ones
+// instead of weights - is below the count).  The sum over greater weights only depends on the value, so a
+// bisection over the 25-bit value range finds t* = the smallest value whose "sum of greater weights" is below the
+// target: everything brighter than t* is kept, everything darker is not, and the elements equal to t* are kept in
+// index order while the running sum stays below the target.  Bit-identical to the sort kernel.
+constexpr int kMassWarpMax = 1024;
+constexpr int kMassWarpThreads = 256;
+
+__global__ void __launch_bounds__(kMassWarpThreads) select_mass_warp_kernel(
+    const __half* __restrict__ map, int n, int rows_total, uint32_t tau_fixed, int topk_count,
+    const uint8_t* __restrict__ row_full, const uint8_t* __restrict__ col_keep, uint8_t* __restrict__ keep) {
+  const int lane = threadIdx.x % 32;
+  const int rowid = blockIdx.x * (kMassWarpThreads / 32) + threadIdx.x / 32;      // h * n + i
+  if (rowid >= rows_total) return;
+  const int h = rowid / n, i = rowid - h * n;
+  const __half* row = map + static_cast<int64_t>(rowid) * n;
+  uint32_t w[32];
+#pragma unroll
+  for (int u = 0; u < 32; ++u) {
+    const int j = lane + 32 * u;
+    w[u] = 0xffffffffu;                                     // beyond the row: compares greater than nothing, never kept
+    if (j < n) {
+      float b = 1.0f - __half2float(row[j]);
+      b = fminf(fmaxf(b, 0.f), 1.f);
+      w[u] = static_cast<uint32_t>(floorf(b * 16777216.0f));                      // exact: b is a multiple of 2^-24
+    }
+  }
+  const bool by_count = topk_count > 0;
+  // amount(u): what element u adds to a sum (its weight, or one in the count form); 0 beyond the row
+  auto greater_than = [&](uint32_t t) -> unsigned long long {
+    uint32_t part = 0;                                      // at most 32 * 2^24 per lane
+#pragma unroll
+    for (int u = 0; u < 32; ++u) {
+      const bool in = (w[u] != 0xffffffffu) && (w[u] > t);
+      part += in ? (by_count ? 1u : w[u]) : 0u;
+    }
+    unsigned long long tot = part;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    return tot;
+  };
+  unsigned long long target;
+  if (by_count) {
+    target = static_cast<unsigned long long>(topk_count);
+  } else {
+    uint32_t part = 0;
+#pragma unroll
+    for (int u = 0; u < 32; ++u) part += (w[u] != 0xffffffffu) ? w[u] : 0u;
+    unsigned long long total = part;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    target = (static_cast<unsigned long long>(tau_fixed) * total + ((1ull << kMassBits) - 1)) >> kMassBits;
+  }
+  // smallest t in [0, 2^24] with greater_than(t) < target; greater_than(2^24) = 0, so t = 2^24 qualifies unless
+  // the target is 0 (then nothing is kept by the rule)
+  uint32_t lo = 0, hi = 1u << kMassBits;
+  if (target == 0) {
+    lo = hi = 0xfffffffeu;                                  // no element reaches it: nothing kept by the rule
+  } else {
+    while (lo < hi) {
+      const uint32_t mid = lo + ((hi - lo) >> 1);
+      if (greater_than(mid) < target) hi = mid; else lo = mid + 1;
+    }
+  }
+  const uint32_t tstar = lo;
+  const unsigned long long above = (target == 0) ? 0ull : greater_than(tstar);
+  const bool whole_row = row_full != nullptr && row_full[rowid] != 0;
+  uint8_t* dst = keep + static_cast<int64_t>(rowid) * n;
+  unsigned long long ties_before = 0;                       // elements equal to t* in earlier groups of 32
+#pragma unroll
+  for (int u = 0; u < 32; ++u) {
+    const int j = lane + 32 * u;
+    const bool tie = (w[u] == tstar);
+    const unsigned bal = __ballot_sync(0xffffffffu, tie);
+    if (j < n) {
+      bool k = false;
+      if (target != 0) {
+        if (w[u] > tstar) {
+          k = true;
+        } else if (tie) {
+          const unsigned long long prior = ties_before + __popc(bal & ((1u << lane) - 1));
+          k = above + prior * (by_count ? 1ull : static_cast<unsigned long long>(tstar)) < target;
+        }
+      }
+      if (!by_count && j == i) k = true;                    // the mass rule always keeps the diagonal block
+      if (whole_row) k = true;
+      if (col_keep != nullptr && col_keep[static_cast<int64_t>(h) * n + j] != 0) k = true;
+      dst[j] = k ? 1 : 0;
+    }
+    ties_before += __popc(bal);
+  }
+}
+
 // ---- work lists ---------------------------------------------------------------------------------
 constexpr int kListThreads = 256;
 
@@ -425,9 +521,16 @@ extern "C" int moddit_select_mass(const void* map_f16, int H, int n, float tau, 
   MODDIT_CHECK_ARG(tau >= 0.f && tau <= 1.f, "select_mass: tau=%g outside [0, 1]", tau);
   if (n > 2048) return fail(MODDIT_E_UNSUPPORTED, "select_mass: n=%d exceeds 2048", n);
   if (int rc = require_sm100()) return rc;
+  const uint32_t tau_fixed = static_cast<uint32_t>(floorf(tau * 16777216.0f));
+  if (n <= kMassWarpMax) {
+    const int rows = H * n;
+    select_mass_warp_kernel<<<ceil_div(rows, kMassWarpThreads / 32), kMassWarpThreads, 0, as_stream(stream)>>>(
+        static_cast<const __half*>(map_f16), n, rows, tau_fixed, 0, nullptr, nullptr, keep);
+    MODDIT_CHECK_LAUNCH("select_mass_warp_kernel");
+    return MODDIT_OK;
+  }
   int P = 2;
   while (P < n) P <<= 1;
-  const uint32_t tau_fixed = static_cast<uint32_t>(floorf(tau * 16777216.0f));
   select_mass_kernel<<<dim3(n, H), kMassThreads, 2 * sizeof(unsigned long long) * P, as_stream(stream)>>>(
       static_cast<const __half*>(map_f16), n, P, tau_fixed, 0, nullptr, nullptr, keep);
   MODDIT_CHECK_LAUNCH("select_mass_kernel");
@@ -442,6 +545,13 @@ extern "C" int moddit_select_topk_blocks(const void* map_f16, int H, int n, int 
   MODDIT_CHECK_ARG(count > 0 && count <= n, "select_topk_blocks: count=%d outside 1..%d", count, n);
   if (n > 2048) return fail(MODDIT_E_UNSUPPORTED, "select_topk_blocks: n=%d exceeds 2048", n);
   if (int rc = require_sm100()) return rc;
+  if (n <= kMassWarpMax) {
+    const int rows = H * n;
+    select_mass_warp_kernel<<<ceil_div(rows, kMassWarpThreads / 32), kMassWarpThreads, 0, as_stream(stream)>>>(
+        static_cast<const __half*>(map_f16), n, rows, 0u, count, row_full, col_keep, keep);
+    MODDIT_CHECK_LAUNCH("select_mass_warp_kernel");
+    return MODDIT_OK;
+  }
   int P = 2;
   while (P < n) P <<= 1;
   select_mass_kernel<<<dim3(n, H), kMassThreads, 2 * sizeof(unsigned long long) * P, as_stream(stream)>>>(

@@ -52,6 +52,10 @@ SIGNATURES = {
     "moddit_solve_workspace_bytes": (c_size_t, [c_int, c_int]),
     "moddit_solve": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_double, c_void_p, c_void_p, c_size_t,
                              c_void_p]),
+    "moddit_solve_small_max_n": (c_int, []),
+    "moddit_solve_small_factor_bytes": (c_size_t, [c_int]),
+    "moddit_solve_small_prepare": (c_int, [c_int, c_int, c_float, c_void_p, c_void_p]),
+    "moddit_solve_small": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "moddit_select_lines": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                                     c_void_p, c_void_p]),
     "moddit_head_modes": (c_int, [c_void_p, c_int, c_float, c_void_p, c_void_p]),

@@ -386,12 +386,52 @@ def solve_factor(n: int, blocks_per_frame: int, regularization: float, device) -
         return fac
 
 
-def solve(mts_: torch.Tensor, n: int, blocks_per_frame: int, regularization: float) -> torch.Tensor:
+def _small_factor(n: int, blocks_per_frame: int, regularization: float, device) -> torch.Tensor:
+    """Float32 Cholesky factor of the small system, computed once per (device, n, bpf, lambda)."""
+    device = torch.device(device)
+    key = ("small", device.index if device.index is not None else torch.cuda.current_device(), n,
+           int(blocks_per_frame), float(regularization))
+    fac = _FACTOR_CACHE.get(key)
+    if fac is not None:
+        return fac
+    with _FACTOR_LOCK:
+        fac = _FACTOR_CACHE.get(key)
+        if fac is None:
+            fac = torch.empty(lib.moddit_solve_small_factor_bytes(n) // 4, device=device, dtype=torch.float32)
+            with torch.cuda.device(device), _timed("moddit_solve_prepare", device):
+                check(lib.moddit_solve_small_prepare(n, int(blocks_per_frame), float(regularization), _ptr(fac),
+                                                     _stream(device)), "moddit_solve_small_prepare")
+            torch.cuda.current_stream(device).synchronize()      # other streams may use the factor later
+            _FACTOR_CACHE[key] = fac
+        return fac
+
+
+def solve(mts_: torch.Tensor, n: int, blocks_per_frame: int, regularization: float,
+          method: str = "auto") -> torch.Tensor:
+    """X (H, 3n) float32 with (M^T M + regularization * I) X = mts.
+
+    method "small": normal equations in shared memory, float32 Cholesky, one warp per head (`moddit_solve_small`;
+    n <= `lib.moddit_solve_small_max_n()`); "structured": the float64 structured elimination against a factor
+    cached per geometry (`moddit_solve`); "auto": "small" where it fits and regularization >= 0.5, else
+    "structured"."""
     dev = _need_cuda(mts_)
     mts_ = mts_.contiguous()
     if mts_.dtype != torch.float32 or mts_.shape[1] != 3 * n:
         raise ValueError("mts must be float32 (H, 3n)")
+    if method not in ("auto", "small", "structured"):
+        raise ValueError("method must be 'auto', 'small' or 'structured'")
     H = mts_.shape[0]
+    # "auto" takes the float32 route only for well-conditioned systems (the regularisation the path uses is 1;
+    # with a tiny one the unregularised rank deficiency is a float32 pivot away)
+    if method == "small" or (method == "auto" and n <= lib.moddit_solve_small_max_n() and regularization >= 0.5):
+        if n > lib.moddit_solve_small_max_n():
+            raise ValueError(f"solve: 3n = {3 * n} unknowns exceed the {3 * lib.moddit_solve_small_max_n()} that fit "
+                             "shared memory; use method='structured'")
+        fac = _small_factor(n, blocks_per_frame, regularization, dev)
+        X = torch.empty(H, 3 * n, device=dev, dtype=torch.float32)
+        with torch.cuda.device(dev), _timed("moddit_solve", dev):
+            check(lib.moddit_solve_small(_ptr(mts_), _ptr(fac), H, n, _ptr(X), _stream(dev)), "moddit_solve_small")
+        return X
     fac = solve_factor(n, blocks_per_frame, regularization, dev)
     wb = lib.moddit_solve_workspace_bytes(H, n)
     ws = torch.empty(wb, device=dev, dtype=torch.uint8)

@@ -140,7 +140,7 @@ def test_mtm_and_solve(ops, n, bpf, lam):
     assert torch.equal(mtm, orc.compute_mtm(n, bpf, lam))
     mts = orc.compute_mts(S, bpf)
     ref = orc.solve_features(mts, n, bpf, lam, precise=True)["X"]
-    X = ops.solve(mts.cuda(), n, bpf, lam).cpu()
+    X = ops.solve(mts.cuda(), n, bpf, lam, method="structured").cpu()
     # float64 structured solve rounded to float32 against a float64 dense solve
     assert torch.allclose(X.double(), ref, rtol=2e-5, atol=2e-6 / min(1.0, lam))
     # and against the reference's own fp32 path within that path's rounding error
@@ -161,6 +161,28 @@ def test_solve_matches_reference_golden(ops, golden_dir):
         assert torch.allclose(X[:, :nd], torch.from_numpy(g[f"ls{ci}_d"]), **tol)
         assert torch.allclose(X[:, nd:nd + n] / 2, torch.from_numpy(g[f"ls{ci}_c"]), **tol)
         assert torch.allclose(X[:, -1], torch.from_numpy(g[f"ls{ci}_bd"]), **tol)
+
+
+@pytest.mark.parametrize("n,bpf,H", [(12, 4, 3), (13, 4, 9), (64, 16, 2), (74, 30, 17)])
+def test_small_solve_in_shared_memory_matches_the_exact_solve(ops, n, bpf, H):
+    """Normal equations in shared memory, float32 Cholesky, one warp per head (the specification's wording; what
+    `ops.solve` picks for n <= 74) against the oracle's float64 solve of the same system and against the structured
+    float64 route; n = 64 is the specification's first configuration, 17 heads need three CTAs."""
+    S = _grid_map(H, n, 64, 40 + n)
+    mts = orc.compute_mts(S, bpf)
+    ref = orc.solve_features(mts, n, bpf, 1.0, precise=True)
+    nd = 2 * n - 1
+    small = ops.solve(mts.cuda(), n, bpf, 1.0, method="small").cpu()
+    auto = ops.solve(mts.cuda(), n, bpf, 1.0).cpu()
+    structured = ops.solve(mts.cuda(), n, bpf, 1.0, method="structured").cpu()
+    assert torch.equal(small, auto)                         # "auto" takes the small route at these sizes
+    for X, tol in ((small, 2e-4), (structured, 2e-5)):
+        assert torch.allclose(X[:, :nd].double(), ref["d"].double(), atol=tol, rtol=1e-3)
+        assert torch.allclose((X[:, nd:nd + n] / 2).double(), ref["c"].double(), atol=tol, rtol=1e-3)
+        assert torch.allclose(X[:, -1].double(), ref["b_d"].double(), atol=tol, rtol=1e-3)
+    assert (small - structured).abs().max().item() <= 2e-4
+    with pytest.raises(Exception, match="exceed"):
+        ops.solve(torch.zeros(1, 3 * 80, device="cuda"), 80, 10, 1.0, method="small")
 
 
 def test_selection_and_mask_bit_exact_vs_golden(ops, golden_dir):
