@@ -51,7 +51,8 @@ def solve_lstsq(warmup_state, S_T, step, blocks_per_frame, layer_idx=0, regulari
     """X = (M^T M + reg I)^-1 M^T S for every head of S_T (H, n, n).
 
     Returns {'d': (H,2n-1) diagonals, 'c': (H,n) verticals / 2, 'b_d': (H,)}; all zeros while
-    step <= warmup_steps - 2, as the reference does.
+    step <= warmup_steps - 2, as the reference does.  S_T is a float16 map (what both map producers write, as in
+    the reference, whose line sums widen it to float32, :231): a float32 S_T is rounded to float16 first.
     """
     num_heads, n = S_T.shape[0], S_T.shape[1]
     if not S_T.is_cuda:

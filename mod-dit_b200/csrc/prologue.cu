@@ -396,6 +396,12 @@ extern "C" int moddit_qkv_prologue(const void* q_in, const void* k_in, const voi
   if (pooled) {
     MODDIT_CHECK_ARG(block_size > 0 && dst_row0 % block_size == 0,
                      "block means need block_size > 0 and dst_row0 (%d) on a block boundary", dst_row0);
+    // a short last block is only right at the very end of the output sequence: anywhere else the rows that
+    // complete the block come from another call and this call's partial mean would be wrong
+    MODDIT_CHECK_ARG(S % block_size == 0 || static_cast<int64_t>(dst_row0) + S == N_out,
+                     "block means need S (%d) to be a multiple of block_size (%d) unless the rows end the output "
+                     "sequence (dst_row0 + S = %lld, N_out = %d)", S, block_size,
+                     static_cast<long long>(dst_row0) + S, N_out);
     bs = block_size;
   }
   MODDIT_CHECK_ARG(ceil_div(S, bs) <= 65535, "S / block_size must fit a grid dimension");

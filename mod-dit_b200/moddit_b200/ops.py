@@ -288,7 +288,12 @@ def mts(S_T: torch.Tensor, blocks_per_frame: int, *, prev: Optional[torch.Tensor
         keep_mask: Optional[torch.Tensor] = None, mask_off: int = 0
         ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """M^T S of a (H,n,n) float16 map.  With `prev` and `keep_mask` (bool (H,R,R), video region starting at
-    block `mask_off`) the history merge `where(keep, S_T, prev)` happens first and is returned too."""
+    block `mask_off`) the history merge `where(keep, S_T, prev)` happens first and is returned too.
+
+    The map is float16 by contract: both producers of this library write float16 maps (the reference's map is
+    float16 too and is only widened for the arithmetic, MoD/mod/cuda_lstsq.py:231), and the line sums are then
+    exact in float32.  A float32 map is rounded to float16 first - values that are not float16 numbers lose
+    their low bits."""
     dev = _need_cuda(S_T)
     if S_T.dtype != torch.float16:
         S_T = S_T.to(torch.float16)
