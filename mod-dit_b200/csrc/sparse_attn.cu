@@ -445,6 +445,414 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
   }
 }
 
+// ====================================================================================================
+// Head dimension 64.
+//
+// At D = 64 a 128 x 128 tile carries half the tensor work of the D = 128 tile for the same 16,384 exponentials, so
+// the kernel above - in which a tile's chain Q K^T -> softmax -> P V is strictly serial because P overwrites S -
+// spends most of a key-tile slot waiting on that chain.  Here tensor memory has room to break the chain:
+//   S_A [0,128)  S_B [128,256)  O_A [256,320)  O_B [320,384)  P_A [384,448)  P_B [448,512)
+// P has columns of its own, so Q K^T of the NEXT entry is issued as soon as the softmax has read S of the current
+// one into registers (barrier kSFree), and a tile's softmax runs back to back while its products run beside it.
+// With the chain gone the two query tiles no longer need one thread to hold them in anti-phase, and each tile gets
+// its own issuing thread (warps 1 and 3: a warp can hand over one tcgen05.mma per ~84 clocks, and the twelve
+// instructions of a tile-entry at this size keep the pipe busy for half of that).
+// What P V(X, e) must not overlap is (1) the softmax overwriting P_X with the next entry's values and (2) the softmax
+// rescaling O_X; both wait for the completion of slot e, which the issuers already signal to the producer
+// (kEmpty, one arrival per issuer, committed after the slot's last MMA).
+// ====================================================================================================
+enum BarrierIndex64 {
+  k6QFull = 0,
+  k6KFirst,
+  k6Full0, k6Full1,
+  k6Empty0, k6Empty1,            // slot e: all its MMAs have completed (one arrival per issuer)
+  k6SFullA, k6SFullB,
+  k6SFreeA, k6SFreeB,            // the softmax warpgroup has read S_X into registers (128 arrivals)
+  k6PLoA, k6PHiA, k6PLoB, k6PHiB,
+  k6OFinalA, k6OFinalB,
+  k6NumBarriers
+};
+
+struct __align__(8) Control64 {
+  unsigned long long bars[k6NumBarriers];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr size_t smem_bytes_d64() { return static_cast<size_t>(6) * kTile * 64 * 2 + 1024 + sizeof(Control64); }
+
+// Maximum of 64 values: eight independent chains of three-input max.
+__device__ __forceinline__ float row_max64(const float* v) {
+  float a[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a[i] = ptx::max3(v[i], v[i + 8], v[i + 16]);
+#pragma unroll
+  for (int c = 24; c + 16 <= 64; c += 16)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = ptx::max3(a[i], v[c + i], v[c + i + 8]);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a[i] = fmaxf(a[i], v[56 + i]);
+  return fmaxf(ptx::max3(a[0], a[1], a[2]), ptx::max3(ptx::max3(a[3], a[4], a[5]), a[6], a[7]));
+}
+
+// P = exp2(S * scale - ref) for 64 columns of one row: pk[32] = 16-bit pairs; the row sum goes into the packed sums.
+template <bool kBF16>
+__device__ __forceinline__ void exp_half(const float* v, float scale_log2, float ref, uint32_t* pk, uint64_t& sum2a,
+                                         uint64_t& sum2b) {
+  const uint64_t scale2 = ptx::pack_f32x2(scale_log2, scale_log2);
+  const uint64_t nref2 = ptx::pack_f32x2(-ref, -ref);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const uint64_t x2 = ptx::fma_f32x2(ptx::pack_f32x2(v[2 * i], v[2 * i + 1]), scale2, nref2);
+    float x0, x1;
+    ptx::unpack_f32x2(x2, x0, x1);
+    const float p0 = ptx::ex2(x0), p1 = ptx::ex2(x1);
+    const uint64_t p2 = ptx::pack_f32x2(p0, p1);
+    if (i & 1) sum2b = ptx::add_f32x2(sum2b, p2); else sum2a = ptx::add_f32x2(sum2a, p2);
+    pk[i] = pack2<kBF16>(p0, p1);
+  }
+}
+
+template <bool kBF16>
+__global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
+    const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+    const __grid_constant__ CUtensorMap tm_v, const int32_t* __restrict__ counts,
+    const int32_t* __restrict__ entries, const int32_t* __restrict__ order, int Hm, int ntk, int N, float scale_log2,
+    int q_split, int kvl_lo, int kvl_hi, void* __restrict__ out_raw, float* __restrict__ lse,
+    int32_t* __restrict__ status, const __grid_constant__ OutScatter scatter) {
+  constexpr int D = 64;
+  constexpr int kTileBytes = kTile * D * 2;       // one Q, K or V tile: 128 rows x 128 bytes
+  constexpr uint32_t kIdescQK = ptx::idesc_f16(128, 128, kBF16, false);
+  constexpr uint32_t kIdescPV = ptx::idesc_f16(128, D, kBF16, true);
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Control64* ctl = reinterpret_cast<Control64*>(smem + 6 * kTileBytes);
+  const uint32_t sQ = ptx::smem_u32(smem);
+  const uint32_t sK = sQ + 2 * kTileBytes;
+  const uint32_t sV = sQ + 4 * kTileBytes;
+  const uint32_t bar0 = ptx::smem_u32(&ctl->bars[0]);
+  auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int npairs = static_cast<int>(gridDim.x) / Hm;
+  const int item = order ? order[blockIdx.x] : static_cast<int>(blockIdx.x);
+  const int mh = item / npairs;
+  const int pair = item - mh * npairs;
+  const int bh = blockIdx.y * Hm + mh;
+  const int ntq = (N + kTile - 1) / kTile;
+  const bool has_b = (2 * pair + 1) < ntq;
+  const int cnt = counts[static_cast<int64_t>(mh) * npairs + pair];
+  const int32_t* ent = entries + (static_cast<int64_t>(mh) * npairs + pair) * ntk;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < k6NumBarriers; ++i) {
+      uint32_t c = 1;
+      if (i == k6Empty0 || i == k6Empty1) c = 2;
+      if (i >= k6SFreeA && i <= k6PHiB) c = 128;
+      ptx::mbar_init(bar(i), c);
+    }
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&tm_q);
+    ptx::prefetch_tensormap(&tm_k);
+    ptx::prefetch_tensormap(&tm_v);
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_base), 512);
+    ptx::tmem_relinquish();
+    ptx::tc_fence_before();
+  }
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+
+  // parity with which slot j's completion shows on k6Empty[j & 1] (k6Empty1 also completes once before slot 1:
+  // the first K tile's stage is released after Q K^T of entry 0)
+  auto empty_parity = [](int j) -> uint32_t { return (j & 1) ? (((j + 1) >> 1) & 1) : ((j >> 1) & 1); };
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        ptx::mbar_expect_tx(bar(k6QFull), (has_b ? 2u : 1u) * kTileBytes);
+        for (int x = 0; x < (has_b ? 2 : 1); ++x)
+          ptx::tma_load_3d(sQ + x * kTileBytes, &tm_q, bar(k6QFull), 0, (2 * pair + x) * kTile, bh);
+        bool ok = true;
+        int issued = 0;
+        if (cnt > 0) {
+          ptx::mbar_expect_tx(bar(k6KFirst), kTileBytes);
+          ptx::tma_load_3d(sK, &tm_k, bar(k6KFirst), 0, (ent[0] >> 8) * kTile, bh);
+        }
+        // entry e: V(e) into V stage e & 1 and K(e + 1) into the other K stage, once slot e - 2 has completed
+        for (int e = 0; e < cnt && ok; ++e) {
+          const int s = e & 1;
+          const bool next = (e + 1) < cnt;
+          if (e >= 2 || s == 1) {
+            ok = ptx::mbar_wait(bar(k6Empty0 + s), (e >= 2) ? empty_parity(e - 2) : 0u, abort_flag);
+            if (!ok) { report(status, 1, 0, e); break; }
+          }
+          ptx::mbar_expect_tx(bar(k6Full0 + s), (next ? 2u : 1u) * kTileBytes);
+          ptx::tma_load_3d(sV + s * kTileBytes, &tm_v, bar(k6Full0 + s), 0, (ent[e] >> 8) * kTile, bh);
+          if (next) ptx::tma_load_3d(sK + (s ^ 1) * kTileBytes, &tm_k, bar(k6Full0 + s), 0, (ent[e + 1] >> 8) * kTile, bh);
+          issued = e + 1;
+        }
+        if (!ok) {
+          // give copies in flight a bounded time to land (their barriers may never be consumed)
+          for (int i = 0; i < 4096 && cnt > 0 && !ptx::mbar_try_wait(bar(k6KFirst), 0); ++i) {}
+          for (int e = max(0, issued - 2); e < issued; ++e)
+            for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(k6Full0 + (e & 1)), (e >> 1) & 1); ++i) {}
+        }
+      }
+    } else if (warp == 1 || warp == 3) {
+      // ------------------------------------------------------------------ MMA issuers, one per query tile
+      if (lane == 0) {
+        const int x = warp >> 1;
+        const uint64_t dqx = ptx::smem_desc_sw128(sQ + x * kTileBytes, 16, 1024);
+        const uint64_t dk[2] = {ptx::smem_desc_sw128(sK, 16, 1024), ptx::smem_desc_sw128(sK + kTileBytes, 16, 1024)};
+        const uint64_t dv[2] = {ptx::smem_desc_sw128(sV, kTileBytes, 1024),
+                                ptx::smem_desc_sw128(sV + kTileBytes, kTileBytes, 1024)};
+        const uint32_t tSx = tmem + x * 128, tOx = tmem + 256 + x * D, tPx = tmem + 384 + x * 64;
+        auto advance = [](uint64_t desc, uint32_t bytes) -> uint64_t {
+          return (desc & 0xffffffff00000000ull) | static_cast<uint32_t>(static_cast<uint32_t>(desc) + (bytes >> 4));
+        };
+        auto issue_qk = [&](int s) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk)
+            ptx::mma_ss(tSx, advance(dqx, kk * 32), advance(dk[s], kk * 32), kIdescQK, kk > 0 ? 1u : 0u);
+          ptx::tc_commit(bar(k6SFullA + x));
+        };
+        auto issue_pv_half = [&](int s, int half, uint32_t acc) {
+#pragma unroll
+          for (int kq = 0; kq < 4; ++kq) {
+            const int kk = half * 4 + kq;
+            ptx::mma_ts(tOx, tPx + kk * 8, advance(dv[s], kk * 2048), kIdescPV, (acc || kq > 0) ? 1u : 0u);
+          }
+        };
+        bool ok = ptx::mbar_wait(bar(k6QFull), 0, abort_flag);
+        if (!ok) report(status, 2, 1 + x, -1);
+        int sub = (cnt > 0) ? ((ent[0] >> (4 * x)) & 0xf) : 0;
+        int n_qk = 0;                       // Q K^T products issued so far for this tile
+        if (ok && cnt > 0) {
+          ok = ptx::mbar_wait(bar(k6KFirst), 0, abort_flag);
+          if (!ok) report(status, 2, 1 + x, 0);
+          if (ok) {
+            ptx::tc_fence_after();
+            if (sub) { issue_qk(0); ++n_qk; }
+            ptx::tc_commit(bar(k6Empty1));    // K stage 0 may take the K tile of entry 2
+          }
+        }
+        uint32_t par_p = 0, acc = 0;
+        for (int e = 0; e < cnt && ok; ++e) {
+          const int s = e & 1;
+          const int subn = (e + 1 < cnt) ? ((ent[e + 1] >> (4 * x)) & 0xf) : 0;
+          ok = ptx::mbar_wait(bar(k6Full0 + s), (e >> 1) & 1, abort_flag);
+          if (!ok) { report(status, 2, 1 + x, e); break; }
+          if (subn) {
+            // S_x is free once the softmax has read the scores of the tile's previous entry
+            if (n_qk > 0) {
+              ok = ptx::mbar_wait(bar(k6SFreeA + x), static_cast<uint32_t>((n_qk - 1) & 1), abort_flag);
+              if (!ok) { report(status, 6, 1 + x, e); break; }
+            }
+            ptx::tc_fence_after();
+            issue_qk(s ^ 1);
+            ++n_qk;
+          }
+          if (sub) {
+            ok = ptx::mbar_wait(bar(k6PLoA + 2 * x), par_p, abort_flag);
+            if (!ok) { report(status, 3, 1 + x, e); break; }
+            ptx::tc_fence_after();
+            issue_pv_half(s, 0, acc);
+            ok = ptx::mbar_wait(bar(k6PHiA + 2 * x), par_p, abort_flag);
+            if (!ok) { report(status, 3, 1 + x, e); break; }
+            ptx::tc_fence_after();
+            issue_pv_half(s, 1, 1u);
+            par_p ^= 1;
+            acc = 1u;
+          }
+          ptx::tc_commit(bar(k6Empty0 + s));  // this issuer's MMAs of slot e are done (second arrival: the other tile's)
+          sub = subn;
+        }
+        ptx::tc_commit(bar(k6OFinalA + x));
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int x = (warp - 4) / 4;                 // 0: tile A, 1: tile B
+    const int wq = warp % 4;                      // tensor-memory lane quarter of this warp
+    const int r = wq * 32 + lane;                 // row inside the tile
+    const int tile = 2 * pair + x;
+    const int grow = tile * kTile + r;            // global query row
+    const int kvl = (grow < q_split) ? kvl_lo : kvl_hi;
+    const int kvl_min = min(kvl_lo, kvl_hi);
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t tS = tmem + lane_base + x * 128;
+    const uint32_t tO = tmem + lane_base + 256 + x * D;
+    const uint32_t tP = tmem + lane_base + 384 + x * 64;
+    const int rh = r >> 6;                        // row half of the tile: the same for the whole warp
+
+    float m = -INFINITY, l = 0.f;
+    uint32_t par_s = 0;
+    int done = 0;
+    bool ok = true;
+    for (int e = 0; e < cnt; ++e) {
+      const int en = ent[e];
+      const int sub = (en >> (4 * x)) & 0xf;
+      if (!sub) continue;
+      const int col0 = (en >> 8) * kTile;
+      ok = ptx::mbar_wait(bar(k6SFullA + x), par_s, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { if (lane == 0) report(status, 4, 2 + x, e); break; }
+      par_s ^= 1;
+      ptx::tc_fence_after();
+      // per 64-key half (flags are the same for every thread of the warp): keep = the rows of this warp keep it
+      const bool keep[2] = {((sub >> (2 * rh)) & 1) != 0, ((sub >> (2 * rh + 1)) & 1) != 0};
+      const bool edge = col0 + kTile > kvl_min;   // the tile reaches past the valid keys of some row
+      float v[kTile];
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+        if (keep[half]) {
+          ptx::tmem_ld32(tS + half * 64, reinterpret_cast<uint32_t*>(v) + half * 64);
+          ptx::tmem_ld32(tS + half * 64 + 32, reinterpret_cast<uint32_t*>(v) + half * 64 + 32);
+        }
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar(k6SFreeA + x));        // the next Q K^T of this tile may overwrite S
+      if (edge) {
+        const int lim = kvl - col0;               // columns >= lim are beyond the valid keys of this row
+#pragma unroll
+        for (int c = 0; c < kTile; ++c)
+          if (keep[c / 64]) v[c] = (c < lim) ? v[c] : -INFINITY;
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+        if (keep[half]) mx = fmaxf(mx, row_max64(v + half * 64));
+      const float m_new = fmaxf(m, mx * scale_log2);
+      // everything of the previous slot has completed: P_x may be overwritten and O_x may be rescaled
+      if (e > 0) {
+        ok = ptx::mbar_wait(bar(k6Empty0 + ((e - 1) & 1)), empty_parity(e - 1), abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { if (lane == 0) report(status, 7, 2 + x, e); break; }
+        ptx::tc_fence_after();
+      }
+      if (done == 0) {
+        m = m_new;
+      } else if (__any_sync(0xffffffffu, m_new > m + kRescaleThreshold)) {
+        const float alpha = (m == -INFINITY) ? 0.f : ptx::ex2(m - m_new);
+        l *= alpha;
+        m = m_new;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          float o[32];
+          ptx::tmem_ld32(tO + c * 32, reinterpret_cast<uint32_t*>(o));
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= alpha;
+          ptx::tmem_st32(tO + c * 32, reinterpret_cast<const uint32_t*>(o));
+        }
+      }
+      const float ref = (m == -INFINITY) ? 0.f : m;
+      uint64_t sum2a = 0, sum2b = 0;    // bit pattern of (0.f, 0.f)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t pk[32];
+        if (keep[half]) {
+          exp_half<kBF16>(v + half * 64, scale_log2, ref, pk, sum2a, sum2b);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pk[i] = 0u;   // a half this row half does not keep: no exponentials at all
+        }
+        ptx::tmem_st32(tP + half * 32, pk);
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar(k6PLoA + 2 * x + half));
+      }
+      float s0, s1, s2, s3;
+      ptx::unpack_f32x2(sum2a, s0, s1);
+      ptx::unpack_f32x2(sum2b, s2, s3);
+      l += (s0 + s1) + (s2 + s3);
+      ++done;
+    }
+
+    if (ok) {
+      ok = ptx::mbar_wait(bar(k6OFinalA + x), 0, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok && lane == 0) report(status, 5, 2 + x, -1);
+    }
+    if (ok && tile < ntq) {
+      ptx::tc_fence_after();
+      const float inv = (done > 0 && l > 0.f) ? 1.f / l : 0.f;
+      uint4* dst;
+      if (scatter.n_peers > 0) {
+        const int pr = min(grow / scatter.rows_per_peer, scatter.n_peers - 1);
+        dst = reinterpret_cast<uint4*>(
+            static_cast<unsigned char*>(scatter.peer[pr]) +
+            (static_cast<int64_t>(scatter.head_base + bh) * scatter.rows_per_peer + (grow - pr * scatter.rows_per_peer)) * D * 2);
+      } else {
+        dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(out_raw) + (static_cast<int64_t>(bh) * N + grow) * D * 2);
+      }
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        if (done > 0) {
+          ptx::tmem_ld32(tO + c * 32, reinterpret_cast<uint32_t*>(o));
+          ptx::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+        }
+        if (grow < N) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 w;
+            w.x = pack2<kBF16>(o[q4 * 8 + 0] * inv, o[q4 * 8 + 1] * inv);
+            w.y = pack2<kBF16>(o[q4 * 8 + 2] * inv, o[q4 * 8 + 3] * inv);
+            w.z = pack2<kBF16>(o[q4 * 8 + 4] * inv, o[q4 * 8 + 5] * inv);
+            w.w = pack2<kBF16>(o[q4 * 8 + 6] * inv, o[q4 * 8 + 7] * inv);
+            dst[c * 4 + q4] = w;
+          }
+        }
+      }
+      if (lse != nullptr && grow < N) {
+        lse[static_cast<int64_t>(bh) * N + grow] =
+            (done > 0 && l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, 512);
+  }
+}
+
+template <bool kBF16>
+int launch_d64(const void* q, const void* k, const void* v, int dtype, int BH, int N, const int32_t* counts,
+               const int32_t* entries, const int32_t* order, int Hm, float softmax_scale, int q_split, int kvl_lo,
+               int kvl_hi, void* out, float* lse, int32_t* status, const OutScatter& scatter, cudaStream_t st) {
+  CUtensorMap tq, tk, tv;
+  if (int rc = make_tmap_rows(&tq, q, dtype, BH, N, 64, kTile)) return rc;
+  if (int rc = make_tmap_rows(&tk, k, dtype, BH, N, 64, kTile)) return rc;
+  if (int rc = make_tmap_rows(&tv, v, dtype, BH, N, 64, kTile)) return rc;
+  const int ntq = ceil_div(N, kTile);
+  const int npairs = (ntq + 1) / 2;
+  auto kernel = sparse_attn_fwd_d64_kernel<kBF16>;
+  const size_t smem = smem_bytes_d64();
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
+  const float scale_log2 = softmax_scale * 1.4426950408889634f;
+  kernel<<<dim3(npairs * Hm, BH / Hm), kThreads, smem, st>>>(tq, tk, tv, counts, entries, order, Hm, ntq, N, scale_log2,
+                                                            q_split, kvl_lo, kvl_hi, out, lse, status, scatter);
+  MODDIT_CHECK_LAUNCH("sparse_attn_fwd_d64_kernel");
+  return MODDIT_OK;
+}
+
 template <int D, bool kBF16>
 int launch(const void* q, const void* k, const void* v, int dtype, int BH, int N, const int32_t* counts,
            const int32_t* entries, const int32_t* order, int Hm, float softmax_scale, int q_split, int kvl_lo, int kvl_hi, void* out,
@@ -494,10 +902,17 @@ static int sparse_attn_dispatch(const void* q, const void* k, const void* v, int
                : launch<128, false>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split, kv_len_lo,
                                     kv_len_hi, out, lse, status, scatter, st);
   }
+#ifdef MODDIT_D64_SHARED_KERNEL
   return dtype == MODDIT_BF16 ? launch<64, true>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split,
                                                  kv_len_lo, kv_len_hi, out, lse, status, scatter, st)
                               : launch<64, false>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split,
                                                   kv_len_lo, kv_len_hi, out, lse, status, scatter, st);
+#else
+  return dtype == MODDIT_BF16 ? launch_d64<true>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split,
+                                                 kv_len_lo, kv_len_hi, out, lse, status, scatter, st)
+                              : launch_d64<false>(q, k, v, dtype, BH, N, counts, entries, order, Hm, softmax_scale, q_split,
+                                                  kv_len_lo, kv_len_hi, out, lse, status, scatter, st);
+#endif
 }
 
 extern "C" int moddit_sparse_attn_fwd(const void* q, const void* k, const void* v, int dtype, int BH, int N, int D,
