@@ -458,15 +458,20 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_kernel(
 // its own issuing thread (warps 1 and 3: a warp can hand over one tcgen05.mma per ~84 clocks, and the twelve
 // instructions of a tile-entry at this size keep the pipe busy for half of that).
 // What P V(X, e) must not overlap is (1) the softmax overwriting P_X with the next entry's values and (2) the softmax
-// rescaling O_X; both wait for the completion of slot e, which the issuers already signal to the producer
-// (kEmpty, one arrival per issuer, committed after the slot's last MMA).
+// rescaling O_X; both wait for tile X's issuer to have finished slot e (kDone_X, committed after the issuer's last
+// MMA of the slot), which is also what tells the producer that the slot's K/V stages are free (it waits for both
+// tiles').  The barrier is per tile on purpose: one barrier for both would release the two tiles' exponentials at
+// the same instant, and they share the special-function unit.
 // ====================================================================================================
+constexpr int kStages64 = 4;      // K and V tiles in flight (16 KB each at D = 64: shared memory has room, and a tile
+                                  // requested only one slot ahead does not always arrive within that slot)
 enum BarrierIndex64 {
   k6QFull = 0,
   k6KFirst,
-  k6Full0, k6Full1,
-  k6Empty0, k6Empty1,            // slot e: all its MMAs have completed (one arrival per issuer)
-  k6SFullA, k6SFullB,
+  k6Full0,                                       // [kStages64] V(e) and K(e + 1) have landed (index e % kStages64)
+  k6DoneA0 = k6Full0 + kStages64,                // [kStages64] tile A's issuer has finished all its MMAs of slot e
+  k6DoneB0 = k6DoneA0 + kStages64,               // [kStages64] the same for tile B
+  k6SFullA = k6DoneB0 + kStages64, k6SFullB,
   k6SFreeA, k6SFreeB,            // the softmax warpgroup has read S_X into registers (128 arrivals)
   k6PLoA, k6PHiA, k6PLoB, k6PHiB,
   k6OFinalA, k6OFinalB,
@@ -479,7 +484,9 @@ struct __align__(8) Control64 {
   int abort_flag;
 };
 
-constexpr size_t smem_bytes_d64() { return static_cast<size_t>(6) * kTile * 64 * 2 + 1024 + sizeof(Control64); }
+constexpr size_t smem_bytes_d64() {
+  return static_cast<size_t>(2 + 2 * kStages64) * kTile * 64 * 2 + 1024 + sizeof(Control64);
+}
 
 // Maximum of 64 values: eight independent chains of three-input max.
 __device__ __forceinline__ float row_max64(const float* v) {
@@ -496,17 +503,57 @@ __device__ __forceinline__ float row_max64(const float* v) {
 }
 
 // P = exp2(S * scale - ref) for 64 columns of one row: pk[32] = 16-bit pairs; the row sum goes into the packed sums.
-template <bool kBF16>
+//
+// The exponential unit does 16 results per clock and SM: a 128 x 128 tile of P costs it 1024 clocks, twice what the
+// tensor pipe needs for the tile's two products at D = 64, and with the chain between the products broken it is
+// the unit this kernel waits for.  kPoly of every 8 column pairs are therefore computed on the FMA pipe instead:
+//   2^x = 2^n * p(f),  n = round(x),  f = x - n in [-1/2, 1/2],  p a cubic with relative error 7.5e-5 (a sixth of
+// the rounding step of a bfloat16 P, a sixth of a float16 one's), 2^n added into the exponent field.  x is first
+// clamped to [-120, 8] by a saturating FMA ((x + 120) / 128 in [0, 1]); the upper end is the most the lazily
+// updated row maximum can trail by, and 2^-120 stands in for anything smaller - rows that must give exact zeros
+// (masked columns) use kPoly = 0.
+#ifndef MODDIT_D64_POLY_PAIRS
+#define MODDIT_D64_POLY_PAIRS 0
+#endif
+constexpr int kPolyPairs64 = MODDIT_D64_POLY_PAIRS;
+
+template <bool kBF16, int kPoly>
 __device__ __forceinline__ void exp_half(const float* v, float scale_log2, float ref, uint32_t* pk, uint64_t& sum2a,
                                          uint64_t& sum2b) {
   const uint64_t scale2 = ptx::pack_f32x2(scale_log2, scale_log2);
   const uint64_t nref2 = ptx::pack_f32x2(-ref, -ref);
+  const float pa = scale_log2 * 0.0078125f;
+  const float pb = (120.f - ref) * 0.0078125f;
+  constexpr float kMagic = 12582912.f - 120.f;            // 1.5 * 2^23 - 120: adding it rounds to an integer
+  const uint64_t k128 = ptx::pack_f32x2(128.f, 128.f);
+  const uint64_t kmag = ptx::pack_f32x2(kMagic, kMagic);
+  const uint64_t kneg = ptx::pack_f32x2(-1.f, -1.f);
+  const uint64_t c3 = ptx::pack_f32x2(0.05517167f, 0.05517167f);
+  const uint64_t c2 = ptx::pack_f32x2(0.24261113f, 0.24261113f);
+  const uint64_t c1 = ptx::pack_f32x2(0.69326097f, 0.69326097f);
+  const uint64_t c0 = ptx::pack_f32x2(0.99992806f, 0.99992806f);
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
-    const uint64_t x2 = ptx::fma_f32x2(ptx::pack_f32x2(v[2 * i], v[2 * i + 1]), scale2, nref2);
-    float x0, x1;
-    ptx::unpack_f32x2(x2, x0, x1);
-    const float p0 = ptx::ex2(x0), p1 = ptx::ex2(x1);
+    float p0, p1;
+    if (((i % 8) * kPoly) % 8 < kPoly) {
+      const uint64_t y2 = ptx::pack_f32x2(ptx::fma_sat(v[2 * i], pa, pb), ptx::fma_sat(v[2 * i + 1], pa, pb));
+      const uint64_t r2 = ptx::fma_f32x2(y2, k128, kmag);         // x + 1.5 * 2^23: the integer n sits in the low bits
+      const uint64_t f2 = ptx::fma_f32x2(y2, k128, ptx::fma_f32x2(r2, kneg, kmag));   // x - n
+      uint64_t q2 = ptx::fma_f32x2(f2, c3, c2);
+      q2 = ptx::fma_f32x2(q2, f2, c1);
+      q2 = ptx::fma_f32x2(q2, f2, c0);
+      float r0, r1, q0, q1;
+      ptx::unpack_f32x2(r2, r0, r1);
+      ptx::unpack_f32x2(q2, q0, q1);
+      p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+      p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+    } else {
+      const uint64_t x2 = ptx::fma_f32x2(ptx::pack_f32x2(v[2 * i], v[2 * i + 1]), scale2, nref2);
+      float x0, x1;
+      ptx::unpack_f32x2(x2, x0, x1);
+      p0 = ptx::ex2(x0);
+      p1 = ptx::ex2(x1);
+    }
     const uint64_t p2 = ptx::pack_f32x2(p0, p1);
     if (i & 1) sum2b = ptx::add_f32x2(sum2b, p2); else sum2a = ptx::add_f32x2(sum2a, p2);
     pk[i] = pack2<kBF16>(p0, p1);
@@ -527,10 +574,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  Control64* ctl = reinterpret_cast<Control64*>(smem + 6 * kTileBytes);
+  Control64* ctl = reinterpret_cast<Control64*>(smem + (2 + 2 * kStages64) * kTileBytes);
   const uint32_t sQ = ptx::smem_u32(smem);
   const uint32_t sK = sQ + 2 * kTileBytes;
-  const uint32_t sV = sQ + 4 * kTileBytes;
+  const uint32_t sV = sK + kStages64 * kTileBytes;
   const uint32_t bar0 = ptx::smem_u32(&ctl->bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
   volatile int* abort_flag = &ctl->abort_flag;
@@ -550,7 +597,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
   if (threadIdx.x == 0) {
     for (int i = 0; i < k6NumBarriers; ++i) {
       uint32_t c = 1;
-      if (i == k6Empty0 || i == k6Empty1) c = 2;
       if (i >= k6SFreeA && i <= k6PHiB) c = 128;
       ptx::mbar_init(bar(i), c);
     }
@@ -569,9 +615,12 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
 
-  // parity with which slot j's completion shows on k6Empty[j & 1] (k6Empty1 also completes once before slot 1:
-  // the first K tile's stage is released after Q K^T of entry 0)
-  auto empty_parity = [](int j) -> uint32_t { return (j & 1) ? (((j + 1) >> 1) & 1) : ((j >> 1) & 1); };
+  // Slot j's completion shows on k6Done_X[j % kStages64].  "Slot -1" is the Q K^T of entry 0, issued before the loop:
+  // it shares the last index, whose phases are therefore one ahead of the others'.
+  auto done_index = [](int j) -> int { return (j + kStages64) % kStages64; };
+  auto done_parity = [](int j) -> uint32_t {
+    return static_cast<uint32_t>((((j + kStages64) % kStages64 == kStages64 - 1) ? (j + 1) / kStages64 : j / kStages64) & 1);
+  };
 
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
@@ -587,24 +636,29 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
           ptx::mbar_expect_tx(bar(k6KFirst), kTileBytes);
           ptx::tma_load_3d(sK, &tm_k, bar(k6KFirst), 0, (ent[0] >> 8) * kTile, bh);
         }
-        // entry e: V(e) into V stage e & 1 and K(e + 1) into the other K stage, once slot e - 2 has completed
+        // entry e: V(e) into V stage e % kStages64 and K(e + 1) into K stage (e + 1) % kStages64, once slot
+        // e - kStages64 has completed in both tiles (it read both stages last)
         for (int e = 0; e < cnt && ok; ++e) {
-          const int s = e & 1;
+          const int s = e % kStages64;
           const bool next = (e + 1) < cnt;
-          if (e >= 2 || s == 1) {
-            ok = ptx::mbar_wait(bar(k6Empty0 + s), (e >= 2) ? empty_parity(e - 2) : 0u, abort_flag);
+          if (e >= kStages64 - 1) {
+            const int j = e - kStages64;
+            ok = ptx::mbar_wait(bar(k6DoneA0 + done_index(j)), done_parity(j), abort_flag) &&
+                 ptx::mbar_wait(bar(k6DoneB0 + done_index(j)), done_parity(j), abort_flag);
             if (!ok) { report(status, 1, 0, e); break; }
           }
           ptx::mbar_expect_tx(bar(k6Full0 + s), (next ? 2u : 1u) * kTileBytes);
           ptx::tma_load_3d(sV + s * kTileBytes, &tm_v, bar(k6Full0 + s), 0, (ent[e] >> 8) * kTile, bh);
-          if (next) ptx::tma_load_3d(sK + (s ^ 1) * kTileBytes, &tm_k, bar(k6Full0 + s), 0, (ent[e + 1] >> 8) * kTile, bh);
+          if (next)
+            ptx::tma_load_3d(sK + ((e + 1) % kStages64) * kTileBytes, &tm_k, bar(k6Full0 + s), 0, (ent[e + 1] >> 8) * kTile,
+                             bh);
           issued = e + 1;
         }
         if (!ok) {
           // give copies in flight a bounded time to land (their barriers may never be consumed)
           for (int i = 0; i < 4096 && cnt > 0 && !ptx::mbar_try_wait(bar(k6KFirst), 0); ++i) {}
-          for (int e = max(0, issued - 2); e < issued; ++e)
-            for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(k6Full0 + (e & 1)), (e >> 1) & 1); ++i) {}
+          for (int e = max(0, issued - kStages64); e < issued; ++e)
+            for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bar(k6Full0 + e % kStages64), (e / kStages64) & 1); ++i) {}
         }
       }
     } else if (warp == 1 || warp == 3) {
@@ -612,24 +666,25 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
       if (lane == 0) {
         const int x = warp >> 1;
         const uint64_t dqx = ptx::smem_desc_sw128(sQ + x * kTileBytes, 16, 1024);
-        const uint64_t dk[2] = {ptx::smem_desc_sw128(sK, 16, 1024), ptx::smem_desc_sw128(sK + kTileBytes, 16, 1024)};
-        const uint64_t dv[2] = {ptx::smem_desc_sw128(sV, kTileBytes, 1024),
-                                ptx::smem_desc_sw128(sV + kTileBytes, kTileBytes, 1024)};
+        const uint64_t dk0 = ptx::smem_desc_sw128(sK, 16, 1024);
+        const uint64_t dv0 = ptx::smem_desc_sw128(sV, kTileBytes, 1024);
         const uint32_t tSx = tmem + x * 128, tOx = tmem + 256 + x * D, tPx = tmem + 384 + x * 64;
         auto advance = [](uint64_t desc, uint32_t bytes) -> uint64_t {
           return (desc & 0xffffffff00000000ull) | static_cast<uint32_t>(static_cast<uint32_t>(desc) + (bytes >> 4));
         };
-        auto issue_qk = [&](int s) {
+        auto issue_qk = [&](int s) {          // s: K stage
+          const uint64_t b0 = advance(dk0, static_cast<uint32_t>(s) * kTileBytes);
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk)
-            ptx::mma_ss(tSx, advance(dqx, kk * 32), advance(dk[s], kk * 32), kIdescQK, kk > 0 ? 1u : 0u);
+            ptx::mma_ss(tSx, advance(dqx, kk * 32), advance(b0, kk * 32), kIdescQK, kk > 0 ? 1u : 0u);
           ptx::tc_commit(bar(k6SFullA + x));
         };
-        auto issue_pv_half = [&](int s, int half, uint32_t acc) {
+        auto issue_pv_half = [&](int s, int half, uint32_t acc) {   // s: V stage
+          const uint64_t b0 = advance(dv0, static_cast<uint32_t>(s) * kTileBytes);
 #pragma unroll
           for (int kq = 0; kq < 4; ++kq) {
             const int kk = half * 4 + kq;
-            ptx::mma_ts(tOx, tPx + kk * 8, advance(dv[s], kk * 2048), kIdescPV, (acc || kq > 0) ? 1u : 0u);
+            ptx::mma_ts(tOx, tPx + kk * 8, advance(b0, kk * 2048), kIdescPV, (acc || kq > 0) ? 1u : 0u);
           }
         };
         bool ok = ptx::mbar_wait(bar(k6QFull), 0, abort_flag);
@@ -642,14 +697,14 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
           if (ok) {
             ptx::tc_fence_after();
             if (sub) { issue_qk(0); ++n_qk; }
-            ptx::tc_commit(bar(k6Empty1));    // K stage 0 may take the K tile of entry 2
+            ptx::tc_commit(bar(k6DoneA0 + kStages64 * x + kStages64 - 1));   // "slot -1": K stage 0 is free again
           }
         }
         uint32_t par_p = 0, acc = 0;
         for (int e = 0; e < cnt && ok; ++e) {
-          const int s = e & 1;
+          const int s = e % kStages64;
           const int subn = (e + 1 < cnt) ? ((ent[e + 1] >> (4 * x)) & 0xf) : 0;
-          ok = ptx::mbar_wait(bar(k6Full0 + s), (e >> 1) & 1, abort_flag);
+          ok = ptx::mbar_wait(bar(k6Full0 + s), (e / kStages64) & 1, abort_flag);
           if (!ok) { report(status, 2, 1 + x, e); break; }
           if (subn) {
             // S_x is free once the softmax has read the scores of the tile's previous entry
@@ -658,7 +713,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
               if (!ok) { report(status, 6, 1 + x, e); break; }
             }
             ptx::tc_fence_after();
-            issue_qk(s ^ 1);
+            issue_qk((e + 1) % kStages64);
             ++n_qk;
           }
           if (sub) {
@@ -673,7 +728,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
             par_p ^= 1;
             acc = 1u;
           }
-          ptx::tc_commit(bar(k6Empty0 + s));  // this issuer's MMAs of slot e are done (second arrival: the other tile's)
+          ptx::tc_commit(bar(k6DoneA0 + kStages64 * x + s));  // this tile's MMAs of slot e are done
           sub = subn;
         }
         ptx::tc_commit(bar(k6OFinalA + x));
@@ -733,9 +788,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
       for (int half = 0; half < 2; ++half)
         if (keep[half]) mx = fmaxf(mx, row_max64(v + half * 64));
       const float m_new = fmaxf(m, mx * scale_log2);
-      // everything of the previous slot has completed: P_x may be overwritten and O_x may be rescaled
+      // this tile's products of the previous slot have completed: P_x may be overwritten and O_x may be rescaled
       if (e > 0) {
-        ok = ptx::mbar_wait(bar(k6Empty0 + ((e - 1) & 1)), empty_parity(e - 1), abort_flag);
+        ok = ptx::mbar_wait(bar(k6DoneA0 + kStages64 * x + done_index(e - 1)), done_parity(e - 1), abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { if (lane == 0) report(status, 7, 2 + x, e); break; }
         ptx::tc_fence_after();
@@ -762,7 +817,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
       for (int half = 0; half < 2; ++half) {
         uint32_t pk[32];
         if (keep[half]) {
-          exp_half<kBF16>(v + half * 64, scale_log2, ref, pk, sum2a, sum2b);
+          if (edge) exp_half<kBF16, 0>(v + half * 64, scale_log2, ref, pk, sum2a, sum2b);   // may hold -inf: exact zeros
+          else exp_half<kBF16, kPolyPairs64>(v + half * 64, scale_log2, ref, pk, sum2a, sum2b);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) pk[i] = 0u;   // a half this row half does not keep: no exponentials at all
