@@ -689,7 +689,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
         };
         bool ok = ptx::mbar_wait(bar(k6QFull), 0, abort_flag);
         if (!ok) report(status, 2, 1 + x, -1);
+        // flags of entry e, e + 1 and e + 2: each is loaded two slots before the issuer needs it (a load issued
+        // where its value is used would put a trip to the L2 on the issuing thread's path every slot)
         int sub = (cnt > 0) ? ((ent[0] >> (4 * x)) & 0xf) : 0;
+        int subn = (cnt > 1) ? ((ent[1] >> (4 * x)) & 0xf) : 0;
         int n_qk = 0;                       // Q K^T products issued so far for this tile
         if (ok && cnt > 0) {
           ok = ptx::mbar_wait(bar(k6KFirst), 0, abort_flag);
@@ -703,7 +706,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
         uint32_t par_p = 0, acc = 0;
         for (int e = 0; e < cnt && ok; ++e) {
           const int s = e % kStages64;
-          const int subn = (e + 1 < cnt) ? ((ent[e + 1] >> (4 * x)) & 0xf) : 0;
+          const int subnn = (e + 2 < cnt) ? ((ent[e + 2] >> (4 * x)) & 0xf) : 0;   // first used in the next slot
           ok = ptx::mbar_wait(bar(k6Full0 + s), (e / kStages64) & 1, abort_flag);
           if (!ok) { report(status, 2, 1 + x, e); break; }
           if (subn) {
@@ -730,6 +733,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
           }
           ptx::tc_commit(bar(k6DoneA0 + kStages64 * x + s));  // this tile's MMAs of slot e are done
           sub = subn;
+          subn = subnn;
         }
         ptx::tc_commit(bar(k6OFinalA + x));
       }
@@ -754,8 +758,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_fwd_d64_kernel(
     uint32_t par_s = 0;
     int done = 0;
     bool ok = true;
+    int en_next = (cnt > 0) ? ent[0] : 0;
     for (int e = 0; e < cnt; ++e) {
-      const int en = ent[e];
+      const int en = en_next;
+      en_next = (e + 1 < cnt) ? ent[e + 1] : 0;   // in flight while this entry is processed
       const int sub = (en >> (4 * x)) & 0xf;
       if (!sub) continue;
       const int col0 = (en >> 8) * kTile;
