@@ -80,6 +80,17 @@ int moddit_pooled_map(const float* qbar, const float* kbar, int BH, int nb, int 
                       int q_block_offset, int k_block_offset, int n, float scale,
                       void* map_f16, void* stream);
 
+/* The same map, bit for bit, in two launches through a caller-owned float32 workspace of
+ * moddit_pooled_map_workspace_bytes(BH, n) = 4 * BH * n * n bytes (16-byte aligned): the logits become a batched
+ * matrix product with one CTA per 64 x 128 tile, and a second kernel takes the row maxima.  About four times
+ * faster than the one-launch form at 24 heads x 900 blocks, and it keeps its speed when a rank holds few heads;
+ * no limit on n from shared memory.
+ */
+size_t moddit_pooled_map_workspace_bytes(int BH, int n);
+int moddit_pooled_map_ws(const float* qbar, const float* kbar, int BH, int nb, int D,
+                         int q_block_offset, int k_block_offset, int n, float scale,
+                         void* map_f16, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Exact sparsity-map replay.  Replaces the pybind function `sparsity_map(q,k,lse,scale,log_thr,
  * q_off,k_off,video_blocks,block_size)` of MoD/mod/cuda_flash_sparsity_kernel.cu:289-334 (kernel

@@ -367,6 +367,128 @@ __global__ void __launch_bounds__(kMapThreads) pooled_map_kernel(const float* __
   }
 }
 
+// ---- the same map in two launches, through a float32 workspace -----------------------------------------------------
+// The kernel above keeps a CTA's 32 x n logits in shared memory so that one launch can take the row maxima: one CTA
+// per SM, every CTA walking all n key blocks tile by tile behind block-wide barriers - 45 us per CTA at n = 900,
+// 4.7 waves of them at 24 heads, and the same 45 us when a rank holds three heads and the grid is less than a wave.
+// With a workspace the logits are a plain batched matrix product with no dependence between tiles: one CTA per
+// 64 x 128 tile (two per SM), one round of loads each; a second kernel takes the row maxima and writes the float16
+// map (a warp per row; the workspace is still in the L2).  Fragments, split and accumulation order are those of the
+// kernel above, so the two routes give the same bits.
+constexpr int kLgRows = 64;     // query blocks per CTA
+constexpr int kLgCols = 128;    // key blocks per CTA
+
+// rows [row0, row0 + kRows) of a (n, D) float32 matrix -> bfloat16 head / remainder rows in shared memory
+template <int kRows>
+__device__ __forceinline__ void stage_split_rows(const float* __restrict__ src, int row0, int n, int D, float scale,
+                                                 __nv_bfloat16* hi_rows, __nv_bfloat16* lo_rows, int ld, int tid) {
+  const int d4 = D / 4;
+  for (int e0 = tid; e0 < kRows * d4; e0 += 8 * kMapThreads) {
+    float4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = e0 + u * kMapThreads;
+      const int r = e / d4, c = e - r * d4;
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (e < kRows * d4 && row0 + r < n)
+        v[u] = __ldg(reinterpret_cast<const float4*>(src + static_cast<int64_t>(row0 + r) * D) + c);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = e0 + u * kMapThreads;
+      if (e >= kRows * d4) break;
+      const int r = e / d4, c = e - r * d4;
+      v[u].x *= scale; v[u].y *= scale; v[u].z *= scale; v[u].w *= scale;
+      uint2 hi, lo;
+      split4(v[u], hi, lo);
+      *reinterpret_cast<uint2*>(hi_rows + r * ld + 4 * c) = hi;
+      *reinterpret_cast<uint2*>(lo_rows + r * ld + 4 * c) = lo;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kMapThreads, 2) pooled_logits_kernel(const float* __restrict__ qbar,
+                                                                       const float* __restrict__ kbar, int nb, int D,
+                                                                       int q_off, int k_off, int n, float scale,
+                                                                       float* __restrict__ lg) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int ld = D + 8;
+  __nv_bfloat16* qhi = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [kLgRows][ld]
+  __nv_bfloat16* qlo = qhi + kLgRows * ld;
+  __nv_bfloat16* khi = qlo + kLgRows * ld;                               // [kLgCols][ld]
+  __nv_bfloat16* klo = khi + kLgCols * ld;
+  const int bh = blockIdx.z;
+  const int i0 = blockIdx.y * kLgRows;
+  const int j0 = blockIdx.x * kLgCols;
+  const int tid = threadIdx.x;
+  const int warp = tid / 32, lane = tid % 32;
+  stage_split_rows<kLgRows>(qbar + (static_cast<int64_t>(bh) * nb + q_off) * D, i0, n, D, scale, qhi, qlo, ld, tid);
+  stage_split_rows<kLgCols>(kbar + (static_cast<int64_t>(bh) * nb + k_off) * D, j0, n, D, 1.f, khi, klo, ld, tid);
+  __syncthreads();
+  const uint32_t a_off = static_cast<uint32_t>(((lane % 16) * ld + (lane / 16) * 8) * 2);
+  const uint32_t b_off = static_cast<uint32_t>(((16 * warp + (lane / 16) * 8 + (lane % 8)) * ld + ((lane / 8) % 2) * 8) * 2);
+  const uint32_t s_qhi = static_cast<uint32_t>(__cvta_generic_to_shared(qhi));
+  const uint32_t s_qlo = static_cast<uint32_t>(__cvta_generic_to_shared(qlo));
+  const uint32_t s_khi = static_cast<uint32_t>(__cvta_generic_to_shared(khi));
+  const uint32_t s_klo = static_cast<uint32_t>(__cvta_generic_to_shared(klo));
+  const int g = lane / 4, t2 = 2 * (lane % 4);
+  constexpr int kMT = kLgRows / 16;
+  float acc[kMT][2][4];
+#pragma unroll
+  for (int mt = 0; mt < kMT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+  for (int ks = 0; ks < D / 16; ++ks) {
+    uint32_t bh_[4], bl_[4];
+    ldmatrix_x4(bh_, s_khi + b_off + ks * 32);
+    ldmatrix_x4(bl_, s_klo + b_off + ks * 32);
+#pragma unroll
+    for (int mt = 0; mt < kMT; ++mt) {
+      uint32_t ah[4], al[4];
+      ldmatrix_x4(ah, s_qhi + a_off + (mt * 16 * ld + ks * 16) * 2);
+      ldmatrix_x4(al, s_qlo + a_off + (mt * 16 * ld + ks * 16) * 2);
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        mma_bf16(acc[mt][nt], al, bh_[2 * nt], bh_[2 * nt + 1]);      // small terms first
+        mma_bf16(acc[mt][nt], ah, bl_[2 * nt], bl_[2 * nt + 1]);
+        mma_bf16(acc[mt][nt], ah, bh_[2 * nt], bh_[2 * nt + 1]);
+      }
+    }
+  }
+  float* dst = lg + static_cast<int64_t>(bh) * n * n;
+#pragma unroll
+  for (int mt = 0; mt < kMT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = i0 + mt * 16 + g + 8 * (i / 2);
+        const int j = j0 + 16 * warp + 8 * nt + t2 + (i % 2);
+        if (r < n && j < n) dst[static_cast<int64_t>(r) * n + j] = acc[mt][nt][i];
+      }
+}
+
+// darkness = 1 - exp(logit - row maximum), a warp per row of the workspace
+__global__ void __launch_bounds__(kMapThreads) pooled_darkness_kernel(const float* __restrict__ lg, int64_t rows, int n,
+                                                                      __half* __restrict__ map) {
+  const int lane = threadIdx.x % 32;
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * (kMapThreads / 32) + threadIdx.x / 32;
+  if (r >= rows) return;
+  const float* row = lg + r * n;
+  float m = -INFINITY;
+  for (int j = lane; j < n; j += 32) m = fmaxf(m, row[j]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __half* dst = map + r * n;
+  for (int j = lane; j < n; j += 32) dst[j] = __float2half_rn(1.f - expf(row[j] - m));
+}
+
+size_t pooled_logits_smem(int D) {
+  return sizeof(__nv_bfloat16) * static_cast<size_t>(2 * (kLgRows + kLgCols)) * (D + 8);
+}
+
 size_t pooled_map_smem(int D, int n) {
   return sizeof(__nv_bfloat16) * (static_cast<size_t>(2 * (kMapRows + kMapCols)) * (D + 8)) +
          sizeof(float) * static_cast<size_t>(kMapRows) * n;
@@ -492,6 +614,42 @@ extern "C" int moddit_pooled_map(const float* qbar, const float* kbar, int BH, i
   pooled_map_kernel<<<dim3(ceil_div(n, kMapRows), BH), kMapThreads, sm, st>>>(qbar, kbar, nb, D, q_block_offset,
                                                                                k_block_offset, n, scale, map);
   MODDIT_CHECK_LAUNCH("pooled_map_kernel");
+  return MODDIT_OK;
+}
+
+extern "C" size_t moddit_pooled_map_workspace_bytes(int BH, int n) {
+  if (BH <= 0 || n <= 0) return 0;
+  return sizeof(float) * static_cast<size_t>(BH) * static_cast<size_t>(n) * static_cast<size_t>(n);
+}
+
+extern "C" int moddit_pooled_map_ws(const float* qbar, const float* kbar, int BH, int nb, int D, int q_block_offset,
+                                    int k_block_offset, int n, float scale, void* map_f16, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(qbar && kbar && map_f16 && workspace, "pooled_map_ws: null pointer");
+  MODDIT_CHECK_ARG(BH > 0 && nb > 0 && n > 0 && D > 0, "pooled_map_ws: sizes must be positive");
+  MODDIT_CHECK_ARG(q_block_offset >= 0 && k_block_offset >= 0 && q_block_offset + n <= nb && k_block_offset + n <= nb,
+                   "pooled_map_ws: video region [%d+%d) / [%d+%d) exceeds %d blocks", q_block_offset, n,
+                   k_block_offset, n, nb);
+  MODDIT_CHECK_ARG(workspace_bytes >= moddit_pooled_map_workspace_bytes(BH, n),
+                   "pooled_map_ws: workspace of %zu bytes, %zu needed", workspace_bytes,
+                   moddit_pooled_map_workspace_bytes(BH, n));
+  if (BH > 65535) return fail(MODDIT_E_UNSUPPORTED, "pooled_map_ws: BH=%d exceeds 65535", BH);
+  if ((D & 15) != 0 || D > 256 || !aligned16(qbar) || !aligned16(kbar) || !aligned16(workspace))
+    return fail(MODDIT_E_ALIGN,
+                "pooled_map_ws: head_dim must be a multiple of 16 (at most 256), inputs and workspace 16-byte aligned");
+  if (int rc = require_sm100()) return rc;
+  cudaStream_t st = as_stream(stream);
+  const size_t sm = pooled_logits_smem(D);
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(pooled_logits_kernel), sm)) return rc;
+  float* lg = static_cast<float*>(workspace);
+  pooled_logits_kernel<<<dim3(ceil_div(n, kLgCols), ceil_div(n, kLgRows), BH), kMapThreads, sm, st>>>(
+      qbar, kbar, nb, D, q_block_offset, k_block_offset, n, scale, lg);
+  MODDIT_CHECK_LAUNCH("pooled_logits_kernel");
+  const int64_t rows = static_cast<int64_t>(BH) * n;
+  pooled_darkness_kernel<<<static_cast<unsigned>((rows + kMapThreads / 32 - 1) / (kMapThreads / 32)), kMapThreads, 0, st>>>(
+      lg, rows, n, static_cast<__half*>(map_f16));
+  MODDIT_CHECK_LAUNCH("pooled_darkness_kernel");
   return MODDIT_OK;
 }
 

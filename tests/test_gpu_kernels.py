@@ -76,17 +76,33 @@ def test_copy_rows_dma_and_kernel_agree(ops):
         assert float(dst[:, 832:].abs().sum()) == 0.0
 
 
-@pytest.mark.parametrize("n,nb,qo,D", [(20, 22, 0, 128), (37, 40, 3, 64), (70, 70, 0, 128)])
+@pytest.mark.parametrize("n,nb,qo,D", [(20, 22, 0, 128), (37, 40, 3, 64), (70, 70, 0, 128), (300, 302, 2, 128),
+                                       (705, 705, 0, 64)])
 def test_pooled_map(ops, n, nb, qo, D):
     torch.manual_seed(1)
     qbar = torch.randn(1, 2, nb, D)
     kbar = torch.randn(1, 2, nb, D)
     scale = D ** -0.5
     ref = orc.pooled_darkness_map(qbar, kbar, q_block_offset=qo, k_block_offset=qo, video_blocks=n, scale=scale)
-    got = ops.pooled_map(qbar.cuda(), kbar.cuda(), q_block_offset=qo, k_block_offset=qo, video_blocks=n,
-                         scale=scale).cpu()
-    assert got.dtype == torch.float16 and got.shape == ref.shape
-    assert (got.float() - ref.float()).abs().max().item() <= 2e-3       # one fp16 ulp near 1.0 is 4.9e-4
+    got = {}
+    for launches in (1, 2):       # one kernel with the rows in shared memory / two kernels through a workspace
+        got[launches] = ops.pooled_map(qbar.cuda(), kbar.cuda(), q_block_offset=qo, k_block_offset=qo,
+                                       video_blocks=n, scale=scale, launches=launches).cpu()
+        assert got[launches].dtype == torch.float16 and got[launches].shape == ref.shape
+        assert (got[launches].float() - ref.float()).abs().max().item() <= 2e-3   # one fp16 ulp near 1.0 is 4.9e-4
+    assert torch.equal(got[1], got[2])          # same fragments, same accumulation order: same bits
+
+
+def test_pooled_map_workspace_checked(ops):
+    from moddit_b200._lib import lib
+    qbar = torch.randn(1, 2, 40, 64, device="cuda")
+    out = torch.empty(1, 2, 40, 40, device="cuda", dtype=torch.float16)
+    need = int(lib.moddit_pooled_map_workspace_bytes(2, 40))
+    assert need == 4 * 2 * 40 * 40
+    ws = torch.empty(need, device="cuda", dtype=torch.uint8)
+    rc = lib.moddit_pooled_map_ws(qbar.data_ptr(), qbar.data_ptr(), 2, 40, 64, 0, 0, 40, 0.125, out.data_ptr(),
+                                  ws.data_ptr(), need - 1, None)
+    assert rc != 0 and b"workspace" in lib.moddit_last_error_string()
 
 
 def _grid_map(H, n, bs, seed):
