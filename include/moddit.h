@@ -80,13 +80,14 @@ int moddit_pooled_map(const float* qbar, const float* kbar, int BH, int nb, int 
                       int q_block_offset, int k_block_offset, int n, float scale,
                       void* map_f16, void* stream);
 
-/* The same map, bit for bit, in two launches through a caller-owned float32 workspace of
- * moddit_pooled_map_workspace_bytes(BH, n) = 4 * BH * n * n bytes (16-byte aligned): the logits become a batched
- * matrix product with one CTA per 64 x 128 tile, and a second kernel takes the row maxima.  About four times
- * faster than the one-launch form at 24 heads x 900 blocks, and it keeps its speed when a rank holds few heads;
- * no limit on n from shared memory.
+/* The same map, bit for bit, in three small launches through a caller-owned workspace of
+ * moddit_pooled_map_workspace_bytes(BH, n, D) bytes (16-byte aligned; 4 * BH * n * n for float32 logits plus
+ * 8 * BH * n * D for the means split into bfloat16 head / remainder rows): the logits become a batched matrix
+ * product with one CTA per 64 x 128 tile, and a last kernel takes the row maxima.  Several times faster than the
+ * one-launch form at 24 heads x 900 blocks, and it keeps its speed when a rank holds few heads; no limit on n from
+ * shared memory.
  */
-size_t moddit_pooled_map_workspace_bytes(int BH, int n);
+size_t moddit_pooled_map_workspace_bytes(int BH, int n, int D);
 int moddit_pooled_map_ws(const float* qbar, const float* kbar, int BH, int nb, int D,
                          int q_block_offset, int k_block_offset, int n, float scale,
                          void* map_f16, void* workspace, size_t workspace_bytes, void* stream);

@@ -416,30 +416,49 @@ __global__ void __launch_bounds__(kSolveThreads) solve_rhs_kernel(const float* _
 // thread i walks column i and consecutive threads read consecutive addresses).  The inner index is split
 // over blockIdx.z so that the whole GPU takes part: a single pass over it is bound by load latency.
 constexpr int kGemvSplit = 16;
+constexpr int kGemvHeads = 4;     // heads per CTA: an element of Sinv is loaded once for all of them
 __global__ void __launch_bounds__(128) solve_gemv_kernel(const double* __restrict__ Sinv,
-                                                         const double* __restrict__ g, int m,
+                                                         const double* __restrict__ g, int m, int H,
                                                          double* __restrict__ y) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  double* gs = reinterpret_cast<double*>(smem_raw);
-  const int h = blockIdx.y;
+  double* gs = reinterpret_cast<double*>(smem_raw);      // [kGemvHeads][per]
+  const int h0 = blockIdx.y * kGemvHeads;
   const int per = (m + kGemvSplit - 1) / kGemvSplit;
   const int j0 = blockIdx.z * per;
   const int j1 = min(m, j0 + per);
-  for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) gs[j - j0] = g[static_cast<int64_t>(h) * m + j];
+  for (int e = threadIdx.x; e < kGemvHeads * per; e += blockDim.x) {
+    const int hh = e / per, j = j0 + (e - hh * per);
+    gs[e] = (h0 + hh < H && j < j1) ? g[static_cast<int64_t>(h0 + hh) * m + j] : 0.0;
+  }
   __syncthreads();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= m) return;
-  double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+  // per head the same four chains, in the same order, as a one-head pass would use
+  double a[kGemvHeads][4];
+#pragma unroll
+  for (int hh = 0; hh < kGemvHeads; ++hh)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) a[hh][c] = 0.0;
   int j = j0;
   for (; j + 3 < j1; j += 4) {
-    a0 = fma(Sinv[static_cast<int64_t>(j) * m + i], gs[j - j0], a0);
-    a1 = fma(Sinv[static_cast<int64_t>(j + 1) * m + i], gs[j + 1 - j0], a1);
-    a2 = fma(Sinv[static_cast<int64_t>(j + 2) * m + i], gs[j + 2 - j0], a2);
-    a3 = fma(Sinv[static_cast<int64_t>(j + 3) * m + i], gs[j + 3 - j0], a3);
+    double s[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) s[c] = Sinv[static_cast<int64_t>(j + c) * m + i];
+#pragma unroll
+    for (int hh = 0; hh < kGemvHeads; ++hh)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) a[hh][c] = fma(s[c], gs[hh * per + (j + c - j0)], a[hh][c]);
   }
-  for (; j < j1; ++j) a0 = fma(Sinv[static_cast<int64_t>(j) * m + i], gs[j - j0], a0);
+  for (; j < j1; ++j) {
+    const double s = Sinv[static_cast<int64_t>(j) * m + i];
+#pragma unroll
+    for (int hh = 0; hh < kGemvHeads; ++hh) a[hh][0] = fma(s, gs[hh * per + (j - j0)], a[hh][0]);
+  }
   // slice partial: y is laid out [slice][head][m]; the back-substitution adds the slices in a fixed order
-  y[(static_cast<int64_t>(blockIdx.z) * gridDim.y + h) * m + i] = (a0 + a1) + (a2 + a3);
+#pragma unroll
+  for (int hh = 0; hh < kGemvHeads; ++hh)
+    if (h0 + hh < H)
+      y[(static_cast<int64_t>(blockIdx.z) * H + (h0 + hh)) * m + i] = (a[hh][0] + a[hh][1]) + (a[hh][2] + a[hh][3]);
 }
 
 __global__ void __launch_bounds__(kSolveThreads) solve_back_kernel(const float* __restrict__ mts,
@@ -711,8 +730,8 @@ extern "C" int moddit_solve(const float* mts, const void* factor, int H, int n, 
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(solve_rhs_kernel), sm_rhs)) return rc;
   solve_rhs_kernel<<<H, kSolveThreads, sm_rhs, st>>>(mts, w, wb, n, g);
   MODDIT_CHECK_LAUNCH("solve_rhs_kernel");
-  solve_gemv_kernel<<<dim3(ceil_div(m, 128), H, kGemvSplit), 128, sizeof(double) * ceil_div(m, kGemvSplit), st>>>(
-      Sinv, g, m, y);
+  solve_gemv_kernel<<<dim3(ceil_div(m, 128), ceil_div(H, kGemvHeads), kGemvSplit), 128,
+                      sizeof(double) * kGemvHeads * ceil_div(m, kGemvSplit), st>>>(Sinv, g, m, H, y);
   MODDIT_CHECK_LAUNCH("solve_gemv_kernel");
   solve_back_kernel<<<H, kSolveThreads, sm_back, st>>>(mts, w, wb, y, n, X);
   MODDIT_CHECK_LAUNCH("solve_back_kernel");

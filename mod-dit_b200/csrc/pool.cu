@@ -367,50 +367,63 @@ __global__ void __launch_bounds__(kMapThreads) pooled_map_kernel(const float* __
   }
 }
 
-// ---- the same map in two launches, through a float32 workspace -----------------------------------------------------
+// ---- the same map in three small launches, through a workspace ------------------------------------------------------
 // The kernel above keeps a CTA's 32 x n logits in shared memory so that one launch can take the row maxima: one CTA
 // per SM, every CTA walking all n key blocks tile by tile behind block-wide barriers - 45 us per CTA at n = 900,
 // 4.7 waves of them at 24 heads, and the same 45 us when a rank holds three heads and the grid is less than a wave.
-// With a workspace the logits are a plain batched matrix product with no dependence between tiles: one CTA per
-// 64 x 128 tile (two per SM), one round of loads each; a second kernel takes the row maxima and writes the float16
-// map (a warp per row; the workspace is still in the L2).  Fragments, split and accumulation order are those of the
-// kernel above, so the two routes give the same bits.
+// With a workspace the logits are a plain batched matrix product with no dependence between tiles:
+//   1. the scaled query means and the key means of the video region are split into bfloat16 head / remainder rows
+//      once (every logit tile would otherwise redo the split of the rows it stages),
+//   2. one CTA per 64 x 128 logit tile (two per SM) copies its rows with cp.async - all of a CTA's copies in
+//      flight at once, no registers in between - and writes float32 logits,
+//   3. a warp per row takes the maximum and writes the float16 map (the logits are still in the L2).
+// Fragments, split and accumulation order are those of the kernel above, so the two routes give the same bits.
 constexpr int kLgRows = 64;     // query blocks per CTA
 constexpr int kLgCols = 128;    // key blocks per CTA
 
-// rows [row0, row0 + kRows) of a (n, D) float32 matrix -> bfloat16 head / remainder rows in shared memory
-template <int kRows>
-__device__ __forceinline__ void stage_split_rows(const float* __restrict__ src, int row0, int n, int D, float scale,
-                                                 __nv_bfloat16* hi_rows, __nv_bfloat16* lo_rows, int ld, int tid) {
+// (BH, nb, D) float32 -> rows [off, off + n) as (BH, n, 2, D) bfloat16: head row, then remainder row
+__global__ void __launch_bounds__(256) split_means_kernel(const float* __restrict__ qbar, const float* __restrict__ kbar,
+                                                          int nb, int D, int q_off, int k_off, int n, float scale,
+                                                          int64_t total4, __nv_bfloat16* __restrict__ qs,
+                                                          __nv_bfloat16* __restrict__ ks) {
+  const int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= total4) return;
+  const bool is_k = blockIdx.y != 0;
   const int d4 = D / 4;
-  for (int e0 = tid; e0 < kRows * d4; e0 += 8 * kMapThreads) {
-    float4 v[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int e = e0 + u * kMapThreads;
-      const int r = e / d4, c = e - r * d4;
-      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (e < kRows * d4 && row0 + r < n)
-        v[u] = __ldg(reinterpret_cast<const float4*>(src + static_cast<int64_t>(row0 + r) * D) + c);
-    }
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int e = e0 + u * kMapThreads;
-      if (e >= kRows * d4) break;
-      const int r = e / d4, c = e - r * d4;
-      v[u].x *= scale; v[u].y *= scale; v[u].z *= scale; v[u].w *= scale;
-      uint2 hi, lo;
-      split4(v[u], hi, lo);
-      *reinterpret_cast<uint2*>(hi_rows + r * ld + 4 * c) = hi;
-      *reinterpret_cast<uint2*>(lo_rows + r * ld + 4 * c) = lo;
-    }
+  const int c = static_cast<int>(e % d4);
+  const int64_t row = e / d4;                    // bh * n + r
+  const int64_t bh = row / n;
+  const int r = static_cast<int>(row - bh * n);
+  const float* src = (is_k ? kbar : qbar) + ((bh * nb + (is_k ? k_off : q_off) + r) * D);
+  float4 v = __ldg(reinterpret_cast<const float4*>(src) + c);
+  if (!is_k) { v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale; }
+  uint2 hi, lo;
+  split4(v, hi, lo);
+  __nv_bfloat16* dst = (is_k ? ks : qs) + row * 2 * D;
+  *reinterpret_cast<uint2*>(dst + 4 * c) = hi;
+  *reinterpret_cast<uint2*>(dst + D + 4 * c) = lo;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(src) : "memory");
+}
+
+// rows [row0, row0 + kRows) of a split matrix (rows past n - 1 repeat row n - 1: their logits are never stored)
+template <int kRows>
+__device__ __forceinline__ void stage_split_rows(const __nv_bfloat16* __restrict__ src, int row0, int n, int D,
+                                                 uint32_t s_hi, uint32_t s_lo, int ld, int tid) {
+  const int cpr = D / 8;                          // 16-byte chunks per row half
+  for (int e = tid; e < kRows * 2 * cpr; e += kMapThreads) {
+    const int r = e / (2 * cpr), w = e - r * 2 * cpr;
+    const int part = w / cpr, c = w - part * cpr;
+    const __nv_bfloat16* g = src + (static_cast<int64_t>(min(row0 + r, n - 1)) * 2 + part) * D + 8 * c;
+    cp_async16((part ? s_lo : s_hi) + static_cast<uint32_t>((r * ld + 8 * c) * 2), g);
   }
 }
 
-__global__ void __launch_bounds__(kMapThreads, 2) pooled_logits_kernel(const float* __restrict__ qbar,
-                                                                       const float* __restrict__ kbar, int nb, int D,
-                                                                       int q_off, int k_off, int n, float scale,
-                                                                       float* __restrict__ lg) {
+__global__ void __launch_bounds__(kMapThreads, 2) pooled_logits_kernel(const __nv_bfloat16* __restrict__ qs,
+                                                                       const __nv_bfloat16* __restrict__ ks, int D,
+                                                                       int n, float* __restrict__ lg) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int ld = D + 8;
   __nv_bfloat16* qhi = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [kLgRows][ld]
@@ -422,15 +435,17 @@ __global__ void __launch_bounds__(kMapThreads, 2) pooled_logits_kernel(const flo
   const int j0 = blockIdx.x * kLgCols;
   const int tid = threadIdx.x;
   const int warp = tid / 32, lane = tid % 32;
-  stage_split_rows<kLgRows>(qbar + (static_cast<int64_t>(bh) * nb + q_off) * D, i0, n, D, scale, qhi, qlo, ld, tid);
-  stage_split_rows<kLgCols>(kbar + (static_cast<int64_t>(bh) * nb + k_off) * D, j0, n, D, 1.f, khi, klo, ld, tid);
-  __syncthreads();
-  const uint32_t a_off = static_cast<uint32_t>(((lane % 16) * ld + (lane / 16) * 8) * 2);
-  const uint32_t b_off = static_cast<uint32_t>(((16 * warp + (lane / 16) * 8 + (lane % 8)) * ld + ((lane / 8) % 2) * 8) * 2);
   const uint32_t s_qhi = static_cast<uint32_t>(__cvta_generic_to_shared(qhi));
   const uint32_t s_qlo = static_cast<uint32_t>(__cvta_generic_to_shared(qlo));
   const uint32_t s_khi = static_cast<uint32_t>(__cvta_generic_to_shared(khi));
   const uint32_t s_klo = static_cast<uint32_t>(__cvta_generic_to_shared(klo));
+  stage_split_rows<kLgRows>(qs + static_cast<int64_t>(bh) * n * 2 * D, i0, n, D, s_qhi, s_qlo, ld, tid);
+  stage_split_rows<kLgCols>(ks + static_cast<int64_t>(bh) * n * 2 * D, j0, n, D, s_khi, s_klo, ld, tid);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+  const uint32_t a_off = static_cast<uint32_t>(((lane % 16) * ld + (lane / 16) * 8) * 2);
+  const uint32_t b_off = static_cast<uint32_t>(((16 * warp + (lane / 16) * 8 + (lane % 8)) * ld + ((lane / 8) % 2) * 8) * 2);
   const int g = lane / 4, t2 = 2 * (lane % 4);
   constexpr int kMT = kLgRows / 16;
   float acc[kMT][2][4];
@@ -440,15 +455,15 @@ __global__ void __launch_bounds__(kMapThreads, 2) pooled_logits_kernel(const flo
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
-  for (int ks = 0; ks < D / 16; ++ks) {
+  for (int ks_ = 0; ks_ < D / 16; ++ks_) {
     uint32_t bh_[4], bl_[4];
-    ldmatrix_x4(bh_, s_khi + b_off + ks * 32);
-    ldmatrix_x4(bl_, s_klo + b_off + ks * 32);
+    ldmatrix_x4(bh_, s_khi + b_off + ks_ * 32);
+    ldmatrix_x4(bl_, s_klo + b_off + ks_ * 32);
 #pragma unroll
     for (int mt = 0; mt < kMT; ++mt) {
       uint32_t ah[4], al[4];
-      ldmatrix_x4(ah, s_qhi + a_off + (mt * 16 * ld + ks * 16) * 2);
-      ldmatrix_x4(al, s_qlo + a_off + (mt * 16 * ld + ks * 16) * 2);
+      ldmatrix_x4(ah, s_qhi + a_off + (mt * 16 * ld + ks_ * 16) * 2);
+      ldmatrix_x4(al, s_qlo + a_off + (mt * 16 * ld + ks_ * 16) * 2);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         mma_bf16(acc[mt][nt], al, bh_[2 * nt], bh_[2 * nt + 1]);      // small terms first
@@ -487,6 +502,13 @@ __global__ void __launch_bounds__(kMapThreads) pooled_darkness_kernel(const floa
 
 size_t pooled_logits_smem(int D) {
   return sizeof(__nv_bfloat16) * static_cast<size_t>(2 * (kLgRows + kLgCols)) * (D + 8);
+}
+// workspace: float32 logits | split query means | split key means (each part a multiple of 16 bytes)
+size_t pooled_ws_logits_bytes(int BH, int n) {
+  return (sizeof(float) * static_cast<size_t>(BH) * n * n + 15) / 16 * 16;
+}
+size_t pooled_ws_split_bytes(int BH, int n, int D) {
+  return sizeof(__nv_bfloat16) * static_cast<size_t>(BH) * n * 2 * D;
 }
 
 size_t pooled_map_smem(int D, int n) {
@@ -617,9 +639,9 @@ extern "C" int moddit_pooled_map(const float* qbar, const float* kbar, int BH, i
   return MODDIT_OK;
 }
 
-extern "C" size_t moddit_pooled_map_workspace_bytes(int BH, int n) {
-  if (BH <= 0 || n <= 0) return 0;
-  return sizeof(float) * static_cast<size_t>(BH) * static_cast<size_t>(n) * static_cast<size_t>(n);
+extern "C" size_t moddit_pooled_map_workspace_bytes(int BH, int n, int D) {
+  if (BH <= 0 || n <= 0 || D <= 0) return 0;
+  return pooled_ws_logits_bytes(BH, n) + 2 * pooled_ws_split_bytes(BH, n, D);
 }
 
 extern "C" int moddit_pooled_map_ws(const float* qbar, const float* kbar, int BH, int nb, int D, int q_block_offset,
@@ -631,9 +653,9 @@ extern "C" int moddit_pooled_map_ws(const float* qbar, const float* kbar, int BH
   MODDIT_CHECK_ARG(q_block_offset >= 0 && k_block_offset >= 0 && q_block_offset + n <= nb && k_block_offset + n <= nb,
                    "pooled_map_ws: video region [%d+%d) / [%d+%d) exceeds %d blocks", q_block_offset, n,
                    k_block_offset, n, nb);
-  MODDIT_CHECK_ARG(workspace_bytes >= moddit_pooled_map_workspace_bytes(BH, n),
+  MODDIT_CHECK_ARG(workspace_bytes >= moddit_pooled_map_workspace_bytes(BH, n, D),
                    "pooled_map_ws: workspace of %zu bytes, %zu needed", workspace_bytes,
-                   moddit_pooled_map_workspace_bytes(BH, n));
+                   moddit_pooled_map_workspace_bytes(BH, n, D));
   if (BH > 65535) return fail(MODDIT_E_UNSUPPORTED, "pooled_map_ws: BH=%d exceeds 65535", BH);
   if ((D & 15) != 0 || D > 256 || !aligned16(qbar) || !aligned16(kbar) || !aligned16(workspace))
     return fail(MODDIT_E_ALIGN,
@@ -642,9 +664,15 @@ extern "C" int moddit_pooled_map_ws(const float* qbar, const float* kbar, int BH
   cudaStream_t st = as_stream(stream);
   const size_t sm = pooled_logits_smem(D);
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(pooled_logits_kernel), sm)) return rc;
-  float* lg = static_cast<float*>(workspace);
-  pooled_logits_kernel<<<dim3(ceil_div(n, kLgCols), ceil_div(n, kLgRows), BH), kMapThreads, sm, st>>>(
-      qbar, kbar, nb, D, q_block_offset, k_block_offset, n, scale, lg);
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  float* lg = reinterpret_cast<float*>(ws);
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(ws + pooled_ws_logits_bytes(BH, n));
+  __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(ws + pooled_ws_logits_bytes(BH, n) + pooled_ws_split_bytes(BH, n, D));
+  const int64_t total4 = static_cast<int64_t>(BH) * n * (D / 4);
+  split_means_kernel<<<dim3(static_cast<unsigned>((total4 + 255) / 256), 2), 256, 0, st>>>(
+      qbar, kbar, nb, D, q_block_offset, k_block_offset, n, scale, total4, qs, ks);
+  MODDIT_CHECK_LAUNCH("split_means_kernel");
+  pooled_logits_kernel<<<dim3(ceil_div(n, kLgCols), ceil_div(n, kLgRows), BH), kMapThreads, sm, st>>>(qs, ks, D, n, lg);
   MODDIT_CHECK_LAUNCH("pooled_logits_kernel");
   const int64_t rows = static_cast<int64_t>(BH) * n;
   pooled_darkness_kernel<<<static_cast<unsigned>((rows + kMapThreads / 32 - 1) / (kMapThreads / 32)), kMapThreads, 0, st>>>(

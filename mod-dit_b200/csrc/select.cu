@@ -83,49 +83,83 @@ __global__ void head_modes_kernel(const float* __restrict__ b_d, int H, float th
 constexpr int kMaskRows = 32;
 constexpr int kMaskThreads = 256;
 
-// One CTA per (32 mask rows, head).  Shared memory holds, per video column, one byte "column selected" and the
-// column's frame index (so the per-frame block-diagonal test is a compare, not a division per element), and one
-// byte per diagonal offset.  Every thread decides two neighbouring blocks of a row at a time and stores them
-// together (rows start on even addresses when the row length is even; odd lengths fall back to single bytes).
+// One CTA per (32 mask rows, head), a warp per row.  Shared memory holds two bit arrays: one bit per mask column
+// ("selected column", and every column outside the video region, which is always kept) and one bit per diagonal
+// offset, the latter padded with zero bits on both sides so that a row may read 32 bits starting anywhere.  For a
+// row, lane l builds the keep bits of columns [32 l, 32 l + 32) of a 1024-column segment with a handful of word
+// operations - column word | diagonal bits funnel-shifted to the row's offset | the row's own frame as a bit range -
+// and the warp then writes the segment 128 bytes per instruction, every lane expanding four bits it fetches from
+// the lane that holds them.  (One byte decided and stored per thread and step made this kernel instruction-bound.)
+__device__ __forceinline__ uint32_t low_bits(int x) { return x >= 32 ? 0xffffffffu : ((1u << x) - 1u); }
+
 __global__ void __launch_bounds__(kMaskThreads) mask_from_lines_kernel(
     const int64_t* __restrict__ selected, int k, const int32_t* __restrict__ modes, int n, int bpf, int voff, int nbt,
-    uint8_t* __restrict__ mask) {
-  extern __shared__ __align__(4) uint8_t flags[];   // [n] columns | [2n-1] diagonals | pad | [n] frame (uint16)
-  uint8_t* col_sel = flags;
-  uint8_t* off_sel = flags + n;
-  uint16_t* frame = reinterpret_cast<uint16_t*>(flags + ((3 * n - 1 + 3) & ~3));
+    int pad_bits, int col_words, int diag_words, uint8_t* __restrict__ mask) {
+  extern __shared__ __align__(4) uint32_t bits_s[];
+  uint32_t* colw = bits_s;                 // [col_words]  bit C
+  uint32_t* dw = bits_s + col_words;       // [diag_words] bit pad_bits + (column - row + n - 1)
   const int h = blockIdx.y;
   const int mode = modes[h];
   const bool frames_on = (mode == MODDIT_MODE_BLOCK_DIAGONAL);
-  for (int i = threadIdx.x; i < 3 * n - 1; i += kMaskThreads) flags[i] = 0;
-  // with the per-frame test off every column gets a frame no row has
-  for (int j = threadIdx.x; j < n; j += kMaskThreads) frame[j] = frames_on ? static_cast<uint16_t>(j / bpf) : 0xffffu;
+  const bool all = (mode == MODDIT_MODE_FULL);
+  for (int w = threadIdx.x; w < col_words; w += kMaskThreads) {
+    // columns outside [voff, voff + n) are text (or padding of the word): always kept
+    const int c0 = 32 * w;
+    const int a = min(max(voff - c0, 0), 32), b = min(max(voff + n - c0, 0), 32);
+    colw[w] = ~(low_bits(b) & ~low_bits(a));
+  }
+  for (int w = threadIdx.x; w < diag_words; w += kMaskThreads) dw[w] = 0u;
   __syncthreads();
   for (int t = threadIdx.x; t < k; t += kMaskThreads) {
-    const int64_t idx = selected[static_cast<int64_t>(h) * k + t];
-    if (idx >= 0 && idx < 3 * n - 1) flags[idx] = 1;   // [0,n): column; n + (offset + n - 1): diagonal
+    const int64_t idx = selected[static_cast<int64_t>(h) * k + t];   // [0,n): column; n + (offset + n - 1): diagonal
+    if (idx >= 0 && idx < n) {
+      const int c = static_cast<int>(idx) + voff;
+      atomicOr(&colw[c >> 5], 1u << (c & 31));
+    } else if (idx >= n && idx < 3 * n - 1) {
+      const int d = static_cast<int>(idx) - n + pad_bits;
+      atomicOr(&dw[d >> 5], 1u << (d & 31));
+    }
   }
   __syncthreads();
-  const bool all = (mode == MODDIT_MODE_FULL);
-  const bool pairs = (nbt & 1) == 0;
-  for (int rr = 0; rr < kMaskRows; ++rr) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  for (int rr = warp; rr < kMaskRows; rr += kMaskThreads / 32) {
     const int R = blockIdx.x * kMaskRows + rr;
     if (R >= nbt) break;
     const int i = R - voff;
     uint8_t* dst = mask + (static_cast<int64_t>(h) * nbt + R) * nbt;
     const bool whole_row = all || i < 0 || i >= n;              // text rows and 'full' heads keep everything
-    const uint16_t fi = (frames_on && !whole_row) ? static_cast<uint16_t>(i / bpf) : 0xfffeu;
-    const uint8_t* diag = off_sel + (n - 1 - i);               // diag[j] = flag of offset j - i
-    auto kept = [&](int C) -> uint32_t {
-      const int j = C - voff;
-      if (whole_row || j < 0 || j >= n) return 1u;
-      return (col_sel[j] | diag[j] | (frame[j] == fi ? 1 : 0)) ? 1u : 0u;
-    };
-    if (pairs) {
-      for (int C = 2 * threadIdx.x; C < nbt; C += 2 * kMaskThreads)
-        *reinterpret_cast<uint16_t*>(dst + C) = static_cast<uint16_t>(kept(C) | (kept(C + 1) << 8));
-    } else {
-      for (int C = threadIdx.x; C < nbt; C += kMaskThreads) dst[C] = static_cast<uint8_t>(kept(C));
+    int f_lo = 0, f_hi = 0;                                     // the row's own frame as a column range
+    if (frames_on && !whole_row) {
+      f_lo = voff + (i / bpf) * bpf;
+      f_hi = min(f_lo + bpf, voff + n);
+    }
+    for (int seg = 0; seg < nbt; seg += 1024) {
+      const int c0 = seg + 32 * lane;
+      uint32_t word = 0xffffffffu;
+      if (!whole_row && c0 < nbt) {
+        const int b = c0 - R + n - 1 + pad_bits;                // >= 0: pad_bits >= voff
+        word = colw[c0 >> 5] | __funnelshift_r(dw[b >> 5], dw[(b >> 5) + 1], b & 31);
+        const int fa = min(max(f_lo - c0, 0), 32), fb = min(max(f_hi - c0, 0), 32);
+        word |= low_bits(fb) & ~low_bits(fa);
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const uint32_t wv = __shfl_sync(0xffffffffu, word, 4 * r + (lane >> 3));
+        const int C = seg + 128 * r + 4 * lane;
+        if (C >= nbt) continue;
+        const uint32_t x = (wv >> ((lane & 7) * 4)) & 0xfu;
+        const uint32_t bytes = (x & 1u) | ((x & 2u) << 7) | ((x & 4u) << 14) | ((x & 8u) << 21);
+        uint8_t* p = dst + C;
+        const uintptr_t addr = reinterpret_cast<uintptr_t>(p);
+        if (C + 3 < nbt && (addr & 3) == 0) {
+          *reinterpret_cast<uint32_t*>(p) = bytes;
+        } else if (C + 3 < nbt && (addr & 1) == 0) {
+          *reinterpret_cast<uint16_t*>(p) = static_cast<uint16_t>(bytes);
+          *reinterpret_cast<uint16_t*>(p + 2) = static_cast<uint16_t>(bytes >> 16);
+        } else {
+          for (int q = 0; q < 4 && C + q < nbt; ++q) p[q] = static_cast<uint8_t>(bytes >> (8 * q));
+        }
+      }
     }
   }
 }
@@ -315,6 +349,7 @@ __global__ void __launch_bounds__(kMassWarpThreads) select_mass_warp_kernel(
 
 // ---- work lists ---------------------------------------------------------------------------------
 constexpr int kListThreads = 256;
+constexpr int kListBatch = 4;
 
 // One warp per (pair of 128-row query tiles, mask head): the warp walks the key tiles 32 at a time, a ballot
 // marks the tiles some sub-block of the pair keeps, and every kept tile is written at its running position (the
@@ -330,12 +365,13 @@ __global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t*
   int32_t* out = entries + (static_cast<int64_t>(h) * npairs + p) * ntk;
   const int lim = min(nbk, kv_block_limit);
   int base = 0;
-  // four steps of 32 key tiles at a time: all their mask bytes are requested before the first ballot, so the warp
-  // waits for the memory system once per 128 key tiles instead of once per 32
-  for (int t0 = 0; t0 < ntk; t0 += 128) {
-    int fls[4];
+  // kListBatch steps of 32 key tiles at a time: all their mask bytes are requested before the first ballot, so the
+  // warp waits for the memory system once per 128 key tiles instead of once per 32 (16 steps at a time measured
+  // slower than 4: 0.083 against 0.060 ms at 24 heads x 902 tiles)
+  for (int t0 = 0; t0 < ntk; t0 += 32 * kListBatch) {
+    int fls[kListBatch];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kListBatch; ++u) {
       const int t = t0 + 32 * u + lane;
       int fl = 0;
       if (t < ntk) {
@@ -358,7 +394,7 @@ __global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t*
       fls[u] = fl;
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kListBatch; ++u) {
       const int t = t0 + 32 * u + lane;
       const unsigned bal = __ballot_sync(0xffffffffu, fls[u] != 0);
       if (fls[u]) out[base + __popc(bal & ((1u << lane) - 1))] = (t << 8) | fls[u];
@@ -374,6 +410,7 @@ __global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t*
 // tile and runs several times longer than the average pair: started late it would be the tail of the launch),
 // then head after head, longest first, so that one head's K and V stay in L2 while its pairs run.
 constexpr int kLongFirst = 2;
+constexpr int kOrderSplit = 4;      // CTAs per head: each ranks a quarter of the pairs against all of them
 __global__ void __launch_bounds__(256) order_pairs_kernel(const int32_t* __restrict__ counts, int npairs,
                                                           int32_t* __restrict__ order) {
   extern __shared__ int32_t cnt_s[];
@@ -383,9 +420,10 @@ __global__ void __launch_bounds__(256) order_pairs_kernel(const int32_t* __restr
   for (int i = threadIdx.x; i < npairs; i += blockDim.x) cnt_s[i] = c[i];
   __syncthreads();
   const int r0 = min(kLongFirst, npairs);
-  for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < npairs; i += kOrderSplit * blockDim.x) {
     const int ci = cnt_s[i];
     int rank = 0;
+#pragma unroll 8
     for (int j = 0; j < npairs; ++j) {
       const int cj = cnt_s[j];
       rank += (cj > ci) || (cj == ci && j < i);
@@ -507,9 +545,17 @@ extern "C" int moddit_mask_from_lines(const int64_t* selected, int k, const int3
     return fail(MODDIT_E_ARG, "mask_from_lines: unknown layout %d", layout);
   }
   if (int rc = require_sm100()) return rc;
-  const size_t smem = static_cast<size_t>((3 * n - 1 + 3) & ~3) + sizeof(uint16_t) * n;
+  // bit arrays: columns padded to the 1024-column segments a warp walks; diagonals with pad_bits zero bits in front
+  // (a row's first word starts at offset -row >= -(voff + n - 1) relative to the main diagonal's n - 1) and room for
+  // a whole segment behind
+  const int col_words = ceil_div(nbt, 1024) * 32;
+  const int pad_bits = ceil_div(voff, 32) * 32 + 32;
+  const int diag_words = (pad_bits + 32 * col_words + n) / 32 + 2;
+  const size_t smem = sizeof(uint32_t) * static_cast<size_t>(col_words + diag_words);
+  if (smem > 200 * 1024) return fail(MODDIT_E_UNSUPPORTED, "mask_from_lines: %d blocks exceed the bit arrays", nbt);
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(mask_from_lines_kernel), smem)) return rc;
   mask_from_lines_kernel<<<dim3(ceil_div(nbt, kMaskRows), H), kMaskThreads, smem, as_stream(stream)>>>(
-      selected, k, modes, n, blocks_per_frame, voff, nbt, mask);
+      selected, k, modes, n, blocks_per_frame, voff, nbt, pad_bits, col_words, diag_words, mask);
   MODDIT_CHECK_LAUNCH("mask_from_lines_kernel");
   return MODDIT_OK;
 }
@@ -576,7 +622,7 @@ extern "C" int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, 
       mask, nbq, nbk, 128 / block_size, ntq, ntq, kv_block_limit, npairs, counts, entries);
   MODDIT_CHECK_LAUNCH("tile_lists_kernel");
   if (order != nullptr) {
-    order_pairs_kernel<<<Hm, 256, sizeof(int32_t) * npairs, as_stream(stream)>>>(counts, npairs, order);
+    order_pairs_kernel<<<dim3(Hm, kOrderSplit), 256, sizeof(int32_t) * npairs, as_stream(stream)>>>(counts, npairs, order);
     MODDIT_CHECK_LAUNCH("order_pairs_kernel");
   }
   return MODDIT_OK;

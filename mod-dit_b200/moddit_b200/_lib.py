@@ -34,7 +34,7 @@ SIGNATURES = {
                                     c_int, c_void_p, c_size_t, c_void_p]),
     "moddit_pooled_map": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_void_p, c_void_p]),
-    "moddit_pooled_map_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "moddit_pooled_map_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "moddit_pooled_map_ws": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                      c_void_p, c_void_p, c_size_t, c_void_p]),
     "moddit_replay_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,

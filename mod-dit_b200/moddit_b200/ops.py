@@ -224,8 +224,9 @@ def pooled_map(qbar: torch.Tensor, kbar: torch.Tensor, *, q_block_offset: int, k
                video_blocks: int, scale: float, launches: int = 2) -> torch.Tensor:
     """(B,H,nb,D) float32 block means -> (B,H,n,n) float16 darkness map, 1 - exp(logit - row maximum).
 
-    launches=2 (`moddit_pooled_map_ws`): logits into a float32 workspace of 4*B*H*n*n bytes, then the row pass;
-    launches=1 (`moddit_pooled_map`): one kernel, no workspace, slower.  Both give the same bits."""
+    launches=2 (`moddit_pooled_map_ws`): float32 logits tile by tile into a workspace (4*B*H*n*n bytes plus the
+    split means), then the row pass; launches=1 (`moddit_pooled_map`): one kernel, no workspace, slower.  Both give
+    the same bits."""
     dev = _need_cuda(qbar, kbar)
     _need_contig(qbar=qbar, kbar=kbar)
     if qbar.dtype != torch.float32 or kbar.dtype != torch.float32 or qbar.shape != kbar.shape:
@@ -239,7 +240,7 @@ def pooled_map(qbar: torch.Tensor, kbar: torch.Tensor, *, q_block_offset: int, k
             check(lib.moddit_pooled_map(_ptr(qbar), _ptr(kbar), B * H, nb, D, q_block_offset, k_block_offset,
                                         video_blocks, float(scale), _ptr(out), _stream(dev)), "moddit_pooled_map")
         return out
-    ws_bytes = int(lib.moddit_pooled_map_workspace_bytes(B * H, video_blocks))
+    ws_bytes = int(lib.moddit_pooled_map_workspace_bytes(B * H, video_blocks, D))
     ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev), _timed("moddit_pooled_map", dev):
         check(lib.moddit_pooled_map_ws(_ptr(qbar), _ptr(kbar), B * H, nb, D, q_block_offset, k_block_offset,

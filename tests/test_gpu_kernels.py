@@ -97,8 +97,8 @@ def test_pooled_map_workspace_checked(ops):
     from moddit_b200._lib import lib
     qbar = torch.randn(1, 2, 40, 64, device="cuda")
     out = torch.empty(1, 2, 40, 40, device="cuda", dtype=torch.float16)
-    need = int(lib.moddit_pooled_map_workspace_bytes(2, 40))
-    assert need == 4 * 2 * 40 * 40
+    need = int(lib.moddit_pooled_map_workspace_bytes(2, 40, 64))
+    assert need == 4 * 2 * 40 * 40 + 2 * (2 * 2 * 40 * 2 * 64)
     ws = torch.empty(need, device="cuda", dtype=torch.uint8)
     rc = lib.moddit_pooled_map_ws(qbar.data_ptr(), qbar.data_ptr(), 2, 40, 64, 0, 0, 40, 0.125, out.data_ptr(),
                                   ws.data_ptr(), need - 1, None)
