@@ -218,10 +218,11 @@ class Harness:
         if self.N % self.world:
             raise SystemExit(f"{self.N} tokens do not divide over {self.world} sequence shards")
         try:
-            self.resharder = mdist.PeerResharder(self.H, self.N, self.D, torch.bfloat16, dev)
+            self.resharder = mdist.PeerResharder(self.H, self.N, self.D, torch.bfloat16, dev,
+                                                 bulk_copy=self.args.bulk_copy)
             self.resharder.enable_pooling(self.bs)
-            self.reshard = ("peer-memory copies (copy engines) + fused output scatter; query/key pooled on the "
-                            "sequence shards")
+            self.reshard = ("peer-memory copies (%s) + fused output scatter; query/key pooled on the sequence shards"
+                            % ("copy engines" if self.args.bulk_copy == "dma" else "copy kernel"))
             try:                   # one exchange up front: a box without peer DMA fails here, on every rank alike
                 probe = torch.zeros(1, self.H, self.N // self.world, self.D, device=dev, dtype=torch.bfloat16)
                 self.resharder.seq_to_head(probe, 2, channel=1)
@@ -828,9 +829,14 @@ def main():
     ap.add_argument("--sweep-lead-ms", type=float, default=6.0,
                     help="device busy-wait before each timed sweep step, so that its launches are queued, not awaited")
     ap.add_argument("--sweep-tau", type=float, default=0.4, help="cumulative-mass threshold of --sweep mass")
-    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--e2e-steps", type=int, default=20,
+                    help="steps of the host-buffer leg (at most --steps); the two-deep copy pipeline fills and drains "
+                         "inside its timed region, about one step's worth of time whatever the count")
     ap.add_argument("--cpu-blocks", type=int, default=480, help="query blocks in the cpu_baseline sample")
     ap.add_argument("--ref-blocks", type=int, default=32, help="query blocks per step of --impl reference")
+    ap.add_argument("--bulk-copy", choices=("dma", "kernel"), default="dma",
+                    help="several GPUs: how the sequence->head pieces travel, copy engines (no SM taken) or this "
+                         "library's copy kernel (plain peer stores)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--prologue-only", action="store_true",
