@@ -24,7 +24,8 @@ _DTYPE = {torch.bfloat16: _lib.MODDIT_BF16, torch.float16: _lib.MODDIT_FP16}
 _TIMING = {"on": False, "only": None, "records": [], "launches": 0,
            "nvtx": os.environ.get("MODDIT_NVTX", "0") not in ("", "0")}
 # kernels launched by one call of each entry point (for launch accounting in benchmarks)
-KERNELS_PER_CALL = {"moddit_pool_blocks": 1, "moddit_pooled_map": 1, "moddit_replay_map": 1, "moddit_mts": 2,
+KERNELS_PER_CALL = {"moddit_pool_blocks": 1, "moddit_pooled_map": 1, "moddit_pooled_map_ws": 3, "moddit_replay_map": 1,
+                    "moddit_mts": 2,
                     "moddit_mtm": 1, "moddit_solve": 3, "moddit_select_lines": 1, "moddit_head_modes": 1,
                     "moddit_mask_from_lines": 1, "moddit_select_mass": 1, "moddit_tile_lists": 2,
                     "moddit_sparse_attn_fwd": 1, "moddit_replay_status": 0,
@@ -242,7 +243,7 @@ def pooled_map(qbar: torch.Tensor, kbar: torch.Tensor, *, q_block_offset: int, k
         return out
     ws_bytes = int(lib.moddit_pooled_map_workspace_bytes(B * H, video_blocks, D))
     ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
-    with torch.cuda.device(dev), _timed("moddit_pooled_map", dev):
+    with torch.cuda.device(dev), _timed("moddit_pooled_map_ws", dev):
         check(lib.moddit_pooled_map_ws(_ptr(qbar), _ptr(kbar), B * H, nb, D, q_block_offset, k_block_offset,
                                        video_blocks, float(scale), _ptr(out), _ptr(ws), ws_bytes, _stream(dev)),
               "moddit_pooled_map_ws")
