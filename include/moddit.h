@@ -271,6 +271,13 @@ int moddit_select_topk_blocks(const void* map_f16, int H, int n, int count, cons
  */
 int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, int block_size, int N,
                       int kv_block_limit, int32_t* counts, int32_t* entries, int32_t* order, void* stream);
+/* The start order alone, for launches over groups of heads: heads [g*heads_per_group, (g+1)*heads_per_group) form
+ * group g, whose part of `order` starts at g*heads_per_group*npairs, is laid out like the order of a launch with
+ * that many heads and holds indices relative to the group's first head.  heads_per_group = Hm gives the order
+ * moddit_tile_lists writes.  (Several GPUs: the sparse forward of a group of heads starts as soon as that group's
+ * rows have arrived from the peers.)
+ */
+int moddit_order_pairs(const int32_t* counts, int Hm, int npairs, int heads_per_group, int32_t* order, void* stream);
 
 /* Block-sparse flash-attention forward.  Replaces `AttentionSparseEngine` (MoD/mod/attn_mask.py:266-331:
  * block_sparse_sage2_attn_cuda for video rows, flashinfer prefill for text rows, sageattn for all-true
@@ -301,6 +308,10 @@ int moddit_copy_rows(const void* src, void* dst, int64_t src_pitch, int64_t dst_
  * arrays of device pointers. */
 int moddit_copy_rows_multi(const void* const* src, void* const* dst, int n_jobs, int64_t src_pitch,
                            int64_t dst_pitch, int64_t width_bytes, int rows, void* stream);
+/* The same jobs on at most `max_ctas` CTAs that walk 64 KB segments round-robin: an exchange that runs beside other
+ * kernels leaves them the rest of the GPU (moddit_copy_rows_multi fills it). */
+int moddit_copy_rows_narrow(const void* const* src, void* const* dst, int n_jobs, int64_t src_pitch,
+                            int64_t dst_pitch, int64_t width_bytes, int rows, int max_ctas, void* stream);
 
 /* The same copy on the GPU's copy engines (one asynchronous 2-D copy, no kernel): for the bulk pieces of the
  * re-shard, which then neither occupy SMs nor compete with the step's kernels; no alignment requirement. */

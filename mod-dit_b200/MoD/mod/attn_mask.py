@@ -191,8 +191,52 @@ def _events(ready):
     return tuple(ev for ev in ready if ev is not None) if isinstance(ready, (tuple, list)) else (ready,)
 
 
+_GROUP_STREAMS: Dict = {}
+
+
+def _group_streams(device, n: int):
+    key = (device.index if device.index is not None else torch.cuda.current_device())
+    have = _GROUP_STREAMS.setdefault(key, [])
+    while len(have) < n:
+        have.append(torch.cuda.Stream(device=device))
+    return have[:n]
+
+
+def _engine_by_head_groups(query, key, value, lists, group_ready, scatter, **fwd_kw):
+    """One launch per group of heads, each on a stream of its own behind the event that says the group's rows have
+    arrived: the first group computes while the later ones are still on the links.  The lists' order must have been
+    made group by group (`tile_lists(..., heads_per_group=...)`).  Returns None with `scatter`, else the output."""
+    H = query.shape[1]
+    G = len(group_ready)
+    hpg = (H + G - 1) // G
+    dev = query.device
+    main = torch.cuda.current_stream(dev)
+    fork = torch.cuda.Event()
+    fork.record(main)                      # the lists are complete
+    out = None if scatter is not None else torch.empty_like(query)
+    npairs = lists.counts.shape[1]
+    flat_order = lists.order.view(-1)
+    for g, st in enumerate(_group_streams(dev, G)):
+        h0, h1 = g * hpg, min(H, (g + 1) * hpg)
+        if h0 >= h1:
+            break
+        st.wait_event(fork)
+        if group_ready[g] is not None:
+            st.wait_event(group_ready[g])
+        with torch.cuda.stream(st):
+            _ops.sparse_attn_fwd(query[:, h0:h1], key[:, h0:h1], value[:, h0:h1], lists.counts[h0:h1],
+                                 lists.entries[h0:h1], order=flat_order[h0 * npairs:h1 * npairs].view(h1 - h0, npairs),
+                                 check_status=False, out=None if out is None else out[:, h0:h1],
+                                 scatter=None if scatter is None else (scatter[0], scatter[1] + h0), **fwd_kw)
+        done = torch.cuda.Event()
+        done.record(st)
+        main.wait_event(done)
+    _ops.post_status(dev)
+    return out
+
+
 def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_token_num=0, block_size=128,
-                          _lists=None, _value_ready=None, _scatter=None):
+                          _lists=None, _value_ready=None, _scatter=None, _group_ready=None):
     """Block-sparse attention of (B,H,S,D) tensors under a bool block mask (:266-331).
 
     Video query rows (index < video_token_num) see the keys below the valid length rounded up to 64, text
@@ -214,13 +258,17 @@ def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_
     for ev in _events(_value_ready):   # inputs produced on another stream (e.g. still arriving from peers)
         torch.cuda.current_stream(query.device).wait_event(ev)
     value = value.contiguous()
-    if pre_defined_mask is None:
-        return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, check_status="deferred",
-                                    scatter=_scatter)
-    valid = _valid_kv(pre_defined_mask, seq_len)
-    border = valid if all_kept else min(seq_len, (valid + 63) // 64 * 64)
-    return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, q_split=video_token_num,
-                                kv_len_lo=border, kv_len_hi=valid, check_status="deferred", scatter=_scatter)
+    fwd_kw = {}
+    if pre_defined_mask is not None:
+        valid = _valid_kv(pre_defined_mask, seq_len)
+        border = valid if all_kept else min(seq_len, (valid + 63) // 64 * 64)
+        fwd_kw = dict(q_split=video_token_num, kv_len_lo=border, kv_len_hi=valid)
+    if _group_ready is not None and len(_group_ready) > 1:
+        if lists.counts.shape[0] != query.shape[1] * query.shape[0]:
+            raise ValueError("head groups need one mask per head")
+        return _engine_by_head_groups(query, key, value, lists, _group_ready, _scatter, **fwd_kw)
+    return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, check_status="deferred",
+                                scatter=_scatter, **fwd_kw)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -291,7 +339,9 @@ def _store_mask(warmup_state: Dict, mask: torch.Tensor, seq_len: int):
     nb = (seq_len + bs - 1) // bs
     if mask.shape[-1] != nb:                      # wan: the mask covers the whole (video-only) sequence
         raise ValueError(f"mask of {mask.shape[-1]} blocks does not cover a sequence of {nb} blocks")
-    warmup_state['_tile_lists'] = (mask, _ops.tile_lists(full, bs, seq_len))
+    groups = int(warmup_state.get('_head_groups') or 1)
+    hpg = (full.shape[0] + groups - 1) // groups if groups > 1 and full.dim() == 3 else None
+    warmup_state['_tile_lists'] = (mask, _ops.tile_lists(full, bs, seq_len, heads_per_group=hpg))
 
 
 def _lists_for(warmup_state: Dict, seq_len: int):
@@ -355,6 +405,11 @@ def SparseAttentionWithMap(
     Optional keyword `output_scatter` (from `moddit_b200.dist.PeerResharder.begin_output`): on sparse steps
     the attention kernel stores its rows straight into the peers' sequence-shard buffers and the returned
     output is None; steps that run dense attention ignore it and return the output tensor as usual.
+    Optional keyword `head_group_ready` (pooled producer only; a list of G torch.cuda.Events, from
+    `PeerResharder.seq_to_head_groups`): query, key and value arrive group of heads by group of heads
+    (ceil(H/G) heads each) and event g fires when group g is complete; the block-sparse forward is then launched
+    once per group, each launch behind its own event, so the first group computes while the others still travel.
+    `warmup_state['_head_groups'] = G` must be set so that the work lists are ordered group by group.
 
     Steps warmup-2 and warmup-1 collect features (dense output); afterwards every predict_T-th step
     refreshes the map, the features and the mask (dense output) and all other steps run the block-sparse
@@ -371,8 +426,8 @@ def SparseAttentionWithMap(
     if use_dense or warmup_state['sparse_type'] == 'full':
         # 'full' is accepted by create_adaptive_mask_state but has no branch in the reference (:598-729); here it
         # means what its name says: dense attention on every step
-        for ev in _events((kwargs.get('value_ready'), kwargs.get('qk_ready'))):   # inputs still arriving on other streams
-            torch.cuda.current_stream(query.device).wait_event(ev)
+        for ev in _events((kwargs.get('value_ready'), kwargs.get('qk_ready'))) + _events(kwargs.get('head_group_ready')):
+            torch.cuda.current_stream(query.device).wait_event(ev)     # inputs still arriving on other streams
         query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
         valid = _valid_kv(pre_defined_mask, seq_len)
         output, _ = dense_attention_with_lse(query, key, value, kv_len=valid)
@@ -393,9 +448,10 @@ def SparseAttentionWithMap(
     if pooled:
         return _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx,
                             value_ready, kwargs.get('output_scatter'), kwargs.get('pooled_qk'),
-                            kwargs.get('qk_ready'))
-    if kwargs.get('pooled_qk') is not None or kwargs.get('qk_ready') is not None:
-        raise ValueError("pooled_qk / qk_ready need warmup_state['score_producer'] == 'pooled'")
+                            kwargs.get('qk_ready'), kwargs.get('head_group_ready'))
+    if kwargs.get('pooled_qk') is not None or kwargs.get('qk_ready') is not None or \
+            kwargs.get('head_group_ready') is not None:
+        raise ValueError("pooled_qk / qk_ready / head_group_ready need warmup_state['score_producer'] == 'pooled'")
     if value_ready is not None:
         torch.cuda.current_stream(query.device).wait_event(value_ready)
     value = value.contiguous()
@@ -511,7 +567,7 @@ def _spargeattn_step(query, key, value, warmup_state):
 
 
 def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, current_step, layer_idx,
-                 value_ready=None, output_scatter=None, pooled_qk=None, qk_ready=None):
+                 value_ready=None, output_scatter=None, pooled_qk=None, qk_ready=None, head_group_ready=None):
     """Variant with the mean-pooled map producer: the mask is re-predicted on every step from the pooled map
     of that step, so no dense pass is needed after the first feature-collection step."""
     seq_len, num_heads = query.size(2), query.size(1)
@@ -519,15 +575,16 @@ def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, curr
     bs = warmup_state['block_size']
 
     def wait_value():
-        for ev in _events((value_ready, qk_ready)):
+        for ev in _events((value_ready, qk_ready)) + _events(head_group_ready):
             torch.cuda.current_stream(query.device).wait_event(ev)
 
     if current_step < warmup_steps - 2:
         wait_value()
         output, _ = dense_attention_with_lse(query, key, value, kv_len=_valid_kv(pre_defined_mask, seq_len))
         return output, {'mode': 'warmup', 'mask': None}
-    if pooled_qk is None and qk_ready is not None:      # query and key are read by the pooling itself
-        torch.cuda.current_stream(query.device).wait_event(qk_ready)
+    if pooled_qk is None:                               # query and key are read by the pooling itself
+        for ev in _events(qk_ready) + _events(head_group_ready):
+            torch.cuda.current_stream(query.device).wait_event(ev)
     dark = compute_pooled_map(query, key, warmup_state, pooled_qk).squeeze(0)
     n = dark.shape[-1]
     mts, _ = _ops.mts(dark, warmup_state['blocks_per_frame'])
@@ -553,7 +610,7 @@ def _pooled_step(query, key, value, warmup_state, logger, pre_defined_mask, curr
     output = AttentionSparseEngine(query, key, value, mask, pre_defined_mask=pre_defined_mask,
                                    video_token_num=warmup_state.get('video_token_num', 0), block_size=bs,
                                    _lists=warmup_state['_tile_lists'][1], _value_ready=(value_ready, qk_ready),
-                                   _scatter=output_scatter)
+                                   _scatter=output_scatter, _group_ready=head_group_ready)
     return output, {'mask': mask}
 
 

@@ -727,8 +727,60 @@ __global__ void __launch_bounds__(256) copy_rows_multi_kernel(const __grid_const
   for (; i < width16; i += stride) d[i] = __ldg(s + i);
 }
 
+// The same jobs on a fixed, small number of CTAs: segments of 64 KB are dealt round-robin to the CTAs, eight
+// 16-byte loads in flight per thread.  Meant for an exchange that runs beside other kernels: a grid that fills
+// the GPU would make them queue behind the copy, this one leaves them most of the SMs.
+constexpr int kCopySegment16 = 4096;     // 16-byte words per segment
+__global__ void __launch_bounds__(256) copy_rows_narrow_kernel(const __grid_constant__ CopyJobs jobs, int n_jobs,
+                                                               int rows, int64_t src_pitch, int64_t dst_pitch,
+                                                               int64_t width16) {
+  const int64_t segs_per_row = (width16 + kCopySegment16 - 1) / kCopySegment16;
+  const int64_t total = static_cast<int64_t>(n_jobs) * rows * segs_per_row;
+  for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const int64_t jr = t / segs_per_row, sg = t - jr * segs_per_row;
+    const int job = static_cast<int>(jr / rows), row = static_cast<int>(jr - static_cast<int64_t>(job) * rows);
+    const uint4* s = reinterpret_cast<const uint4*>(jobs.src[job] + row * src_pitch) + sg * kCopySegment16;
+    uint4* d = reinterpret_cast<uint4*>(jobs.dst[job] + row * dst_pitch) + sg * kCopySegment16;
+    const int n16 = static_cast<int>(min(static_cast<int64_t>(kCopySegment16), width16 - sg * kCopySegment16));
+    int i = threadIdx.x;
+    for (; i + 7 * 256 < n16; i += 8 * 256) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldg(s + i + u * 256);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) d[i + u * 256] = v[u];
+    }
+    for (; i < n16; i += 256) d[i] = __ldg(s + i);
+  }
+}
+
 }  // namespace
 }  // namespace moddit
+
+extern "C" int moddit_copy_rows_narrow(const void* const* src, void* const* dst, int n_jobs, int64_t src_pitch,
+                                       int64_t dst_pitch, int64_t width_bytes, int rows, int max_ctas, void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(src && dst, "copy_rows_narrow: null pointer table");
+  MODDIT_CHECK_ARG(n_jobs >= 1 && n_jobs <= kMaxCopyJobs, "copy_rows_narrow: n_jobs=%d outside [1, %d]", n_jobs, kMaxCopyJobs);
+  MODDIT_CHECK_ARG(rows > 0 && rows <= 65535 && width_bytes > 0, "copy_rows_narrow: rows=%d width=%lld out of range", rows,
+                   static_cast<long long>(width_bytes));
+  MODDIT_CHECK_ARG(max_ctas >= 1 && max_ctas <= 4096, "copy_rows_narrow: max_ctas=%d outside [1, 4096]", max_ctas);
+  if ((src_pitch & 15) || (dst_pitch & 15) || (width_bytes & 15))
+    return fail(MODDIT_E_ALIGN, "copy_rows_narrow: pitches and width must be multiples of 16 bytes");
+  CopyJobs jobs = {};
+  for (int i = 0; i < n_jobs; ++i) {
+    if (!src[i] || !dst[i] || !aligned16(src[i]) || !aligned16(dst[i]))
+      return fail(MODDIT_E_ALIGN, "copy_rows_narrow: job %d has a null or unaligned pointer", i);
+    jobs.src[i] = static_cast<const unsigned char*>(src[i]);
+    jobs.dst[i] = static_cast<unsigned char*>(dst[i]);
+  }
+  const int64_t width16 = width_bytes / 16;
+  const int64_t total = static_cast<int64_t>(n_jobs) * rows * ((width16 + kCopySegment16 - 1) / kCopySegment16);
+  const unsigned grid = static_cast<unsigned>(total < max_ctas ? total : max_ctas);
+  copy_rows_narrow_kernel<<<grid, 256, 0, as_stream(stream)>>>(jobs, n_jobs, rows, src_pitch, dst_pitch, width16);
+  MODDIT_CHECK_LAUNCH("copy_rows_narrow_kernel");
+  return MODDIT_OK;
+}
 
 extern "C" int moddit_copy_rows_multi(const void* const* src, void* const* dst, int n_jobs, int64_t src_pitch,
                                       int64_t dst_pitch, int64_t width_bytes, int rows, void* stream) {

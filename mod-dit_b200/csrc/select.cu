@@ -411,11 +411,16 @@ __global__ void __launch_bounds__(kListThreads) tile_lists_kernel(const uint8_t*
 // then head after head, longest first, so that one head's K and V stay in L2 while its pairs run.
 constexpr int kLongFirst = 2;
 constexpr int kOrderSplit = 4;      // CTAs per head: each ranks a quarter of the pairs against all of them
+// With heads_per_group < Hm the heads are ordered group by group (heads [g * heads_per_group, ...) form group g):
+// group g's part of `order` starts at g * heads_per_group * npairs, is laid out like a whole order of that many
+// heads and holds indices relative to the group's first head - what a launch over that group's heads alone needs.
 __global__ void __launch_bounds__(256) order_pairs_kernel(const int32_t* __restrict__ counts, int npairs,
-                                                          int32_t* __restrict__ order) {
+                                                          int heads_per_group, int32_t* __restrict__ order) {
   extern __shared__ int32_t cnt_s[];
   const int h = blockIdx.x;
-  const int Hm = gridDim.x;
+  const int g = h / heads_per_group, hl = h - g * heads_per_group;
+  const int Hg = min(heads_per_group, static_cast<int>(gridDim.x) - g * heads_per_group);
+  int32_t* og = order + static_cast<int64_t>(g) * heads_per_group * npairs;
   const int32_t* c = counts + static_cast<int64_t>(h) * npairs;
   for (int i = threadIdx.x; i < npairs; i += blockDim.x) cnt_s[i] = c[i];
   __syncthreads();
@@ -428,9 +433,9 @@ __global__ void __launch_bounds__(256) order_pairs_kernel(const int32_t* __restr
       const int cj = cnt_s[j];
       rank += (cj > ci) || (cj == ci && j < i);
     }
-    const int64_t pos = (rank < r0) ? static_cast<int64_t>(rank) * Hm + h
-                                    : static_cast<int64_t>(r0) * Hm + static_cast<int64_t>(h) * (npairs - r0) + (rank - r0);
-    order[pos] = h * npairs + i;
+    const int64_t pos = (rank < r0) ? static_cast<int64_t>(rank) * Hg + hl
+                                    : static_cast<int64_t>(r0) * Hg + static_cast<int64_t>(hl) * (npairs - r0) + (rank - r0);
+    og[pos] = hl * npairs + i;
   }
 }
 
@@ -622,9 +627,26 @@ extern "C" int moddit_tile_lists(const uint8_t* mask, int Hm, int nbq, int nbk, 
       mask, nbq, nbk, 128 / block_size, ntq, ntq, kv_block_limit, npairs, counts, entries);
   MODDIT_CHECK_LAUNCH("tile_lists_kernel");
   if (order != nullptr) {
-    order_pairs_kernel<<<dim3(Hm, kOrderSplit), 256, sizeof(int32_t) * npairs, as_stream(stream)>>>(counts, npairs, order);
+    order_pairs_kernel<<<dim3(Hm, kOrderSplit), 256, sizeof(int32_t) * npairs, as_stream(stream)>>>(counts, npairs, Hm, order);
     MODDIT_CHECK_LAUNCH("order_pairs_kernel");
   }
+  return MODDIT_OK;
+}
+
+extern "C" int moddit_order_pairs(const int32_t* counts, int Hm, int npairs, int heads_per_group, int32_t* order,
+                                  void* stream) {
+  clear_error();
+  MODDIT_CHECK_ARG(counts && order, "order_pairs: null pointer");
+  MODDIT_CHECK_ARG(Hm > 0 && Hm <= 65535 && npairs > 0, "order_pairs: Hm=%d npairs=%d out of range", Hm, npairs);
+  MODDIT_CHECK_ARG(heads_per_group > 0 && heads_per_group <= Hm, "order_pairs: heads_per_group=%d outside [1, %d]",
+                   heads_per_group, Hm);
+  if (sizeof(int32_t) * static_cast<size_t>(npairs) > 200 * 1024)
+    return fail(MODDIT_E_UNSUPPORTED, "order_pairs: npairs=%d too large", npairs);
+  if (int rc = require_sm100()) return rc;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(order_pairs_kernel), sizeof(int32_t) * npairs)) return rc;
+  order_pairs_kernel<<<dim3(Hm, kOrderSplit), 256, sizeof(int32_t) * npairs, as_stream(stream)>>>(counts, npairs,
+                                                                                                 heads_per_group, order);
+  MODDIT_CHECK_LAUNCH("order_pairs_kernel");
   return MODDIT_OK;
 }
 

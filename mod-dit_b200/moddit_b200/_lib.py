@@ -70,9 +70,11 @@ SIGNATURES = {
     "moddit_select_topk_blocks": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "moddit_tile_lists": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                   c_void_p, c_void_p]),
+    "moddit_order_pairs": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moddit_copy_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "moddit_copy_rows_dma": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "moddit_copy_rows_multi": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "moddit_copy_rows_narrow": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
     "moddit_sparse_attn_fwd_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                                c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p,
                                                c_int, c_int, c_void_p, c_void_p, c_void_p]),

@@ -148,6 +148,7 @@ class PeerResharder:
     """
 
     COPY_STREAMS = 4      # side streams the copy-engine pieces of one exchange are spread over
+    NARROW_CTAS = 48      # CTAs of one exchange in 'narrow' mode
 
     def __init__(self, heads: int, seq_len: int, head_dim: int, dtype: torch.dtype, device: torch.device,
                  group: Optional[dist.ProcessGroup] = None, n_inputs: int = 3, timeout_ms: int = 20000,
@@ -165,8 +166,9 @@ class PeerResharder:
         self.dtype, self.device = dtype, device
         self.esize = torch.empty((), dtype=dtype).element_size()
         self.timeout_ms = timeout_ms
-        if bulk_copy not in ("dma", "kernel"):
-            raise ValueError("bulk_copy must be 'dma' (copy engines) or 'kernel' (this library's copy kernel)")
+        if bulk_copy not in ("dma", "kernel", "narrow"):
+            raise ValueError("bulk_copy must be 'dma' (copy engines), 'kernel' (this library's copy kernel on the "
+                             "whole GPU) or 'narrow' (the copy kernel on NARROW_CTAS CTAs)")
         self.bulk_copy = bulk_copy
         self._copy_streams = None
         self.inputs, self.in_handles = [], []
@@ -199,6 +201,40 @@ class PeerResharder:
         self._bulk(src, dst, row, self.N * self.D * self.esize, row, self.hp)
         sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # every rank's stores have landed
         return [self.inputs[slot] for slot in slots]
+
+    def seq_to_head_groups(self, xs, slots, groups: int, channel: int = 0):
+        """`seq_to_head_many` delivered group of heads by group of heads: the local heads are cut into `groups` runs of
+        ceil(H/P / groups) heads; run g of every tensor is sent to every owner, then a barrier, then event g is
+        recorded on the current stream - a consumer that works head by head starts on run 0 while the later runs
+        are still on the links.  Returns (tensors, events)."""
+        for x in xs:
+            if tuple(x.shape) != (1, self.H, self.ns, self.D) or x.dtype != self.dtype or not x.is_contiguous():
+                raise ValueError("inputs must be contiguous (1, H, N/P, D) tensors of the configured dtype")
+        groups = max(1, min(int(groups), self.hp))
+        hpg = (self.hp + groups - 1) // groups
+        sync = self.in_handles[slots[0]]
+        cur = torch.cuda.current_stream(self.device)
+        sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # readers of the previous contents are done
+        row = self.ns * self.D * self.esize                            # bytes of one (head, sequence shard) piece
+        head = self.N * self.D * self.esize                            # bytes of one head in an owner's buffer
+        events = []
+        for g in range(groups):
+            h0, h1 = g * hpg, min(self.hp, (g + 1) * hpg)
+            if h0 >= h1:
+                events.append(events[-1])
+                continue
+            src, dst = [], []
+            for step in range(self.world):
+                peer = (self.rank + step) % self.world
+                for x, slot in zip(xs, slots):
+                    src.append(x.data_ptr() + (peer * self.hp + h0) * row)
+                    dst.append(int(self.in_handles[slot].buffer_ptrs[peer]) + h0 * head + self.rank * row)
+            self._bulk(src, dst, row, head, row, h1 - h0)
+            sync.barrier(channel=channel, timeout_ms=self.timeout_ms)  # every rank's rows of this run have landed
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            events.append(ev)
+        return [self.inputs[slot] for slot in slots], events
 
     def head_to_seq(self, x: torch.Tensor, channel: int = 0) -> torch.Tensor:
         """Push this rank's (1, H/P, N, D) head shard back; returns the local (1, H, N/P, D) sequence shard."""
@@ -241,7 +277,11 @@ class PeerResharder:
                 cur.wait_event(done)
             return
         for i in range(0, len(src), 24):
-            self._ops.copy_rows_multi(src[i:i + 24], dst[i:i + 24], src_pitch, dst_pitch, width, rows, self.device)
+            if self.bulk_copy == "narrow":
+                self._ops.copy_rows_narrow(src[i:i + 24], dst[i:i + 24], src_pitch, dst_pitch, width, rows, self.device,
+                                           max_ctas=self.NARROW_CTAS)
+            else:
+                self._ops.copy_rows_multi(src[i:i + 24], dst[i:i + 24], src_pitch, dst_pitch, width, rows, self.device)
 
     # ---- block means of query and key, pooled on the sequence shards ----------------------------------------
     def enable_pooling(self, block_size: int) -> None:

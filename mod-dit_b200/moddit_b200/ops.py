@@ -584,10 +584,11 @@ class TileLists(tuple):
         return self.counts, self.entries, self.order
 
 
-def tile_lists(mask: torch.Tensor, block_size: int, n_tokens: int, kv_block_limit: Optional[int] = None
-               ) -> TileLists:
+def tile_lists(mask: torch.Tensor, block_size: int, n_tokens: int, kv_block_limit: Optional[int] = None,
+               heads_per_group: Optional[int] = None) -> TileLists:
     """Work lists of the sparse forward for a bool (H, nbq, nbk) block mask, plus the start order of the
-    (head, query-tile pair) work items (long lists first)."""
+    (head, query-tile pair) work items (long lists first).  With `heads_per_group` the order is made group by
+    group of that many heads (`moddit_order_pairs`), for one launch per group over slices of the lists."""
     dev = _need_cuda(mask)
     if mask.dtype != torch.bool or mask.dim() != 3:
         raise ValueError("mask must be a bool (H, nbq, nbk) tensor")
@@ -599,9 +600,13 @@ def tile_lists(mask: torch.Tensor, block_size: int, n_tokens: int, kv_block_limi
     entries = torch.empty(Hm, npairs, ntq, device=dev, dtype=torch.int32)
     order = torch.empty(Hm, npairs, device=dev, dtype=torch.int32)
     lim = nbk if kv_block_limit is None else int(kv_block_limit)
+    grouped = heads_per_group is not None and 0 < int(heads_per_group) < Hm
     with torch.cuda.device(dev), _timed("moddit_tile_lists", dev):
         check(lib.moddit_tile_lists(_ptr(mask), Hm, nbq, nbk, block_size, n_tokens, lim, _ptr(counts),
-                                    _ptr(entries), _ptr(order), _stream(dev)), "moddit_tile_lists")
+                                    _ptr(entries), None if grouped else _ptr(order), _stream(dev)), "moddit_tile_lists")
+        if grouped:
+            check(lib.moddit_order_pairs(_ptr(counts), Hm, npairs, int(heads_per_group), _ptr(order), _stream(dev)),
+                  "moddit_order_pairs")
     return TileLists(counts, entries, order)
 
 
@@ -630,6 +635,17 @@ def copy_rows_multi(src_ptrs, dst_ptrs, src_pitch: int, dst_pitch: int, width_by
     with torch.cuda.device(device), _timed("moddit_copy_rows", device):
         check(lib.moddit_copy_rows_multi(src, dst, n, src_pitch, dst_pitch, width_bytes, rows, _stream(device)),
               "moddit_copy_rows_multi")
+
+
+def copy_rows_narrow(src_ptrs, dst_ptrs, src_pitch: int, dst_pitch: int, width_bytes: int, rows: int,
+                     device: torch.device, max_ctas: int = 48) -> None:
+    """`copy_rows_multi` on at most `max_ctas` CTAs (an exchange that runs beside other kernels)."""
+    n = len(src_ptrs)
+    src = (ctypes.c_void_p * n)(*src_ptrs)
+    dst = (ctypes.c_void_p * n)(*dst_ptrs)
+    with torch.cuda.device(device), _timed("moddit_copy_rows", device):
+        check(lib.moddit_copy_rows_narrow(src, dst, n, src_pitch, dst_pitch, width_bytes, rows, int(max_ctas),
+                                          _stream(device)), "moddit_copy_rows_narrow")
 
 
 # ---------------------------------------------------------------------------------------------

@@ -87,9 +87,9 @@ def state():
     st = create_adaptive_mask_state("hunyuan", he - hb, T * F, 128, F, T, warmup_steps=2, top_k=6, predict_T=5, block_size=bs)
     st["score_producer"] = "pooled"
     return st
-st_a, st_b = state(), state()
+st_a, st_b, st_c = state(), state(), state()
 side = torch.cuda.Stream(device=dev)
-for step in range(3):
+for step in range(4):
     qh, kh, vh = (t[:, hb:he].contiguous().to(dev) for t in (q, k, v))
     out_a, _ = SparseAttentionWithMap(qh, kh, vh, st_a, log, current_step=step)
     shard = [t[:, :, b:e].contiguous().to(dev) for t in (q, k, v)]
@@ -105,6 +105,19 @@ for step in range(3):
     assert torch.equal(out_a, out_b), step
     if step == 2:
         assert torch.equal(st_a["mask"], st_b["mask"])
+    # (c) the heads arrive in two groups and the sparse forward runs once per group, scattering its rows to the peers
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        (qg, kg, vg), group_ready = pr.seq_to_head_groups(shard, [0, 1, 2], 2, channel=0)
+    pooled = pr.pool_to_head(shard[0], shard[1], channel=1)
+    st_c["_head_groups"] = 2
+    scatter = pr.begin_output(channel=1)
+    out_c, _ = SparseAttentionWithMap(qg, kg, vg, st_c, log, current_step=step, pooled_qk=pooled,
+                                      head_group_ready=group_ready, output_scatter=scatter)
+    out_c = pr.finish_output(channel=1).clone() if out_c is None else pr.head_to_seq(out_c, channel=1).clone()
+    gathered = [torch.empty_like(out_a) for _ in range(world)]
+    dist.all_gather(gathered, out_a.contiguous())
+    assert torch.equal(out_c, torch.cat(gathered, dim=1)[:, :, b:e]), step
     torch.cuda.synchronize(); dist.barrier()
 ops.raise_on_status(dev)
 dist.barrier(); dist.destroy_process_group()

@@ -149,3 +149,36 @@ def test_medium_shape_against_chunked_oracle(ops):
     out = ops.sparse_attn_fwd(q.cuda(), k.cuda(), v.cuda(), counts, entries)
     ref = orc.masked_attention(q, k, v, mask, bs)
     _check(out, ref)
+
+
+def test_head_groups_give_the_same_output_as_one_launch(ops):
+    """One launch per group of heads over slices of the lists (order made group by group) against one launch."""
+    from MoD.mod.attn_mask import AttentionSparseEngine
+    torch.manual_seed(7)
+    H, N, D, bs = 5, 1536, 128, 128
+    q, k, v = (torch.randn(1, H, N, D, device="cuda").bfloat16() for _ in range(3))
+    mask = torch.rand(H, N // bs, N // bs, device="cuda") < 0.35
+    idx = torch.arange(N // bs, device="cuda")
+    mask[:, idx, idx] = True
+    whole = ops.tile_lists(mask, bs, N)
+    ref = AttentionSparseEngine(q, k, v, mask, block_size=bs, _lists=whole)
+    for groups in (2, 3, 5):
+        hpg = (H + groups - 1) // groups
+        lists = ops.tile_lists(mask, bs, N, heads_per_group=hpg)
+        npairs = lists.counts.shape[1]
+        live = torch.arange(lists.entries.shape[-1], device="cuda")[None, None, :] < whole.counts[:, :, None]
+        assert torch.equal(lists.counts, whole.counts) and torch.equal(lists.entries[live], whole.entries[live])
+        flat = lists.order.view(-1)
+        for g in range(groups):                               # every group's order is a permutation of its own items
+            h0, h1 = g * hpg, min(H, (g + 1) * hpg)
+            if h0 < h1:
+                part = flat[h0 * npairs:h1 * npairs].sort().values
+                assert torch.equal(part, torch.arange((h1 - h0) * npairs, device="cuda", dtype=torch.int32))
+        ev = torch.cuda.Event()
+        ev.record()
+        ready = [ev if g % 2 == 0 else None for g in range(groups)]
+        out = AttentionSparseEngine(q, k, v, mask, block_size=bs, _lists=lists, _group_ready=ready)
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref), groups
+    ops.raise_on_status(q.device)
+
