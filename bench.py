@@ -378,7 +378,7 @@ def run_ours(args):
     # and every launch is counted; the per-stage breakdown comes from a few untimed steps afterwards, so that
     # two event records per entry-point call do not load the host while short multi-GPU steps are timed.
     step_no = 2 + args.warmup
-    repeat_ms, repeat_attn, launches = [], [], 0
+    repeat_ms, repeat_attn, repeat_host, launches = [], [], [], 0
     repeats = 1
     r = 0
     sampler.mark_begin()
@@ -387,17 +387,20 @@ def run_ours(args):
         ops.stage_timing(True, only=("moddit_sparse_attn_fwd",))
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
+        host0 = time.perf_counter()
         for i in range(args.steps):
             layer(q_in, k_in, v_in, step_no)
             step_no += 1
+        host_ms = (time.perf_counter() - host0) * 1e3       # what the host needed to queue the steps (no waiting)
         ev1.record()
         barrier()
         ms = ev0.elapsed_time(ev1)
         attn = sum(t for _, t in ops.stage_records()) / args.steps
         launches = ops.launches_recorded()
-        (ms_max, attn_max), _ = hx.reduce([ms, attn], [0.0])
+        (ms_max, attn_max, host_max), _ = hx.reduce([ms, attn, host_ms], [0.0])
         repeat_ms.append(ms_max)
         repeat_attn.append(attn_max)
+        repeat_host.append(host_max)
         if r == 0:
             want = args.repeats if args.repeats > 0 else int(min(25, max(1, -(-1000.0 // max(ms_max, 1e-3)))))
             repeats = max(1, want)
@@ -532,6 +535,7 @@ def run_ours(args):
             "sparsity": round(sparsity_sum / world, 4),
             "sparsity_per_head": {"min": round(-sp_min_neg, 4), "max": round(sp_max, 4)},
             "reshard": hx.reshard,
+            "host_queue_ms_per_step": round(sorted(repeat_host)[len(repeat_host) // 2] / args.steps, 3),
             "repeats": {"n": repeats, "reported": "median", "ms_per_step_min": round(min(repeat_ms) / args.steps, 3),
                         "ms_per_step_max": round(max(repeat_ms) / args.steps, 3)},
             "mask_pred_ms": round(pred_ms, 3), "mask_pred_pct": round(100.0 * pred_ms / max(pred_ms + attn_ms, 1e-9), 2),
