@@ -209,6 +209,7 @@ class Harness:
         self.N = T * Hh * Ww + self.cfg["text_tokens"]
         self.comm_stream = torch.cuda.Stream(device=self.dev) if self.world > 1 else None
         self.qk_stream = torch.cuda.Stream(device=self.dev) if self.world > 1 else None
+        self.timeline = None            # a list while --timeline steps run: one dict of timing events per step
         self.resharder, self.value_group, self.reshard = None, None, "none"
         if self.world > 1:
             self._setup_resharder()
@@ -282,6 +283,10 @@ class Harness:
                                             head_group_ready=group_ready, output_scatter=scatter)
             return resharder.finish_output(channel=0) if out is None else resharder.head_to_seq(out, channel=0)
         state.pop("_head_groups", None)
+        marks = None
+        if world > 1 and self.timeline is not None:
+            marks = {k: torch.cuda.Event(enable_timing=True) for k in ("in", "v", "qk", "pool", "out")}
+            marks["in"].record(torch.cuda.current_stream(dev))
         if world > 1:
             main = torch.cuda.current_stream(dev)
             self.comm_stream.wait_stream(main)
@@ -289,7 +294,7 @@ class Harness:
                 # value is not needed until the attention kernel: it travels while the mask is predicted
                 vs_h = (resharder.seq_to_head(vs, 2, channel=1) if resharder is not None
                         else mdist.seq_to_head(vs, group=self.value_group))
-                ready = torch.cuda.Event()
+                ready = marks["v"] if marks else torch.cuda.Event()
                 ready.record(self.comm_stream)
             if resharder is not None:
                 # the mask needs only block means of query and key: they are pooled on the sequence shards and
@@ -297,10 +302,12 @@ class Harness:
                 self.qk_stream.wait_stream(main)
                 with torch.cuda.stream(self.qk_stream):
                     qh, kh = resharder.seq_to_head_many([qs, ks], [0, 1], channel=0)
-                    qk_ready = torch.cuda.Event()
+                    qk_ready = marks["qk"] if marks else torch.cuda.Event()
                     qk_ready.record(self.qk_stream)
                 if pooled_mode:
                     pooled = resharder.pool_to_head(qs, ks, channel=0)
+                    if marks:
+                        marks["pool"].record(main)
                 else:
                     main.wait_event(qk_ready)
                     qk_ready = None
@@ -321,6 +328,9 @@ class Harness:
             else:
                 # sparse steps wrote their rows straight into the peers' buffers; dense steps did not
                 out = resharder.finish_output(channel=0) if out is None else resharder.head_to_seq(out, channel=0)
+            if marks and resharder is not None and pooled_mode:
+                marks["out"].record(main)
+                self.timeline.append(marks)
         return out
 
     def head_groups(self):
@@ -420,6 +430,25 @@ def run_ours(args):
     records = ops.stage_records()
     ops.stage_timing(False)
     ops.check_health(dev)
+    timeline = None
+    if args.timeline and world > 1 and hx.head_groups() == 1 and hx.resharder is not None:
+        # where a step's time goes on this rank: milliseconds from the layer's first operation to the arrival of
+        # value / query+key, to the end of the pooling exchange, and to the end of the output barrier
+        hx.timeline = []
+        ops.stage_timing(True, only=("moddit_sparse_attn_fwd",))
+        for i in range(10):
+            layer(q_in, k_in, v_in, step_no + 10 + i)
+        torch.cuda.synchronize(dev)
+        attn_tl = sum(t for _, t in ops.stage_records()) / 10
+        ops.stage_timing(False)
+        tl = {k: statistics.median(m["in"].elapsed_time(m[k]) for m in hx.timeline) for k in ("v", "qk", "pool", "out")}
+        hx.timeline = None
+        timeline = {"value_arrived_ms": round(tl["v"], 3), "query_key_arrived_ms": round(tl["qk"], 3),
+                    "pooled_means_exchanged_ms": round(tl["pool"], 3), "output_barrier_done_ms": round(tl["out"], 3),
+                    "attention_kernel_ms": round(attn_tl, 3),
+                    "attention_started_ms": round(tl["out"] - attn_tl, 3), "rank": rank,
+                    "note": "medians over 10 steps on rank 0, from the layer's first operation; attention_started "
+                            "= output_barrier_done - attention_kernel, an upper bound (it includes the output barrier)"}
 
     mask = state["mask"]
     flops_local = kept_flops(mask, bs, D)
@@ -535,6 +564,7 @@ def run_ours(args):
             "sparsity": round(sparsity_sum / world, 4),
             "sparsity_per_head": {"min": round(-sp_min_neg, 4), "max": round(sp_max, 4)},
             "reshard": hx.reshard,
+            "timeline": timeline,
             "host_queue_ms_per_step": round(sorted(repeat_host)[len(repeat_host) // 2] / args.steps, 3),
             "repeats": {"n": repeats, "reported": "median", "ms_per_step_min": round(min(repeat_ms) / args.steps, 3),
                         "ms_per_step_max": round(max(repeat_ms) / args.steps, 3)},
@@ -874,6 +904,9 @@ def main():
                     help="several GPUs: how the sequence->head pieces travel, copy engines (no SM taken) or this "
                          "library's copy kernel (plain peer stores)")
     ap.add_argument("--narrow-ctas", type=int, default=0, help="CTAs of one exchange with --bulk-copy narrow")
+    ap.add_argument("--timeline", action="store_true",
+                    help="several GPUs, one head group: ten extra steps with events at the arrival of the inputs and the "
+                         "end of the step")
     ap.add_argument("--copy-streams", type=int, default=0, help="side streams of one exchange with --bulk-copy dma")
     ap.add_argument("--head-groups", type=int, default=0,
                     help="several GPUs: the sequence->head exchange delivers the local heads in this many groups and "
