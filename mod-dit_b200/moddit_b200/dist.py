@@ -136,6 +136,32 @@ def head_to_seq(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> t
     return out
 
 
+def group_pieces(world: int, rank: int, heads_per_rank: int, groups: int, row_bytes: int, head_bytes: int,
+                 x_ptrs, peer_bases):
+    """The strided copies of a sequence->head exchange delivered in `groups` runs of the local heads.
+
+    x_ptrs[t]: address of this rank's (H, N/P, D) shard of tensor t; peer_bases[t][p]: address of rank p's
+    (H/P, N, D) buffer for tensor t; row_bytes = one (head, sequence shard) piece, head_bytes = one head in an
+    owner's buffer.  Returns a list with one (src addresses, dst addresses, rows) triple per run: every piece is
+    `rows` rows of row_bytes, source pitch row_bytes, destination pitch head_bytes.  Peers are visited starting
+    with the rank itself, so that the ranks do not all write to the same owner at once."""
+    groups = max(1, min(int(groups), heads_per_rank))
+    hpg = (heads_per_rank + groups - 1) // groups
+    out = []
+    for g in range(groups):
+        h0, h1 = g * hpg, min(heads_per_rank, (g + 1) * hpg)
+        if h0 >= h1:
+            break
+        src, dst = [], []
+        for step in range(world):
+            peer = (rank + step) % world
+            for t, x in enumerate(x_ptrs):
+                src.append(x + (peer * heads_per_rank + h0) * row_bytes)
+                dst.append(peer_bases[t][peer] + h0 * head_bytes + rank * row_bytes)
+        out.append((src, dst, h1 - h0))
+    return out
+
+
 class PeerResharder:
     """Sequence<->head re-shard through peer-mapped (symmetric) buffers on one NVLink/NVSwitch node.
 
@@ -210,26 +236,16 @@ class PeerResharder:
         for x in xs:
             if tuple(x.shape) != (1, self.H, self.ns, self.D) or x.dtype != self.dtype or not x.is_contiguous():
                 raise ValueError("inputs must be contiguous (1, H, N/P, D) tensors of the configured dtype")
-        groups = max(1, min(int(groups), self.hp))
-        hpg = (self.hp + groups - 1) // groups
         sync = self.in_handles[slots[0]]
         cur = torch.cuda.current_stream(self.device)
         sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # readers of the previous contents are done
         row = self.ns * self.D * self.esize                            # bytes of one (head, sequence shard) piece
         head = self.N * self.D * self.esize                            # bytes of one head in an owner's buffer
+        bases = [[int(p) for p in self.in_handles[slot].buffer_ptrs] for slot in slots]
         events = []
-        for g in range(groups):
-            h0, h1 = g * hpg, min(self.hp, (g + 1) * hpg)
-            if h0 >= h1:
-                events.append(events[-1])
-                continue
-            src, dst = [], []
-            for step in range(self.world):
-                peer = (self.rank + step) % self.world
-                for x, slot in zip(xs, slots):
-                    src.append(x.data_ptr() + (peer * self.hp + h0) * row)
-                    dst.append(int(self.in_handles[slot].buffer_ptrs[peer]) + h0 * head + self.rank * row)
-            self._bulk(src, dst, row, head, row, h1 - h0)
+        for src, dst, rows in group_pieces(self.world, self.rank, self.hp, groups, row, head,
+                                           [x.data_ptr() for x in xs], bases):
+            self._bulk(src, dst, row, head, row, rows)
             sync.barrier(channel=channel, timeout_ms=self.timeout_ms)  # every rank's rows of this run have landed
             ev = torch.cuda.Event()
             ev.record(cur)

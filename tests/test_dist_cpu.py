@@ -80,3 +80,44 @@ def test_pool_partition_covers_every_block_once():
         md.pool_partition(1000, 128, 8, 0)      # a shard shorter than a block
     with pytest.raises(ValueError):
         md.pool_partition(1001, 128, 2, 0)
+
+
+def test_group_pieces_place_every_row_once():
+    """The exchange by groups of heads, emulated on byte arrays for 2, 4 and 8 ranks: after every rank's pieces of
+    groups 0..g have been copied, the owners hold exactly the heads of those groups, and after the last group the
+    whole head-major tensor; nothing is written twice."""
+    import numpy as np
+    md = _load_dist_module()
+    for world, H, N, D, groups in ((2, 8, 12, 2, 3), (4, 24, 16, 2, 2), (8, 24, 32, 1, 3), (8, 24, 32, 1, 1), (4, 8, 8, 3, 5)):
+        hp, ns, esize, T = H // world, N // world, 2, 3
+        row, head = ns * D * esize, N * D * esize
+        full = [np.random.default_rng(t).integers(1, 255, size=(H, N, D * esize), dtype=np.uint8) for t in range(T)]
+        # one flat address space: shards of every rank, then owners' buffers
+        shard_bytes, buf_bytes = H * row, hp * head
+        x_ptr = lambda r, t: (r * T + t) * shard_bytes
+        b_ptr = lambda r, t: world * T * shard_bytes + (r * T + t) * buf_bytes
+        mem = np.zeros(world * T * (shard_bytes + buf_bytes), dtype=np.uint8)
+        written = np.zeros_like(mem)
+        for r in range(world):
+            for t in range(T):
+                mem[x_ptr(r, t):x_ptr(r, t) + shard_bytes] = full[t][:, r * ns:(r + 1) * ns].reshape(-1)
+        plans = [md.group_pieces(world, r, hp, groups, row, head, [x_ptr(r, t) for t in range(T)],
+                                 [[b_ptr(p, t) for p in range(world)] for t in range(T)]) for r in range(world)]
+        n_groups = len(plans[0])
+        assert all(len(p) == n_groups for p in plans) and n_groups == min(groups, hp, -(-hp // -(-hp // min(groups, hp))))
+        hpg = -(-hp // min(groups, hp))
+        for g in range(n_groups):
+            for r in range(world):
+                src, dst, rows = plans[r][g]
+                assert len(src) == len(dst) == world * T
+                for s_, d_ in zip(src, dst):
+                    for j in range(rows):
+                        mem[d_ + j * head:d_ + j * head + row] = mem[s_ + j * row:s_ + j * row + row]
+                        written[d_ + j * head:d_ + j * head + row] += 1
+            upto = min(hp, (g + 1) * hpg)
+            for r in range(world):
+                for t in range(T):
+                    got = mem[b_ptr(r, t):b_ptr(r, t) + buf_bytes].reshape(hp, N, D * esize)
+                    assert np.array_equal(got[:upto], full[t][r * hp:r * hp + upto])
+        assert written[world * T * shard_bytes:].min() == 1 and written.max() == 1
+
