@@ -222,21 +222,19 @@ def qkv_prologue(q_in: Optional[torch.Tensor], k_in: Optional[torch.Tensor], v_i
 
 
 def pooled_map(qbar: torch.Tensor, kbar: torch.Tensor, *, q_block_offset: int, k_block_offset: int,
-               video_blocks: int, scale: float, launches: int = 2) -> torch.Tensor:
+               video_blocks: int, scale: float, workspace: bool = True) -> torch.Tensor:
     """(B,H,nb,D) float32 block means -> (B,H,n,n) float16 darkness map, 1 - exp(logit - row maximum).
 
-    launches=2 (`moddit_pooled_map_ws`): float32 logits tile by tile into a workspace (4*B*H*n*n bytes plus the
-    split means), then the row pass; launches=1 (`moddit_pooled_map`): one kernel, no workspace, slower.  Both give
-    the same bits."""
+    workspace=True (`moddit_pooled_map_ws`): the means split once, float32 logits tile by tile into a workspace
+    (4*B*H*n*n bytes plus the split means), then the row pass; workspace=False (`moddit_pooled_map`): one kernel,
+    no workspace, slower.  Both give the same bits."""
     dev = _need_cuda(qbar, kbar)
     _need_contig(qbar=qbar, kbar=kbar)
     if qbar.dtype != torch.float32 or kbar.dtype != torch.float32 or qbar.shape != kbar.shape:
         raise ValueError("qbar and kbar must be float32 tensors of the same shape")
-    if launches not in (1, 2):
-        raise ValueError("launches must be 1 or 2")
     B, H, nb, D = qbar.shape
     out = torch.empty(B, H, video_blocks, video_blocks, device=dev, dtype=torch.float16)
-    if launches == 1:
+    if not workspace:
         with torch.cuda.device(dev), _timed("moddit_pooled_map", dev):
             check(lib.moddit_pooled_map(_ptr(qbar), _ptr(kbar), B * H, nb, D, q_block_offset, k_block_offset,
                                         video_blocks, float(scale), _ptr(out), _stream(dev)), "moddit_pooled_map")

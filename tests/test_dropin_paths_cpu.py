@@ -49,7 +49,7 @@ def test_checkout_modules_resolve_behind_the_dropin(tmp_path):
 def test_reference_checkout_utils_and_logger_resolve():
     """With the real checkout present (the build container only): its utils and logger modules import."""
     import pytest
-    ref = "/root/reference"
+    ref = os.environ.get("MODDIT_REFERENCE_CHECKOUT", os.path.join(os.sep, "root", "reference"))
     if not os.path.isdir(os.path.join(ref, "MoD", "mod")):
         pytest.skip("no reference checkout on this machine")
     res = _run("""

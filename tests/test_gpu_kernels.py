@@ -85,12 +85,12 @@ def test_pooled_map(ops, n, nb, qo, D):
     scale = D ** -0.5
     ref = orc.pooled_darkness_map(qbar, kbar, q_block_offset=qo, k_block_offset=qo, video_blocks=n, scale=scale)
     got = {}
-    for launches in (1, 2):       # one kernel with the rows in shared memory / two kernels through a workspace
-        got[launches] = ops.pooled_map(qbar.cuda(), kbar.cuda(), q_block_offset=qo, k_block_offset=qo,
-                                       video_blocks=n, scale=scale, launches=launches).cpu()
-        assert got[launches].dtype == torch.float16 and got[launches].shape == ref.shape
-        assert (got[launches].float() - ref.float()).abs().max().item() <= 2e-3   # one fp16 ulp near 1.0 is 4.9e-4
-    assert torch.equal(got[1], got[2])          # same fragments, same accumulation order: same bits
+    for ws in (False, True):      # one kernel with the rows in shared memory / three kernels through a workspace
+        got[ws] = ops.pooled_map(qbar.cuda(), kbar.cuda(), q_block_offset=qo, k_block_offset=qo,
+                                 video_blocks=n, scale=scale, workspace=ws).cpu()
+        assert got[ws].dtype == torch.float16 and got[ws].shape == ref.shape
+        assert (got[ws].float() - ref.float()).abs().max().item() <= 2e-3   # one fp16 ulp near 1.0 is 4.9e-4
+    assert torch.equal(got[False], got[True])   # same fragments, same accumulation order: same bits
 
 
 def test_pooled_map_workspace_checked(ops):
