@@ -209,6 +209,7 @@ class Harness:
         self.N = T * Hh * Ww + self.cfg["text_tokens"]
         self.comm_stream = torch.cuda.Stream(device=self.dev) if self.world > 1 else None
         self.qk_stream = torch.cuda.Stream(device=self.dev) if self.world > 1 else None
+        self.stepped = False            # a step has run: the re-shard buffers were last used before a closing barrier
         self.timeline = None            # a list while --timeline steps run: one dict of timing events per step
         self.resharder, self.value_group, self.reshard = None, None, "none"
         if self.world > 1:
@@ -275,13 +276,16 @@ class Harness:
             main = torch.cuda.current_stream(dev)
             self.qk_stream.wait_stream(main)
             with torch.cuda.stream(self.qk_stream):
-                (qh, kh, vh), group_ready = resharder.seq_to_head_groups([qs, ks, vs], [0, 1, 2], groups, channel=0)
-            pooled = resharder.pool_to_head(qs, ks, channel=0)
-            scatter = resharder.begin_output(channel=0)
+                (qh, kh, vh), group_ready = resharder.seq_to_head_groups([qs, ks, vs], [0, 1, 2], groups, channel=0,
+                                                                         quiesced=self.stepped)
+            pooled = resharder.pool_to_head(qs, ks, channel=0, quiesced=self.stepped)
+            scatter = resharder.begin_output(channel=0, consumed=self.stepped)
             state["_head_groups"] = groups
             out, _ = SparseAttentionWithMap(qh, kh, vh, state, self.logger, current_step=step, pooled_qk=pooled,
                                             head_group_ready=group_ready, output_scatter=scatter)
-            return resharder.finish_output(channel=0) if out is None else resharder.head_to_seq(out, channel=0)
+            out = resharder.finish_output(channel=0) if out is None else resharder.head_to_seq(out, channel=0)
+            self.stepped = True
+            return out
         state.pop("_head_groups", None)
         marks = None
         if world > 1 and self.timeline is not None:
@@ -292,7 +296,9 @@ class Harness:
             self.comm_stream.wait_stream(main)
             with torch.cuda.stream(self.comm_stream):
                 # value is not needed until the attention kernel: it travels while the mask is predicted
-                vs_h = (resharder.seq_to_head(vs, 2, channel=1) if resharder is not None
+                # after the first call every rank has passed the barrier that closed the previous step (the output
+                # exchange) with all its kernels done, so the barriers that would open this step's exchanges are skipped
+                vs_h = (resharder.seq_to_head(vs, 2, channel=1, quiesced=self.stepped) if resharder is not None
                         else mdist.seq_to_head(vs, group=self.value_group))
                 ready = marks["v"] if marks else torch.cuda.Event()
                 ready.record(self.comm_stream)
@@ -301,18 +307,19 @@ class Harness:
                 # sent to the head owners, so the prediction runs while the rows themselves still travel
                 self.qk_stream.wait_stream(main)
                 with torch.cuda.stream(self.qk_stream):
-                    qh, kh = resharder.seq_to_head_many([qs, ks], [0, 1], channel=0)
+                    qh, kh = resharder.seq_to_head_many([qs, ks], [0, 1], channel=0, quiesced=self.stepped)
                     qk_ready = marks["qk"] if marks else torch.cuda.Event()
                     qk_ready.record(self.qk_stream)
                 if pooled_mode:
-                    pooled = resharder.pool_to_head(qs, ks, channel=0)
+                    pooled = resharder.pool_to_head(qs, ks, channel=0, quiesced=self.stepped)
                     if marks:
                         marks["pool"].record(main)
                 else:
                     main.wait_event(qk_ready)
                     qk_ready = None
                 qs, ks = qh, kh
-                scatter = resharder.begin_output(channel=0)
+                # the pooling exchange above ended with a barrier on this stream: the previous output is consumed
+                scatter = resharder.begin_output(channel=0, consumed=pooled_mode and self.stepped)
             else:
                 qs, ks = mdist.seq_to_head(qs), mdist.seq_to_head(ks)
             vs = vs_h
@@ -328,6 +335,7 @@ class Harness:
             else:
                 # sparse steps wrote their rows straight into the peers' buffers; dense steps did not
                 out = resharder.finish_output(channel=0) if out is None else resharder.head_to_seq(out, channel=0)
+                self.stepped = True
             if marks and resharder is not None and pooled_mode:
                 marks["out"].record(main)
                 self.timeline.append(marks)
@@ -503,6 +511,10 @@ def run_ours(args):
                     d.copy_(h, non_blocking=True)
                 in_ready[b].record(s_in)
             main.wait_event(in_ready[b])
+            if world > 1:
+                # the output lives in the re-shard's own buffer, which the next step's kernels on the peers write
+                # again: the copy of the previous output to the host has to be out of it first
+                main.wait_event(out_done[1 - b])
             out = layer(dev_in[b][0], dev_in[b][1], dev_in[b][2], step)
             in_free[b].record(main)
             done = torch.cuda.Event()

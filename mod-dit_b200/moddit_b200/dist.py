@@ -205,18 +205,25 @@ class PeerResharder:
         self.output = symm_mem.empty((1, self.H, self.ns, self.D), dtype=dtype, device=device)
         self.out_handle = symm_mem.rendezvous(self.output, self.group)
 
-    def seq_to_head(self, x: torch.Tensor, slot: int, channel: int = 0) -> torch.Tensor:
+    # `quiesced=True` on the calls below skips the barrier that opens them ("every rank has finished with the
+    # previous contents").  It is for a caller whose previous use of these buffers was followed, on every rank and
+    # on the stream this call is ordered behind, by one of this class's closing barriers - e.g. the step before
+    # ended with `finish_output` or `head_to_seq`: a rank passes that barrier only when all ranks have reached it,
+    # i.e. have finished every kernel that read the buffers.
+
+    def seq_to_head(self, x: torch.Tensor, slot: int, channel: int = 0, quiesced: bool = False) -> torch.Tensor:
         """Push this rank's (1, H, N/P, D) shard into slot `slot` of every owner; returns the local head shard
         (1, H/P, N, D), valid on the current stream once the call returns."""
-        return self.seq_to_head_many([x], [slot], channel)[0]
+        return self.seq_to_head_many([x], [slot], channel, quiesced)[0]
 
-    def seq_to_head_many(self, xs, slots, channel: int = 0):
+    def seq_to_head_many(self, xs, slots, channel: int = 0, quiesced: bool = False):
         """Several tensors between one pair of barriers (slot i receives xs[i])."""
         for x in xs:
             if tuple(x.shape) != (1, self.H, self.ns, self.D) or x.dtype != self.dtype or not x.is_contiguous():
                 raise ValueError("inputs must be contiguous (1, H, N/P, D) tensors of the configured dtype")
         sync = self.in_handles[slots[0]]
-        sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # readers of the previous contents are done
+        if not quiesced:
+            sync.barrier(channel=channel, timeout_ms=self.timeout_ms)  # readers of the previous contents are done
         row = self.ns * self.D * self.esize                            # bytes of one (head, sequence shard) piece
         src, dst = [], []
         for step in range(self.world):
@@ -228,7 +235,7 @@ class PeerResharder:
         sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # every rank's stores have landed
         return [self.inputs[slot] for slot in slots]
 
-    def seq_to_head_groups(self, xs, slots, groups: int, channel: int = 0):
+    def seq_to_head_groups(self, xs, slots, groups: int, channel: int = 0, quiesced: bool = False):
         """`seq_to_head_many` delivered group of heads by group of heads: the local heads are cut into `groups` runs of
         ceil(H/P / groups) heads; run g of every tensor is sent to every owner, then a barrier, then event g is
         recorded on the current stream - a consumer that works head by head starts on run 0 while the later runs
@@ -238,7 +245,8 @@ class PeerResharder:
                 raise ValueError("inputs must be contiguous (1, H, N/P, D) tensors of the configured dtype")
         sync = self.in_handles[slots[0]]
         cur = torch.cuda.current_stream(self.device)
-        sync.barrier(channel=channel, timeout_ms=self.timeout_ms)     # readers of the previous contents are done
+        if not quiesced:
+            sync.barrier(channel=channel, timeout_ms=self.timeout_ms)  # readers of the previous contents are done
         row = self.ns * self.D * self.esize                            # bytes of one (head, sequence shard) piece
         head = self.N * self.D * self.esize                            # bytes of one head in an owner's buffer
         bases = [[int(p) for p in self.in_handles[slot].buffer_ptrs] for slot in slots]
@@ -311,7 +319,7 @@ class PeerResharder:
         self.pooled = symm_mem.empty((2, 1, self.hp, self.pool_nb, self.D), dtype=torch.float32, device=self.device)
         self.pooled_handle = symm_mem.rendezvous(self.pooled, self.group)
 
-    def pool_to_head(self, q: torch.Tensor, k: torch.Tensor, channel: int = 0):
+    def pool_to_head(self, q: torch.Tensor, k: torch.Tensor, channel: int = 0, quiesced: bool = False):
         """Block means of this rank's (1, H, N/P, D) query and key shards, delivered to the head owners.
 
         Returns this rank's (1, H/P, nb, D) float32 means of query and key - equal, bit for bit, to pooling
@@ -324,7 +332,8 @@ class PeerResharder:
         first, end, halo_rows, tail_rows = self.pool_part
         bs = self.pool_bs
         row = self.D * self.esize
-        self.halo_handle.barrier(channel=channel, timeout_ms=self.timeout_ms)   # last call's readers are done
+        if not quiesced:
+            self.halo_handle.barrier(channel=channel, timeout_ms=self.timeout_ms)   # last call's readers are done
         if tail_rows:
             nxt = self.rank + 1
             base = int(self.halo_handle.buffer_ptrs[nxt])
@@ -342,10 +351,13 @@ class PeerResharder:
         return self.pooled[0], self.pooled[1]
 
     # ---- output re-shard fused into the attention kernel's epilogue ------------------------------------
-    def begin_output(self, channel: int = 0):
+    def begin_output(self, channel: int = 0, consumed: bool = False):
         """Call before a kernel that stores its output rows straight into the peers' buffers; returns the
-        `scatter` argument for `ops.sparse_attn_fwd` (peer buffer pointers, first global head of this rank)."""
-        self.out_handle.barrier(channel=channel, timeout_ms=self.timeout_ms)   # previous output has been consumed
+        `scatter` argument for `ops.sparse_attn_fwd` (peer buffer pointers, first global head of this rank).
+        consumed=True skips the barrier: for a caller that, on every rank, read the previous output on this stream
+        and has since passed another of this class's barriers on it (`pool_to_head` ends with one)."""
+        if not consumed:
+            self.out_handle.barrier(channel=channel, timeout_ms=self.timeout_ms)   # previous output has been consumed
         return [int(p) for p in self.out_handle.buffer_ptrs], self.rank * self.hp
 
     def finish_output(self, channel: int = 0) -> torch.Tensor:

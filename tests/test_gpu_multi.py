@@ -96,10 +96,12 @@ for step in range(4):
     main = torch.cuda.current_stream(dev)
     side.wait_stream(main)
     with torch.cuda.stream(side):
-        qs, ks = pr.seq_to_head_many(shard[:2], [0, 1], channel=0)
-        vs = pr.seq_to_head(shard[2], 2, channel=0)
+        # after the first step the previous use of the buffers ended with a closing barrier (finish_output below):
+        # the opening barriers may be skipped
+        qs, ks = pr.seq_to_head_many(shard[:2], [0, 1], channel=0, quiesced=step > 0)
+        vs = pr.seq_to_head(shard[2], 2, channel=0, quiesced=step > 0)
         ready = torch.cuda.Event(); ready.record(side)
-    pooled = pr.pool_to_head(shard[0], shard[1], channel=1)
+    pooled = pr.pool_to_head(shard[0], shard[1], channel=1, quiesced=step > 0)
     out_b, _ = SparseAttentionWithMap(qs, ks, vs, st_b, log, current_step=step, value_ready=ready, qk_ready=ready,
                                       pooled_qk=pooled)
     assert torch.equal(out_a, out_b), step
