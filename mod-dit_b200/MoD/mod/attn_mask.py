@@ -264,8 +264,8 @@ def AttentionSparseEngine(query, key, value, mask, pre_defined_mask=None, video_
         border = valid if all_kept else min(seq_len, (valid + 63) // 64 * 64)
         fwd_kw = dict(q_split=video_token_num, kv_len_lo=border, kv_len_hi=valid)
     if _group_ready is not None and len(_group_ready) > 1:
-        if lists.counts.shape[0] != query.shape[1] * query.shape[0]:
-            raise ValueError("head groups need one mask per head")
+        if query.shape[0] != 1 or lists.counts.shape[0] != query.shape[1]:
+            raise ValueError("head groups need a batch of one and one mask per head")
         return _engine_by_head_groups(query, key, value, lists, _group_ready, _scatter, **fwd_kw)
     return _ops.sparse_attn_fwd(query, key, value, counts, entries, order=order, check_status="deferred",
                                 scatter=_scatter, **fwd_kw)
