@@ -161,6 +161,7 @@ def test_head_groups_give_the_same_output_as_one_launch(ops):
     idx = torch.arange(N // bs, device="cuda")
     mask[:, idx, idx] = True
     whole = ops.tile_lists(mask, bs, N)
+    assert torch.equal(whole.order.view(-1).cpu(), torch.from_numpy(orc.pair_order(whole.counts.cpu().numpy())))
     ref = AttentionSparseEngine(q, k, v, mask, block_size=bs, _lists=whole)
     for groups in (2, 3, 5):
         hpg = (H + groups - 1) // groups
@@ -174,6 +175,7 @@ def test_head_groups_give_the_same_output_as_one_launch(ops):
             if h0 < h1:
                 part = flat[h0 * npairs:h1 * npairs].sort().values
                 assert torch.equal(part, torch.arange((h1 - h0) * npairs, device="cuda", dtype=torch.int32))
+        assert torch.equal(flat.cpu(), torch.from_numpy(orc.pair_order(whole.counts.cpu().numpy(), hpg)))
         ev = torch.cuda.Event()
         ev.record()
         ready = [ev if g % 2 == 0 else None for g in range(groups)]
