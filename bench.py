@@ -569,9 +569,9 @@ def run_ours(args):
                 "frac_of_nominal_2250": round(achieved / 2250.0, 4), "kernel_ms": round(attn_ms, 3),
                 "flops_per_launch": flops_local, "traffic": load_traffic(args.workload, (hx.he - hx.hb) / H)}
         if world > 1 and hx.head_groups() > 1:
-            roof["note"] = (f"{hx.head_groups()} launches per step, one per group of heads, overlap on streams of their "
-                            "own: kernel_ms adds up their event-bracketed times and is an upper bound of the time the "
-                            "kernel takes, so achieved and frac are lower bounds; flops_per_launch is the whole step's")
+            roof["note"] = (f"{hx.head_groups()} launches per step, one per group of heads, overlapping at their ends "
+                            "on streams of their own: kernel_ms spans them, from the first launch to the end of the "
+                            "last, and flops_per_launch is the whole step's")
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,

@@ -57,6 +57,32 @@ def launches_recorded() -> int:
     return _TIMING["launches"]
 
 
+def timing_active(name: str) -> bool:
+    """Whether calls of entry point `name` are being timed right now."""
+    return bool(_TIMING["on"]) and (_TIMING["only"] is None or name in _TIMING["only"])
+
+
+class records_suppressed:
+    """Inside this context entry-point calls are still counted as launches but leave no timing record: for a caller
+    that issues several overlapping launches of one kernel on streams of their own and records their common span
+    itself (`add_span`), so that the overlap is not counted several times."""
+
+    def __enter__(self):
+        self.prev = _TIMING.get("suppress", False)
+        _TIMING["suppress"] = True
+        return self
+
+    def __exit__(self, *exc):
+        _TIMING["suppress"] = self.prev
+        return False
+
+
+def add_span(name: str, start: "torch.cuda.Event", end: "torch.cuda.Event") -> None:
+    """A timing record made by the caller (two timing events, possibly recorded on different streams)."""
+    if _TIMING["on"]:
+        _TIMING["records"].append((name, start, end))
+
+
 class _timed:
     __slots__ = ("name", "dev", "start")
 
@@ -67,7 +93,7 @@ class _timed:
         self.start = None
         if _TIMING["nvtx"]:
             torch.cuda.nvtx.range_push(self.name)
-        if _TIMING["on"] and (_TIMING["only"] is None or self.name in _TIMING["only"]):
+        if _TIMING["on"] and (_TIMING["only"] is None or self.name in _TIMING["only"]) and not _TIMING.get("suppress"):
             self.start = torch.cuda.Event(enable_timing=True)
             self.start.record(torch.cuda.current_stream(self.dev))
         return self
